@@ -1,0 +1,77 @@
+"""Ahead-of-time build of libfrnn_b200.so (sm_100a only) with nvcc.
+
+Replaces the reference's per-shape JIT (flashrnn/flashrnn/cuda_init.py:95-168 and
+cuda_init_parametric.py:92-358): one library, built once, no compile at call time.
+
+    python -m flashrnn_b200.build [--force] [--jobs N]
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+OBJ = PKG / "_build"
+LIB = PKG / "libfrnn_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v",
+]
+
+
+def _nvcc() -> str:
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(exe).exists():
+        raise RuntimeError("nvcc not found; libfrnn_b200.so cannot be built")
+    return exe
+
+
+def _sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def _stale(out: Path, deps: list[Path]) -> bool:
+    return not out.exists() or any(d.stat().st_mtime > out.stat().st_mtime for d in deps)
+
+
+def _compile(src: Path, headers: list[Path], force: bool) -> Path:
+    obj = OBJ / (src.stem + ".o")
+    if force or _stale(obj, [src] + headers):
+        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        (OBJ / (src.stem + ".log")).write_text(res.stdout + res.stderr)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stderr[-4000:]}")
+    return obj
+
+
+def build(force: bool = False, jobs: int | None = None) -> Path:
+    """Compile every .cu under csrc/ for sm_100a and link the shared library next to the package."""
+    OBJ.mkdir(exist_ok=True)
+    headers = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "frnn.h"]
+    srcs = _sources()
+    jobs = jobs or min(len(srcs), os.cpu_count() or 4)
+    with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
+        objs = list(ex.map(lambda s: _compile(s, headers, force), srcs))
+    if force or _stale(LIB, objs):
+        cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stderr[-4000:]}")
+    return LIB
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--jobs", type=int, default=None)
+    a = ap.parse_args()
+    print(build(a.force, a.jobs))
+    sys.exit(0)

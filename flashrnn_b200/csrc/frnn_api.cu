@@ -1,0 +1,322 @@
+// C ABI of libfrnn_b200.so (declared in include/frnn.h): validation, tile selection, launches.
+// No device memory is allocated or freed here and the host is never synchronised with the device,
+// except in frnn_read_device_status.
+#include "../../include/frnn.h"
+
+#include <mutex>
+
+#include "frnn_aux.cuh"
+
+namespace frnn {
+
+struct CellDims { int Gr, Gw, Gt, S, GC; };
+static bool cell_dims(int cell, CellDims* d) {
+  switch (cell) {
+    case CELL_LSTM:  *d = {4, 4, 4, 2, 4}; return true;
+    case CELL_GRU:   *d = {3, 3, 4, 1, 4}; return true;
+    case CELL_ELMAN: *d = {1, 1, 1, 1, 0}; return true;
+    case CELL_SLSTM: *d = {4, 4, 4, 4, 5}; return true;
+  }
+  return false;
+}
+
+LoopKernel get_fwd_kernel(int cell, int kt, int nt) {
+  switch (cell) {
+    case CELL_LSTM: return get_fwd_kernel_lstm(kt, nt);
+    case CELL_GRU: return get_fwd_kernel_gru(kt, nt);
+    case CELL_ELMAN: return get_fwd_kernel_elman(kt, nt);
+    case CELL_SLSTM: return get_fwd_kernel_slstm(kt, nt);
+  }
+  return LoopKernel{nullptr, 0, nullptr};
+}
+LoopKernel get_bwd_kernel(int cell, int kt, int nt) {
+  switch (cell) {
+    case CELL_LSTM: return get_bwd_kernel_lstm(kt, nt);
+    case CELL_GRU: return get_bwd_kernel_gru(kt, nt);
+    case CELL_ELMAN: return get_bwd_kernel_elman(kt, nt);
+    case CELL_SLSTM: return get_bwd_kernel_slstm(kt, nt);
+  }
+  return LoopKernel{nullptr, 0, nullptr};
+}
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+constexpr size_t kMaxDynSmem = 227 * 1024;
+constexpr size_t kStatusBytes = 256;
+
+struct WsLayout { size_t rpack_fwd, rpack_bwd, grads, dg0, total; };
+static WsLayout workspace_layout(const frnn_problem& pr, const CellDims& cd) {
+  WsLayout w;
+  const size_t rbytes = (size_t)cd.Gr * pr.N * pr.D * pr.D * 2;
+  size_t off = kStatusBytes;
+  w.rpack_fwd = off; off = align_up(off + rbytes, 256);
+  w.rpack_bwd = off; off = align_up(off + rbytes, 256);
+  w.grads = off; off = align_up(off + ((size_t)cd.Gr * pr.N * pr.D * pr.D + (size_t)cd.Gt * pr.N * pr.D) * 4, 256);
+  w.dg0 = off;
+  if (pr.cell == CELL_GRU) off = align_up(off + (size_t)pr.B * pr.T * pr.N * pr.D * 2, 256);
+  w.total = off;
+  return w;
+}
+
+// A tile (cluster size, batch tile) is usable when both loop kernels exist for it, the CTA fits the
+// instantiation's thread bound and the shared-memory budget.
+static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
+  const int D = pr.D;
+  if (cs < 1 || cs > 8 || D % cs) return false;
+  const int U = D / cs;
+  if (U % 16) return false;
+  if (bt != 8 && bt != 16 && bt != 32) return false;
+  const int kt = D / 16, nt = bt / 8, threads = 2 * cd.Gr * U;
+  const LoopKernel f = get_fwd_kernel(pr.cell, kt, nt), b = get_bwd_kernel(pr.cell, kt, nt);
+  if (!f.fn || !b.fn) return false;
+  if (threads > f.max_threads || threads > b.max_threads || threads < 32) return false;
+  if (f.smem_bytes(U, threads) > kMaxDynSmem || b.smem_bytes(U, threads) > kMaxDynSmem) return false;
+  return true;
+}
+
+// Default tile per problem.  Small-batch problems are bound by the per-step latency of the serial chain, so
+// the head is spread over as many SMs as a portable cluster allows; large-batch problems already fill the
+// GPU with (head, batch tile) pairs and take the smallest cluster (no cross-CTA exchange when it is 1).
+static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs, int want_bt, int* cs_out, int* bt_out) {
+  int bt_pref[3];
+  if (pr.B <= 8) { bt_pref[0] = 8; bt_pref[1] = 16; bt_pref[2] = 32; }
+  else { bt_pref[0] = 16; bt_pref[1] = 8; bt_pref[2] = 32; }
+  for (int bi = 0; bi < 3; ++bi) {
+    const int bt = want_bt ? want_bt : bt_pref[bi];
+    const long long pairs = (long long)((pr.B + bt - 1) / bt) * pr.N;
+    const bool fill = pairs >= 128;
+    // power-of-two cluster sizes first, then the others
+    const int order_small[8] = {8, 4, 2, 1, 6, 3, 7, 5};
+    const int order_large[8] = {1, 2, 4, 8, 3, 6, 5, 7};
+    for (int ci = 0; ci < 8; ++ci) {
+      const int cs = want_cs ? want_cs : (fill ? order_large[ci] : order_small[ci]);
+      if (tile_ok(pr, cd, cs, bt)) { *cs_out = cs; *bt_out = bt; return true; }
+      if (want_cs) break;
+    }
+    if (want_bt) break;
+  }
+  return false;
+}
+
+static int validate_problem(const frnn_problem* pr, CellDims* cd) {
+  if (!pr) return FRNN_ERR_NULL;
+  if (!cell_dims(pr->cell, cd)) return FRNN_ERR_CELL;
+  if (pr->dtype_io != FRNN_DTYPE_BF16) return FRNN_ERR_DTYPE;
+  if (pr->dtype_state != FRNN_DTYPE_BF16 && pr->dtype_state != FRNN_DTYPE_F32) return FRNN_ERR_DTYPE;
+  if (pr->B < 1 || pr->T < 1 || pr->N < 1 || pr->D < 1) return FRNN_ERR_SHAPE;
+  if (pr->N > 65535) return FRNN_ERR_SHAPE;
+  if (pr->D % 16) return FRNN_ERR_SHAPE;
+  bool kt_ok = false;
+  for (int i = 0; i < kNumKT; ++i) kt_ok = kt_ok || (kKTs[i] * 16 == pr->D);
+  if (!kt_ok) return FRNN_ERR_SHAPE;
+  return FRNN_OK;
+}
+
+static int fill_plan(const frnn_problem* pr, int cs, int bt, int stages, frnn_plan* out) {
+  CellDims cd;
+  const int rc = validate_problem(pr, &cd);
+  if (rc) return rc;
+  if (!out) return FRNN_ERR_NULL;
+  if (stages != 0 && stages != kStages) return FRNN_ERR_PLAN;
+  int ccs = 0, cbt = 0;
+  if (!choose_tile(*pr, cd, cs, bt, &ccs, &cbt)) return (cs || bt) ? FRNN_ERR_PLAN : FRNN_ERR_SHAPE;
+  if ((long long)((pr->B + cbt - 1) / cbt) > 65535) return FRNN_ERR_SHAPE;
+  frnn_plan pl = {};
+  pl.abi_version = FRNN_ABI_VERSION;
+  pl.prob = *pr;
+  pl.cluster_size = ccs;
+  pl.units_per_cta = pr->D / ccs;
+  pl.batch_tile = cbt;
+  pl.threads = 2 * cd.Gr * pl.units_per_cta;
+  pl.wx_stages = kStages;
+  pl.cache_slots = cd.GC;
+  pl.cache_bytes = (uint64_t)pr->B * pr->T * cd.GC * pr->N * pr->D * 2;
+  const WsLayout w = workspace_layout(*pr, cd);
+  pl.workspace_bytes = w.total;
+  pl.grads_offset = w.grads;
+  pl.grads_count = (uint64_t)cd.Gr * pr->N * pr->D * pr->D + (uint64_t)cd.Gt * pr->N * pr->D;
+  *out = pl;
+  return FRNN_OK;
+}
+
+static int check_plan(const frnn_plan* pl, CellDims* cd) {
+  if (!pl) return FRNN_ERR_NULL;
+  if (pl->abi_version != FRNN_ABI_VERSION) return FRNN_ERR_PLAN;
+  const int rc = validate_problem(&pl->prob, cd);
+  if (rc) return rc;
+  if (!tile_ok(pl->prob, *cd, pl->cluster_size, pl->batch_tile)) return FRNN_ERR_PLAN;
+  if (pl->units_per_cta * pl->cluster_size != pl->prob.D) return FRNN_ERR_PLAN;
+  if (pl->threads != 2 * cd->Gr * pl->units_per_cta) return FRNN_ERR_PLAN;
+  if (pl->workspace_bytes != workspace_layout(pl->prob, *cd).total) return FRNN_ERR_PLAN;
+  return FRNN_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static cudaError_t launch_loop(const LoopKernel& k, const frnn_plan& pl, const LoopParams& lp, cudaStream_t stream) {
+  const size_t smem = k.smem_bytes(pl.units_per_cta, pl.threads);
+  cudaError_t e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)pl.cluster_size, (unsigned)((pl.prob.B + pl.batch_tile - 1) / pl.batch_tile), (unsigned)pl.prob.N);
+  cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)pl.cluster_size;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pl.cluster_size > 1 ? 1 : 0;
+  void* args[1] = {const_cast<LoopParams*>(&lp)};
+  return cudaLaunchKernelExC(&cfg, k.fn, args);
+}
+
+static int sm_count_cached() {
+  static std::mutex mu;
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cached[dev] = v;
+  }
+  return cached[dev];
+}
+
+}  // namespace frnn
+
+using namespace frnn;
+
+extern "C" {
+
+int frnn_abi_version(void) { return FRNN_ABI_VERSION; }
+
+int frnn_query(const frnn_problem* problem, frnn_plan* out) { return fill_plan(problem, 0, 0, 0, out); }
+
+int frnn_query_tile(const frnn_problem* problem, int cluster_size, int batch_tile, int wx_stages, frnn_plan* out) {
+  return fill_plan(problem, cluster_size, batch_tile, wx_stages, out);
+}
+
+int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
+  CellDims cd;
+  int rc = check_plan(plan, &cd);
+  if (rc) return rc;
+  if (!a || !a->Wx || !a->R || !a->b || !a->s0 || !a->states || !a->workspace) return FRNN_ERR_NULL;
+  const frnn_problem& pr = plan->prob;
+  if (pr.training && cd.GC > 0 && !a->cache) return FRNN_ERR_NULL;
+  if (!aligned16(a->Wx) || !aligned16(a->R) || !aligned16(a->b) || !aligned16(a->s0) || !aligned16(a->states) ||
+      !aligned16(a->workspace) || (a->cache && !aligned16(a->cache)))
+    return FRNN_ERR_ALIGN;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const WsLayout w = workspace_layout(pr, cd);
+  unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+
+  cudaError_t e = cudaMemsetAsync(ws, 0, kStatusBytes, stream);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
+  if (e != cudaSuccess) return (int)e;
+
+  LoopParams lp = {};
+  lp.Wx = static_cast<const __nv_bfloat16*>(a->Wx);
+  lp.Rpack = reinterpret_cast<const uint4*>(ws + w.rpack_fwd);
+  lp.bias = static_cast<const __nv_bfloat16*>(a->b);
+  lp.s0 = a->s0;
+  lp.states = a->states;
+  lp.cache = pr.training ? static_cast<__nv_bfloat16*>(a->cache) : nullptr;
+  lp.status = reinterpret_cast<unsigned*>(ws);
+  lp.B = pr.B; lp.T = pr.T; lp.N = pr.N; lp.D = pr.D;
+  lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
+  lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
+  lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip;
+  const LoopKernel k = get_fwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8);
+  e = launch_loop(k, *plan, lp, stream);
+  return (int)e;
+}
+
+int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_) {
+  CellDims cd;
+  int rc = check_plan(plan, &cd);
+  if (rc) return rc;
+  const frnn_problem& pr = plan->prob;
+  if (!pr.training) return FRNN_ERR_TRAINING;
+  if (!a || !a->R || !a->s0 || !a->states || !a->dstates || !a->dWx || !a->ds0 || !a->workspace) return FRNN_ERR_NULL;
+  if (cd.GC > 0 && !a->cache) return FRNN_ERR_NULL;
+  if (!aligned16(a->R) || !aligned16(a->s0) || !aligned16(a->states) || !aligned16(a->dstates) || !aligned16(a->dWx) ||
+      !aligned16(a->ds0) || !aligned16(a->workspace) || (a->cache && !aligned16(a->cache)))
+    return FRNN_ERR_ALIGN;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const WsLayout w = workspace_layout(pr, cd);
+  unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+  float* grads = reinterpret_cast<float*>(ws + w.grads);
+  const size_t nR = (size_t)cd.Gr * pr.N * pr.D * pr.D, nb = (size_t)cd.Gt * pr.N * pr.D;
+
+  cudaError_t e = cudaMemsetAsync(ws, 0, kStatusBytes, stream);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemsetAsync(grads, 0, (nR + nb) * sizeof(float), stream);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_pack_recurrent(a->R, ws + w.rpack_bwd, cd.Gr, pr.N, pr.D, 1, stream);
+  if (e != cudaSuccess) return (int)e;
+
+  LoopParams lp = {};
+  lp.Rpack = reinterpret_cast<const uint4*>(ws + w.rpack_bwd);
+  lp.s0 = a->s0;
+  lp.states = const_cast<void*>(a->states);
+  lp.cache = static_cast<__nv_bfloat16*>(const_cast<void*>(a->cache));
+  lp.dstates = a->dstates;
+  lp.dWx = static_cast<__nv_bfloat16*>(a->dWx);
+  lp.dg0 = reinterpret_cast<__nv_bfloat16*>(ws + w.dg0);
+  lp.ds0 = a->ds0;
+  lp.dbias = grads + nR;
+  lp.status = reinterpret_cast<unsigned*>(ws);
+  lp.B = pr.B; lp.T = pr.T; lp.N = pr.N; lp.D = pr.D;
+  lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
+  lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
+  lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip;
+  const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8);
+  e = launch_loop(k, *plan, lp, stream);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_recurrent_grad(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
+                            a->s0, grads, sm_count_cached(), stream);
+  return (int)e;
+}
+
+int frnn_finalize_grads(const frnn_plan* plan, const void* grads_f32, void* dR, void* db, void* stream_) {
+  CellDims cd;
+  int rc = check_plan(plan, &cd);
+  if (rc) return rc;
+  if (!grads_f32 || !dR || !db) return FRNN_ERR_NULL;
+  const frnn_problem& pr = plan->prob;
+  const size_t nR = (size_t)cd.Gr * pr.N * pr.D * pr.D, nb = (size_t)cd.Gt * pr.N * pr.D;
+  return (int)launch_cast_grads(static_cast<const float*>(grads_f32), dR, db, nR, nb, static_cast<cudaStream_t>(stream_));
+}
+
+int frnn_read_device_status(const void* workspace, void* stream_, frnn_dev_status* out) {
+  if (!workspace || !out) return FRNN_ERR_NULL;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  cudaError_t e = cudaMemcpyAsync(out, workspace, sizeof(frnn_dev_status), cudaMemcpyDeviceToHost, stream);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaStreamSynchronize(stream);
+}
+
+const char* frnn_status_string(int code) {
+  switch (code) {
+    case FRNN_OK: return "ok";
+    case FRNN_ERR_NULL: return "frnn: a required pointer is NULL";
+    case FRNN_ERR_CELL: return "frnn: unknown cell (expected lstm, gru, elman or slstm)";
+    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256})";
+    case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b must be bfloat16; states bfloat16 or float32)";
+    case FRNN_ERR_ALIGN: return "frnn: tensor pointers must be 16-byte aligned";
+    case FRNN_ERR_PLAN: return "frnn: invalid plan or tile for this problem";
+    case FRNN_ERR_TRAINING: return "frnn: backward needs a plan made with training = 1";
+    case FRNN_ERR_DEVICE: return "frnn: no sm_100 device / kernel image";
+    case FRNN_ERR_TOO_LARGE: return "frnn: size beyond the fixed limit of this entry point";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "frnn: unknown status";
+}
+
+}  // extern "C"

@@ -1,0 +1,38 @@
+// Host-side launchers shared by the translation units of libfrnn_b200.so.
+#pragma once
+#include "frnn_common.cuh"
+
+namespace frnn {
+
+// head dims (D = 16*KT) and batch tiles (BT = 8*NT) the time-loop kernels are instantiated for
+#define FRNN_FOREACH_KT(X, ...) X(2, __VA_ARGS__) X(4, __VA_ARGS__) X(6, __VA_ARGS__) X(8, __VA_ARGS__) X(12, __VA_ARGS__) X(16, __VA_ARGS__)
+constexpr int kNumKT = 6;
+constexpr int kKTs[kNumKT] = {2, 4, 6, 8, 12, 16};
+constexpr int kNumNT = 3;
+constexpr int kNTs[kNumNT] = {1, 2, 4};
+
+struct LoopKernel {
+  const void* fn;      // kernel entry
+  int max_threads;     // __launch_bounds__ of the instantiation
+  size_t (*smem_bytes)(int U, int threads);
+};
+
+// defined once per (cell, direction) in frnn_inst_*.cu; returns fn == nullptr when not instantiated
+LoopKernel get_fwd_kernel(int cell, int kt, int nt);
+LoopKernel get_bwd_kernel(int cell, int kt, int nt);
+LoopKernel get_fwd_kernel_lstm(int kt, int nt);
+LoopKernel get_fwd_kernel_gru(int kt, int nt);
+LoopKernel get_fwd_kernel_elman(int kt, int nt);
+LoopKernel get_fwd_kernel_slstm(int kt, int nt);
+LoopKernel get_bwd_kernel_lstm(int kt, int nt);
+LoopKernel get_bwd_kernel_gru(int kt, int nt);
+LoopKernel get_bwd_kernel_elman(int kt, int nt);
+LoopKernel get_bwd_kernel_slstm(int kt, int nt);
+
+cudaError_t launch_pack_recurrent(const void* R, void* out, int Gr, int N, int D, int transpose, cudaStream_t stream);
+cudaError_t launch_recurrent_grad(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,
+                                  const void* dg0, const void* states, const void* s0, float* dR, int sm_count,
+                                  cudaStream_t stream);
+cudaError_t launch_cast_grads(const float* src, void* dR, void* db, size_t nR, size_t nb, cudaStream_t stream);
+
+}  // namespace frnn

@@ -1,0 +1,324 @@
+// Backward time loop (reverse recurrence), one persistent launch for all T steps.
+//
+// Same work split as the forward kernel: a cluster of CS CTAs owns one (head, batch tile); CTA c owns
+// hidden units [c*U, (c+1)*U).  It keeps the TRANSPOSED slice R^T[p in its units][all Gr*D gate rows] in
+// registers as warp-MMA A fragments: warp (g, ug) holds the columns of gate g for 16 of its units.
+// Per step t = T-1 .. 0
+//   phase B  every thread owns fixed (unit pair, batch row) items: total dh = external cotangent +
+//            recurrent part (sum of the Gr partial products left in shared memory by phase A of the
+//            previous iteration, optionally clipped); closed-form cell backward in fp32 gives the gate
+//            deltas; the deltas of the R-connected gates are pushed (bf16) into the delta buffer of EVERY
+//            CTA of the cluster through distributed shared memory; dWx goes to global memory; db and
+//            the carried cotangents (dc, dn, GRU's z*dh) stay in registers;
+//   one cluster barrier;
+//   phase A  dh_{t-1}[p] partials = R^T slice x deltas (BT x Gr*D) on the tensor cores -> shared memory.
+// Cache / state / cotangent values are prefetched kStages steps ahead with cp.async.
+//
+// Replaces FLASHRNNCellFusedBackward (reference flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:129-624),
+// the FLASHRNNPointwiseBackward functions (fused/*_fused_pointwise.cuh; GRU: alternating/gru_pointwise.cu:120-193)
+// and gradientBiasAggregationKernel (flashrnn_fused_backward.cu:626-665).
+#pragma once
+#include "frnn_common.cuh"
+
+namespace frnn {
+
+// Closed-form backward of one cell update, fp32.
+//   dh        total cotangent of h_t (external + recurrent)
+//   dext[k]   external cotangents of the states 1..NEXT-1 (dext[0] unused)
+//   car[s]    in: cotangent carried from step t+1 for state s (s >= 1); out: carried to step t-1.
+//             car[0] out = the direct (non-matrix) part of dh_{t-1} (GRU: z * dh), else 0.
+//   cur[k]/prv[k]  needed states (Cell::need(k)) at t and t-1
+//   dR_[g]    deltas of the R-connected gates (order of R), dW_[g] of the Wx gates, dB_[g] of the bias gates
+template <int CELL>
+__device__ __forceinline__ void cell_backward(float dh, const float* dext, float* car, const float* cache,
+                                              const float* cur, const float* prv, float* dR_, float* dW_,
+                                              float* dB_) {
+  if constexpr (CELL == CELL_LSTM) {  // vanilla_fwbw/bw.py:100-133
+    const float ig = cache[0], fg = cache[1], zv = cache[2], og = cache[3];
+    const float tc = fast_tanh(cur[0]);
+    const float dc = dext[1] + car[1] + dh * og * (1.f - tc * tc);
+    dR_[0] = dc * zv * ig * (1.f - ig);
+    dR_[1] = dc * prv[0] * fg * (1.f - fg);
+    dR_[2] = dc * ig * (1.f - zv * zv);
+    dR_[3] = dh * tc * og * (1.f - og);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) { dW_[g] = dR_[g]; dB_[g] = dR_[g]; }
+    car[0] = 0.f; car[1] = dc * fg;
+  } else if constexpr (CELL == CELL_GRU) {  // alternating/gru_pointwise.cu:120-193
+    const float gr = cache[0], rg = cache[1], zg = cache[2], nv = cache[3];
+    const float dz = dh * (prv[0] - nv) * zg * (1.f - zg);
+    const float dn = dh * (1.f - zg) * (1.f - nv * nv);
+    const float dr = dn * gr * rg * (1.f - rg);
+    const float dg = dn * rg;
+    dR_[0] = dg; dR_[1] = dr; dR_[2] = dz;
+    dW_[0] = dr; dW_[1] = dz; dW_[2] = dn;
+    dB_[0] = dg; dB_[1] = dr; dB_[2] = dz; dB_[3] = dn;
+    car[0] = zg * dh;
+  } else if constexpr (CELL == CELL_ELMAN) {  // fused/elman_fused_pointwise.cuh:62-93
+    const float dg = dh * (1.f - cur[0] * cur[0]);
+    dR_[0] = dg; dW_[0] = dg; dB_[0] = dg;
+    car[0] = 0.f;
+  } else {  // sLSTM, vanilla_fwbw/bw.py:136-189 (stabiliser m treated as a constant)
+    const float ig = cache[0], fg = cache[1], zv = cache[2], og = cache[3], omsf = cache[4];
+    const float cn = cur[0], n2 = cur[1];
+    const float inv_n = __fdividef(1.f, n2);
+    const float dc = dext[1] + car[1] + dh * og * inv_n;
+    const float dn = dext[2] + car[2] - dh * og * cn * inv_n * inv_n;
+    dR_[0] = ig * (zv * dc + dn);
+    dR_[1] = fg * (dc * prv[0] + dn * prv[1]) * omsf;
+    dR_[2] = dc * ig * (1.f - zv * zv);
+    dR_[3] = dh * cn * inv_n * og * (1.f - og);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) { dW_[g] = dR_[g]; dB_[g] = dR_[g]; }
+    car[0] = 0.f; car[1] = fg * dc; car[2] = fg * dn; car[3] = 0.f;
+  }
+}
+
+template <int CELL, int KT, int NT>
+__host__ __device__ constexpr size_t bwd_smem_bytes(int U, int threads) {
+  using C = Cell<CELL>;
+  constexpr int D = KT * 16, BT = NT * 8;
+  constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
+  constexpr int GCA = C::GC > 0 ? C::GC : 1;
+  return (size_t)2 * BT * (C::Gr * D + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 +
+         (size_t)kStages * GCA * IPT * threads * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * threads * 8;
+}
+
+template <int CELL, int KT, int NT>
+__global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __grid_constant__ LoopParams p) {
+  using C = Cell<CELL>;
+  constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, NNEED = C::NNEED, NEXT = C::NEXT;
+  constexpr int D = KT * 16, BT = NT * 8, GS = Gr * D + 8;
+  constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);
+  constexpr int GCA = GC > 0 ? GC : 1;
+  constexpr int NSS = NNEED + NEXT;  // 8-byte slots per item and stage in the state ring
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
+  const int U = p.U, CS = p.CS, T = p.T, N = p.N, B = p.B;
+  const int PS = U + 4;
+  const int n = blockIdx.z, bt0 = blockIdx.y * BT;
+  const uint32_t crank = (CS > 1) ? cluster_ctarank() : 0u;
+  const int unit0 = (int)crank * U;
+  const size_t ND = (size_t)N * D;
+  const int f32 = p.state_f32;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* dgbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                      // [2][BT][GS]
+  float* part = reinterpret_cast<float*>(smem_raw + (size_t)2 * BT * GS * 2);             // [Gr][BT][PS]
+  uint32_t* ringc = reinterpret_cast<uint32_t*>(part + (size_t)Gr * BT * PS);             // [kStages][GCA][IPT][nthr]
+  uint2* rings = reinterpret_cast<uint2*>(ringc + (size_t)kStages * GCA * IPT * nthr);    // [kStages][NSS][IPT][nthr]
+
+  // ---- R^T slice: rows p = 16 units of this CTA, columns = gate g_w's D output units
+  const int nUT = U >> 4;
+  const int g_w = warp / nUT, ug_w = warp - g_w * nUT;
+  uint4 Rreg[KT];
+  {
+    const uint4* src = p.Rpack + ((((size_t)n * Gr + g_w) * (D / 16) + (unit0 / 16 + ug_w)) * KT) * 32 + lane;
+#pragma unroll
+    for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(src + k * 32);
+  }
+
+  // ---- items
+  const int half_u = U >> 1, nitems = half_u * BT;
+  int it_bl[IPT], it_up[IPT];
+  bool it_on[IPT], it_ok[IPT];
+  size_t wx_off[IPT], st_off[IPT], ch_off[IPT], s0_off[IPT];
+  float car[IPT][S][2], cur[IPT][NNEED][2], dbacc[IPT][Gt][2];
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int q = tid + i * nthr;
+    it_on[i] = q < nitems;
+    const int bl = it_on[i] ? q / half_u : 0, up = it_on[i] ? q - bl * half_u : 0;
+    it_bl[i] = bl; it_up[i] = up;
+    const int bg = bt0 + bl, d = unit0 + 2 * up;
+    it_ok[i] = it_on[i] && bg < B;
+    const int bgc = bg < B ? bg : B - 1;
+    wx_off[i] = ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d;
+    st_off[i] = ((size_t)bgc * T) * ND + (size_t)n * D + d;
+    ch_off[i] = ((size_t)bgc * T * GCA) * ND + (size_t)n * D + d;
+    s0_off[i] = ((size_t)bgc) * ND + (size_t)n * D + d;  // + s*B*ND
+#pragma unroll
+    for (int s = 0; s < S; ++s) { car[i][s][0] = 0.f; car[i][s][1] = 0.f; }
+#pragma unroll
+    for (int g = 0; g < Gt; ++g) { dbacc[i][g][0] = 0.f; dbacc[i][g][1] = 0.f; }
+#pragma unroll
+    for (int k = 0; k < NNEED; ++k) {
+      float2 v = make_float2(0.f, 0.f);
+      if (it_ok[i]) v = load_state2(p.states, st_off[i] + ((size_t)C::need(k) * B * T + (T - 1)) * ND, f32);
+      cur[i][k][0] = v.x; cur[i][k][1] = v.y;
+    }
+  }
+  for (int idx = tid; idx < Gr * BT * PS; idx += nthr) part[idx] = 0.f;
+
+  // ---- prefetch ring: everything step t needs except what is carried in registers
+  auto issue = [&](int t, int stage) {
+    if (t >= 0) {
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) {
+        if (!it_ok[i]) continue;
+#pragma unroll
+        for (int k = 0; k < GC; ++k)
+          cp_async4(ringc + ((size_t)(stage * GCA + k) * IPT + i) * nthr + tid,
+                    p.cache + ch_off[i] + ((size_t)t * GC + k) * ND);
+#pragma unroll
+        for (int k = 0; k < NNEED; ++k) {  // state at t-1 (initial state for t == 0)
+          uint2* dst = rings + ((size_t)(stage * NSS + k) * IPT + i) * nthr + tid;
+          const size_t off = (t > 0) ? st_off[i] + ((size_t)C::need(k) * B * T + (t - 1)) * ND
+                                     : s0_off[i] + (size_t)C::need(k) * B * ND;
+          const void* base = (t > 0) ? p.states : p.s0;
+          if (f32) cp_async8(dst, static_cast<const float*>(base) + off);
+          else cp_async4(dst, static_cast<const __nv_bfloat16*>(base) + off);
+        }
+#pragma unroll
+        for (int k = 0; k < NEXT; ++k) {  // external cotangent of state k at t
+          uint2* dst = rings + ((size_t)(stage * NSS + NNEED + k) * IPT + i) * nthr + tid;
+          const size_t off = st_off[i] + ((size_t)k * B * T + t) * ND;
+          if (f32) cp_async8(dst, static_cast<const float*>(p.dstates) + off);
+          else cp_async4(dst, static_cast<const __nv_bfloat16*>(p.dstates) + off);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < IPT; ++i)
+    if (!it_ok[i])
+      for (int s = 0; s < kStages; ++s) {
+#pragma unroll
+        for (int k = 0; k < GCA; ++k) ringc[((size_t)(s * GCA + k) * IPT + i) * nthr + tid] = 0u;
+#pragma unroll
+        for (int k = 0; k < NSS; ++k) rings[((size_t)(s * NSS + k) * IPT + i) * nthr + tid] = make_uint2(0u, 0u);
+      }
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) issue(T - 1 - s, s);
+
+  if (CS > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+
+  const uint32_t dg_u32 = smem_u32(dgbuf);
+  auto ring_state = [&](int stage, int slot, int i) -> float2 {
+    const uint2 w = rings[((size_t)(stage * NSS + slot) * IPT + i) * nthr + tid];
+    if (f32) return make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
+    return unpack_bf16x2(w.x);
+  };
+
+  int stage = 0;
+  for (int t = T - 1; t >= 0; --t) {
+    const int buf = t & 1;
+    cp_async_wait<kStages - 1>();
+    float dwv[IPT][Gw][2], dg0v[IPT][2];
+    // ---------------- phase B: pointwise backward, push the R-gate deltas to every CTA of the cluster
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_on[i]) continue;
+      float rec[2] = {car[i][0][0], car[i][0][1]};
+#pragma unroll
+      for (int g = 0; g < Gr; ++g) {
+        const float2 v = *reinterpret_cast<const float2*>(part + ((size_t)g * BT + it_bl[i]) * PS + 2 * it_up[i]);
+        rec[0] += v.x; rec[1] += v.y;
+      }
+      float prvv[NNEED][2], extv[NEXT][2], chv[GCA][2];
+#pragma unroll
+      for (int k = 0; k < NNEED; ++k) { const float2 v = ring_state(stage, k, i); prvv[k][0] = v.x; prvv[k][1] = v.y; }
+#pragma unroll
+      for (int k = 0; k < NEXT; ++k) { const float2 v = ring_state(stage, NNEED + k, i); extv[k][0] = v.x; extv[k][1] = v.y; }
+#pragma unroll
+      for (int k = 0; k < GC; ++k) {
+        const float2 v = unpack_bf16x2(ringc[((size_t)(stage * GCA + k) * IPT + i) * nthr + tid]);
+        chv[k][0] = v.x; chv[k][1] = v.y;
+      }
+      float dRv[2][Gr];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float r = rec[e];
+        if (p.gclip > 0.f) r = clampf(r, p.gclip);
+        float dext[NEXT], cr[S], cc[GCA], cu[NNEED], pv[NNEED], dW_[Gw], dB_[Gt];
+#pragma unroll
+        for (int k = 0; k < NEXT; ++k) dext[k] = extv[k][e];
+#pragma unroll
+        for (int s = 0; s < S; ++s) cr[s] = car[i][s][e];
+#pragma unroll
+        for (int k = 0; k < GC; ++k) cc[k] = chv[k][e];
+#pragma unroll
+        for (int k = 0; k < NNEED; ++k) { cu[k] = cur[i][k][e]; pv[k] = prvv[k][e]; }
+        cell_backward<CELL>(dext[0] + r, dext, cr, cc, cu, pv, dRv[e], dW_, dB_);
+#pragma unroll
+        for (int s = 0; s < S; ++s) car[i][s][e] = it_ok[i] ? cr[s] : 0.f;
+#pragma unroll
+        for (int g = 0; g < Gw; ++g) dwv[i][g][e] = dW_[g];
+#pragma unroll
+        for (int g = 0; g < Gt; ++g) dbacc[i][g][e] += it_ok[i] ? dB_[g] : 0.f;
+        if (!it_ok[i]) {
+#pragma unroll
+          for (int g = 0; g < Gr; ++g) dRv[e][g] = 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < NNEED; ++k) cur[i][k][e] = pv[k];
+      }
+      dg0v[i][0] = dRv[0][0]; dg0v[i][1] = dRv[1][0];
+#pragma unroll
+      for (int g = 0; g < Gr; ++g) {
+        const uint32_t v = pack_bf16x2(dRv[0][g], dRv[1][g]);
+        const uint32_t local = dg_u32 + (uint32_t)((buf * BT * GS + it_bl[i] * GS + g * D + unit0 + 2 * it_up[i]) * 2);
+        if (CS > 1) {
+          for (int c = 0; c < CS; ++c) st_cluster_u32(map_to_cta(local, (uint32_t)c), v);
+        } else {
+          *reinterpret_cast<uint32_t*>(dgbuf + buf * BT * GS + it_bl[i] * GS + g * D + unit0 + 2 * it_up[i]) = v;
+        }
+      }
+    }
+    if (CS > 1) cluster_arrive();
+    // ---------------- off the critical path: dWx to global memory, next prefetch
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_ok[i]) continue;
+#pragma unroll
+      for (int g = 0; g < Gw; ++g)
+        *reinterpret_cast<uint32_t*>(p.dWx + wx_off[i] + ((size_t)t * Gw + g) * ND) = pack_bf16x2(dwv[i][g][0], dwv[i][g][1]);
+      if (CELL == CELL_GRU)
+        *reinterpret_cast<uint32_t*>(p.dg0 + st_off[i] + (size_t)t * ND) = pack_bf16x2(dg0v[i][0], dg0v[i][1]);
+    }
+    issue(t - kStages, stage);
+    stage = (stage + 1 == kStages) ? 0 : stage + 1;
+    if (CS > 1) cluster_wait(); else __syncthreads();
+    // ---------------- phase A: part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
+    {
+      float acc[NT][4];
+      warp_mma_rows<KT, NT>(Rreg, dgbuf + buf * BT * GS, GS, g_w * D, lane, acc);
+      const int gid = lane >> 2, tig = lane & 3;
+      float* dst = part + (size_t)g_w * BT * PS + ug_w * 16 + gid;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b0 = nt * 8 + 2 * tig;
+        dst[(size_t)b0 * PS] = acc[nt][0];
+        dst[(size_t)(b0 + 1) * PS] = acc[nt][1];
+        dst[(size_t)b0 * PS + 8] = acc[nt][2];
+        dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+  // ---- cotangent of the initial states, bias gradient
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    if (!it_ok[i]) continue;
+    float rec[2] = {car[i][0][0], car[i][0][1]};
+#pragma unroll
+    for (int g = 0; g < Gr; ++g) {
+      const float2 v = *reinterpret_cast<const float2*>(part + ((size_t)g * BT + it_bl[i]) * PS + 2 * it_up[i]);
+      rec[0] += v.x; rec[1] += v.y;
+    }
+    store_state2(p.ds0, s0_off[i], f32, rec[0], rec[1]);
+#pragma unroll
+    for (int s = 1; s < S; ++s) store_state2(p.ds0, s0_off[i] + (size_t)s * B * ND, f32, car[i][s][0], car[i][s][1]);
+    const int d = unit0 + 2 * it_up[i];
+#pragma unroll
+    for (int g = 0; g < Gt; ++g) {
+      atomicAdd(p.dbias + ((size_t)g * N + n) * D + d, dbacc[i][g][0]);
+      atomicAdd(p.dbias + ((size_t)g * N + n) * D + d + 1, dbacc[i][g][1]);
+    }
+  }
+}
+
+}  // namespace frnn

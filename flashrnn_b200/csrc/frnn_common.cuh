@@ -1,0 +1,194 @@
+// Shared device helpers of the sm_100a time-loop kernels: PTX wrappers (warp MMA, ldmatrix, cp.async,
+// cluster barrier / distributed shared memory), fp32 gate math and the per-cell traits.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace frnn {
+
+enum { CELL_LSTM = 0, CELL_GRU = 1, CELL_ELMAN = 2, CELL_SLSTM = 3 };
+
+// Gate / state counts per cell (reference registry flashrnn/flashrnn/flashrnn.py:49-71) plus what this
+// implementation caches for the backward pass and which states the backward has to re-read.
+//   GC    cached values per (b,t,n,d)
+//   NNEED states whose value at t-1 / t the closed-form backward needs (indices given by need(i))
+//   NEXT  leading states whose external cotangent enters the backward (h, c, n; never m)
+template <int CELL> struct Cell;
+template <> struct Cell<CELL_LSTM> {
+  static constexpr int Gr = 4, Gw = 4, Gt = 4, S = 2, GC = 4, NNEED = 1, NEXT = 2;
+  __host__ __device__ static constexpr int need(int) { return 1; }
+};
+template <> struct Cell<CELL_GRU> {
+  static constexpr int Gr = 3, Gw = 3, Gt = 4, S = 1, GC = 4, NNEED = 1, NEXT = 1;
+  __host__ __device__ static constexpr int need(int) { return 0; }
+};
+template <> struct Cell<CELL_ELMAN> {
+  static constexpr int Gr = 1, Gw = 1, Gt = 1, S = 1, GC = 0, NNEED = 1, NEXT = 1;
+  __host__ __device__ static constexpr int need(int) { return 0; }
+};
+template <> struct Cell<CELL_SLSTM> {
+  static constexpr int Gr = 4, Gw = 4, Gt = 4, S = 4, GC = 5, NNEED = 2, NEXT = 3;
+  __host__ __device__ static constexpr int need(int i) { return i == 0 ? 1 : 2; }
+};
+
+// Time steps of inputs kept in flight ahead of the step being computed (cp.async ring depth).
+constexpr int kStages = 4;
+
+// Arguments of both time-loop kernels (forward uses the first block, backward all of it).
+struct LoopParams {
+  const __nv_bfloat16* Wx;   // [B,T,Gw,N,D]
+  const uint4* Rpack;        // recurrent matrix repacked into warp-MMA A fragments
+  const __nv_bfloat16* bias; // [Gt,N,D]
+  const void* s0;            // [S,B,1,N,D]
+  void* states;              // [S,B,T,N,D]  (forward: out, backward: in)
+  __nv_bfloat16* cache;      // [B,T,GC,N,D] (forward: out or null, backward: in)
+  const void* dstates;       // [S,B,T,N,D]
+  __nv_bfloat16* dWx;        // [B,T,Gw,N,D]
+  __nv_bfloat16* dg0;        // [B,T,N,D]   GRU only: delta of the recurrent-only gate
+  void* ds0;                 // [S,B,1,N,D]
+  float* dbias;              // fp32 [Gt,N,D] accumulated with atomics
+  unsigned* status;
+  int B, T, N, D;
+  int U;                     // hidden units owned by one CTA (multiple of 16)
+  int CS;                    // CTAs per cluster = D / U
+  int state_f32;             // states / dstates / s0 / ds0 are fp32 (else bf16)
+  float fclip, gclip;        // <= 0: off
+};
+
+// ------------------------------------------------------------------------------------------------ PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// shared::cluster address of `local_addr` (a shared::cta address of this CTA) inside CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ math
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float fast_tanh(float x) {
+#ifdef FRNN_APPROX_TANH
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+#else
+  return __fdividef(2.f, 1.f + __expf(-2.f * x)) - 1.f;
+#endif
+}
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
+__device__ __forceinline__ float clampf(float x, float v) { return fminf(fmaxf(x, -v), v); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
+  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
+  return __bfloat1622float2(v);
+}
+
+// Loads / stores of a pair of adjacent state values in the run-time state dtype.
+__device__ __forceinline__ float2 load_state2(const void* base, size_t elem_off, int f32) {
+  if (f32) return *reinterpret_cast<const float2*>(static_cast<const float*>(base) + elem_off);
+  return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(base) + elem_off));
+}
+__device__ __forceinline__ void store_state2(void* base, size_t elem_off, int f32, float lo, float hi) {
+  if (f32) *reinterpret_cast<float2*>(static_cast<float*>(base) + elem_off) = make_float2(lo, hi);
+  else *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(base) + elem_off) = pack_bf16x2(lo, hi);
+}
+
+// ------------------------------------------------------------------------------------------------ warp MMA
+// acc[nt][.] (16 rows x 8*NT batch columns, fp32) = Areg (16 x 16*KT, fragments in registers) times the
+// operand tile held in shared memory as `opnd[batch row][k]` (k contiguous, `stride` elements per row),
+// columns kofs .. kofs+16*KT.  Independent accumulator sets keep the dependent-MMA chains short.
+template <int KT, int NT>
+__device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __nv_bfloat16* opnd, int stride, int kofs,
+                                              int lane, float (&out)[NT][4]) {
+  constexpr int NACC = (NT >= 4) ? 1 : (4 / NT);
+  float acc[NACC][NT][4];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[a][nt][c] = 0.f;
+  const int j = lane >> 3, r = lane & 7;
+  if constexpr (NT == 1) {
+    // one ldmatrix.x4 covers two k-steps of the single 8-row batch tile
+    const uint32_t base = smem_u32(opnd + r * stride + kofs + (j >> 1) * 16 + (j & 1) * 8);
+#pragma unroll
+    for (int k = 0; k < KT; k += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(base + k * 32, b0, b1, b2, b3);
+      mma_bf16_16816(acc[k % NACC][0], Areg[k], b0, b1);
+      mma_bf16_16816(acc[(k + 1) % NACC][0], Areg[k + 1], b2, b3);
+    }
+  } else {
+    // one ldmatrix.x4 covers one k-step of two 8-row batch tiles
+    const uint32_t base = smem_u32(opnd + ((j >> 1) * 8 + r) * stride + kofs + (j & 1) * 8);
+#pragma unroll
+    for (int k = 0; k < KT; ++k) {
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(base + (np * 16 * stride + k * 16) * 2, b0, b1, b2, b3);
+        mma_bf16_16816(acc[k % NACC][2 * np], Areg[k], b0, b1);
+        mma_bf16_16816(acc[k % NACC][2 * np + 1], Areg[k], b2, b3);
+      }
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float s = acc[0][nt][c];
+#pragma unroll
+      for (int a = 1; a < NACC; ++a) s += acc[a][nt][c];
+      out[nt][c] = s;
+    }
+}
+
+// Threads per CTA the kernels are compiled for, by k-steps held in registers per warp.
+template <int KT> struct MaxThreads { static constexpr int v = (KT >= 12) ? 384 : 512; };
+
+}  // namespace frnn

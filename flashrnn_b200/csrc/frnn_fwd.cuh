@@ -1,0 +1,257 @@
+// Forward time loop: one persistent launch runs all T steps.
+//
+// Work split.  A cluster of CS CTAs owns one (head, batch tile of BT rows); CTA `c` of the cluster owns the
+// hidden units [c*U, (c+1)*U).  Its slice of the recurrent matrix (Gr*U gate rows x D) lives in registers
+// as warp-MMA A fragments for the whole sequence: warp (g, ug) holds gate g of 16 units.  Per step
+//   phase A  every warp multiplies its 16 x D slice with h_{t-1} (BT x D, bf16, shared memory) on the
+//            tensor cores and drops the fp32 pre-activations into shared memory;
+//   phase B  every thread owns fixed (unit pair, batch row) items: it adds Wx_t (prefetched kStages steps
+//            ahead with cp.async) and the bias, runs the cell in fp32 with the non-h states carried in
+//            registers, and pushes the new h (bf16) into the h_t buffer of EVERY CTA of the cluster
+//            through distributed shared memory; states / activation cache go straight to global memory;
+//   one cluster barrier (or __syncthreads when CS == 1) ends the step.  No relaunch, no grid-wide sync.
+//
+// Replaces FLASHRNNCellFusedForward (reference flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:146-659)
+// and the per-cell FLASHRNNPointwiseForward functions (fused/{lstm,gru,elman,slstm}_fused_pointwise.cuh).
+#pragma once
+#include "frnn_common.cuh"
+
+namespace frnn {
+
+// One cell update in fp32.  pre[g] = (R h)[g];  wx[g], bias[g] as laid out by the reference's gate orders
+// (vanilla/lstm.py:19, vanilla/gru.py:16-20, vanilla/elman.py:16-20, vanilla/slstm.py:16-18).
+// st[]: previous states in, new states out.  cache[]: values kept for the backward pass.
+template <int CELL>
+__device__ __forceinline__ void cell_forward(const float* pre, const float* wx, const float* bias, float* st,
+                                             float* cache) {
+  if constexpr (CELL == CELL_LSTM) {
+    const float ig = fast_sigmoid(pre[0] + wx[0] + bias[0]);
+    const float fg = fast_sigmoid(pre[1] + wx[1] + bias[1]);
+    const float zv = fast_tanh(pre[2] + wx[2] + bias[2]);
+    const float og = fast_sigmoid(pre[3] + wx[3] + bias[3]);
+    const float c = fg * st[1] + ig * zv;
+    st[0] = og * fast_tanh(c);
+    st[1] = c;
+    cache[0] = ig; cache[1] = fg; cache[2] = zv; cache[3] = og;
+  } else if constexpr (CELL == CELL_GRU) {
+    const float gr = pre[0] + bias[0];                       // recurrent-only gate
+    const float rg = fast_sigmoid(wx[0] + pre[1] + bias[1]);
+    const float zg = fast_sigmoid(wx[1] + pre[2] + bias[2]);
+    const float nv = fast_tanh(wx[2] + bias[3] + rg * gr);   // input-only gate n
+    st[0] = zg * st[0] + (1.f - zg) * nv;
+    cache[0] = gr; cache[1] = rg; cache[2] = zg; cache[3] = nv;
+  } else if constexpr (CELL == CELL_ELMAN) {
+    st[0] = fast_tanh(pre[0] + wx[0] + bias[0]);
+  } else {  // sLSTM; "m' = i~ when n == 0" is applied per element (fused/slstm_fused_pointwise.cuh:53-62)
+    const float ir = pre[0] + wx[0] + bias[0];
+    const float fr = pre[1] + wx[1] + bias[1];
+    const float zv = fast_tanh(pre[2] + wx[2] + bias[2]);
+    const float og = fast_sigmoid(pre[3] + wx[3] + bias[3]);
+    const float lfm = log_sigmoid(fr) + st[3];
+    const float mn = (st[2] == 0.f) ? ir : fmaxf(ir, lfm);
+    const float ig = fminf(1.f, __expf(ir - mn));
+    const float fg = fminf(1.f, __expf(lfm - mn));
+    const float c = fg * st[1] + ig * zv;
+    const float n = fmaxf(fg * st[2] + ig, 1.f);
+    st[0] = og * __fdividef(c, n);
+    st[1] = c; st[2] = n; st[3] = mn;
+    cache[0] = ig; cache[1] = fg; cache[2] = zv; cache[3] = og; cache[4] = 1.f - fast_sigmoid(fr);
+  }
+}
+
+// dynamic shared memory of the forward kernel, in bytes
+template <int CELL, int KT, int NT>
+__host__ __device__ constexpr size_t fwd_smem_bytes(int U, int threads) {
+  using C = Cell<CELL>;
+  constexpr int D = KT * 16, BT = NT * 8;
+  constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
+  return (size_t)2 * BT * (D + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
+         (size_t)kStages * C::Gw * IPT * threads * 4;
+}
+
+template <int CELL, int KT, int NT>
+__global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __grid_constant__ LoopParams p) {
+  using C = Cell<CELL>;
+  constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC;
+  constexpr int D = KT * 16, BT = NT * 8, HS = D + 8;
+  constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);  // items (unit pair x batch row) per thread
+  constexpr int GCA = GC > 0 ? GC : 1;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
+  const int U = p.U, CS = p.CS, T = p.T, N = p.N, B = p.B;
+  const int PS = Gr * U + 4;  // row pitch of the pre-activation tile; == 4 (mod 16) keeps the stores conflict-free
+  const int n = blockIdx.z, bt0 = blockIdx.y * BT;
+  const uint32_t crank = (CS > 1) ? cluster_ctarank() : 0u;
+  const int unit0 = (int)crank * U;
+  const size_t ND = (size_t)N * D;
+
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* hbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [2][BT][HS]
+  float* pre = reinterpret_cast<float*>(smem_raw + (size_t)2 * BT * HS * 2);     // [BT][PS]
+  uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);           // [kStages][Gw][IPT][nthr]
+
+  // ---- this warp's slice of R: gate g_w of units [unit0 + 16*ug_w, +16), all D inputs, as A fragments
+  const int nUT = U >> 4;
+  const int g_w = warp / nUT, ug_w = warp - g_w * nUT;
+  uint4 Rreg[KT];
+  {
+    const uint4* src = p.Rpack + ((((size_t)n * Gr + g_w) * (D / 16) + (unit0 / 16 + ug_w)) * KT) * 32 + lane;
+#pragma unroll
+    for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(src + k * 32);
+  }
+
+  // ---- this thread's items
+  const int half_u = U >> 1, nitems = half_u * BT;
+  int it_bl[IPT], it_up[IPT];
+  bool it_on[IPT], it_ok[IPT];
+  size_t wx_off[IPT], st_off[IPT], ch_off[IPT];
+  float bias[IPT][Gt][2], st[IPT][S][2];
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int q = tid + i * nthr;
+    it_on[i] = q < nitems;
+    const int bl = it_on[i] ? q / half_u : 0, up = it_on[i] ? q - bl * half_u : 0;
+    it_bl[i] = bl; it_up[i] = up;
+    const int bg = bt0 + bl, d = unit0 + 2 * up;
+    it_ok[i] = it_on[i] && bg < B;
+    const int bgc = bg < B ? bg : B - 1;
+    wx_off[i] = ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d;         // + (t*Gw + g)*ND
+    st_off[i] = ((size_t)bgc * T) * ND + (size_t)n * D + d;              // + (s*B*T + t)*ND
+    ch_off[i] = ((size_t)bgc * T * GCA) * ND + (size_t)n * D + d;        // + (t*GC + k)*ND
+#pragma unroll
+    for (int g = 0; g < Gt; ++g) {
+      const float2 bv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.bias + ((size_t)g * N + n) * D + d));
+      bias[i][g][0] = bv.x; bias[i][g][1] = bv.y;
+    }
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      float2 v = make_float2(0.f, 0.f);
+      if (it_ok[i]) v = load_state2(p.s0, ((size_t)s * B + bg) * ND + (size_t)n * D + d, p.state_f32);
+      st[i][s][0] = v.x; st[i][s][1] = v.y;
+    }
+  }
+
+  // ---- h_{-1} of the whole head for this batch tile -> hbuf[0]
+  for (int idx = tid; idx < BT * (D / 2); idx += nthr) {
+    const int bl = idx / (D / 2), dp = idx - bl * (D / 2);
+    const int bg = bt0 + bl;
+    float2 v = make_float2(0.f, 0.f);
+    if (bg < B) v = load_state2(p.s0, ((size_t)bg) * ND + (size_t)n * D + 2 * dp, p.state_f32);
+    *reinterpret_cast<uint32_t*>(hbuf + bl * HS + 2 * dp) = pack_bf16x2(v.x, v.y);
+  }
+
+  // ---- Wx prefetch ring: stage s <- step s
+  auto issue_wx = [&](int t, int stage) {
+    if (t < T) {
+#pragma unroll
+      for (int i = 0; i < IPT; ++i) {
+        if (it_ok[i]) {
+#pragma unroll
+          for (int g = 0; g < Gw; ++g)
+            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * nthr + tid,
+                      p.Wx + wx_off[i] + ((size_t)t * Gw + g) * ND);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < IPT; ++i)
+    if (!it_ok[i])
+      for (int s = 0; s < kStages; ++s)
+#pragma unroll
+        for (int g = 0; g < Gw; ++g) ring[((size_t)(s * Gw + g) * IPT + i) * nthr + tid] = 0u;
+#pragma unroll
+  for (int s = 0; s < kStages; ++s) issue_wx(s, s);
+
+  // every CTA of the cluster must be resident (and its hbuf[0] written) before remote stores start
+  if (CS > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
+
+  const uint32_t hbuf_u32 = smem_u32(hbuf);
+
+  for (int t = 0; t < T; ++t) {
+    const int cur = t & 1, nxt = cur ^ 1, stage = t % kStages;
+    // ---------------- phase A: pre[b][g*U + u] = sum_p R[g][u][p] * h_{t-1}[b][p]
+    {
+      float acc[NT][4];
+      warp_mma_rows<KT, NT>(Rreg, hbuf + cur * BT * HS, HS, 0, lane, acc);
+      const int gid = lane >> 2, tig = lane & 3;
+      float* dst = pre + g_w * U + ug_w * 16 + gid;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int b0 = nt * 8 + 2 * tig;
+        dst[(size_t)b0 * PS] = acc[nt][0];
+        dst[(size_t)(b0 + 1) * PS] = acc[nt][1];
+        dst[(size_t)b0 * PS + 8] = acc[nt][2];
+        dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    // ---------------- phase B: cell update of this thread's items, push h_t to every CTA of the cluster
+    cp_async_wait<kStages - 1>();
+    float hnew[IPT][2], cch[IPT][GCA][2];
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_on[i]) continue;
+      float prv[2][Gr], wxv[2][Gw];
+#pragma unroll
+      for (int g = 0; g < Gr; ++g) {
+        const float2 v = *reinterpret_cast<const float2*>(pre + (size_t)it_bl[i] * PS + g * U + 2 * it_up[i]);
+        prv[0][g] = v.x; prv[1][g] = v.y;
+      }
+#pragma unroll
+      for (int g = 0; g < Gw; ++g) {
+        const float2 v = unpack_bf16x2(ring[((size_t)(stage * Gw + g) * IPT + i) * nthr + tid]);
+        wxv[0][g] = v.x; wxv[1][g] = v.y;
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float sv[S], bv[Gt], cv[GCA];
+#pragma unroll
+        for (int s = 0; s < S; ++s) sv[s] = st[i][s][e];
+#pragma unroll
+        for (int g = 0; g < Gt; ++g) bv[g] = bias[i][g][e];
+        cell_forward<CELL>(prv[e], wxv[e], bv, sv, cv);
+        if (p.fclip > 0.f) sv[0] = clampf(sv[0], p.fclip);
+        if (!it_ok[i]) {  // rows beyond B: keep everything zero
+#pragma unroll
+          for (int s = 0; s < S; ++s) sv[s] = 0.f;
+        }
+#pragma unroll
+        for (int s = 0; s < S; ++s) st[i][s][e] = sv[s];
+#pragma unroll
+        for (int k = 0; k < GC; ++k) cch[i][k][e] = cv[k];
+        hnew[i][e] = sv[0];
+      }
+      const uint32_t hv = pack_bf16x2(hnew[i][0], hnew[i][1]);
+      // the recurrence continues from the bf16-rounded h, the value every consumer of `states` sees
+      if (!p.state_f32) { const float2 r = unpack_bf16x2(hv); st[i][0][0] = r.x; st[i][0][1] = r.y; }
+      const uint32_t local = hbuf_u32 + (uint32_t)((nxt * BT * HS + it_bl[i] * HS + unit0 + 2 * it_up[i]) * 2);
+      if (CS > 1) {
+        for (int c = 0; c < CS; ++c) st_cluster_u32(map_to_cta(local, (uint32_t)c), hv);
+      } else {
+        *reinterpret_cast<uint32_t*>(hbuf + nxt * BT * HS + it_bl[i] * HS + unit0 + 2 * it_up[i]) = hv;
+      }
+    }
+    if (CS > 1) cluster_arrive();
+    // ---------------- off the critical path: results to global memory, next Wx prefetch
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_ok[i]) continue;
+#pragma unroll
+      for (int s = 0; s < S; ++s)
+        store_state2(p.states, st_off[i] + ((size_t)s * B * T + t) * ND, p.state_f32, st[i][s][0], st[i][s][1]);
+      if (GC > 0 && p.cache != nullptr) {
+#pragma unroll
+        for (int k = 0; k < GC; ++k)
+          *reinterpret_cast<uint32_t*>(p.cache + ch_off[i] + ((size_t)t * GC + k) * ND) =
+              pack_bf16x2(cch[i][k][0], cch[i][k][1]);
+      }
+    }
+    issue_wx(t + kStages, stage);
+    if (CS > 1) cluster_wait(); else __syncthreads();
+  }
+  cp_async_wait<0>();
+}
+
+}  // namespace frnn

@@ -1,0 +1,5 @@
+// Instantiates the fwd time-loop kernel of the lstm cell for every supported head dim and batch tile.
+#define FRNN_INST_CELL CELL_LSTM
+#define FRNN_INST_BWD 0
+#define FRNN_INST_NAME get_fwd_kernel_lstm
+#include "frnn_inst.cuh"

@@ -1,0 +1,154 @@
+/*
+ * frnn.h -- C ABI of the B200-native FlashRNN recurrent hot path (libfrnn_b200.so).
+ *
+ * Plain C: pointers, sizes and PODs only (no torch / C++ types).  Every entry point states which
+ * interface of the reference it replaces (paths are inside the reference project).
+ *
+ * Conventions
+ *   - All tensor pointers are DEVICE pointers to dense row-major tensors in the reference's
+ *     user-facing layouts (reference flashrnn/flashrnn/flashrnn.py:165-173):
+ *         Wx[B,T,Gw,N,D]  R[Gr,N,D,D] (R[g,n,d_out,d_in])  b[Gt,N,D]
+ *         s0[S,B,1,N,D]   states[S,B,T,N,D]   dstates like states   dWx like Wx   ds0 like s0
+ *   - The library never allocates or frees device memory and never synchronises the host with the
+ *     device (except frnn_read_device_status, which copies one small struct back).  The caller provides
+ *     the activation cache and a workspace whose sizes frnn_query reports.
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, in order.
+ *   - Return value: 0 = OK; negative = host-side validation error (nothing was launched);
+ *     positive = a CUDA runtime error code (cudaError_t) raised by a launch.
+ *   - Re-entrant and thread-safe for distinct workspaces.
+ */
+#ifndef FRNN_H_
+#define FRNN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FRNN_ABI_VERSION 1
+
+/* cells: gate/state counts follow the reference registry flashrnn/flashrnn/flashrnn.py:49-71 */
+enum { FRNN_CELL_LSTM = 0, FRNN_CELL_GRU = 1, FRNN_CELL_ELMAN = 2, FRNN_CELL_SLSTM = 3 };
+enum { FRNN_DTYPE_BF16 = 0, FRNN_DTYPE_F32 = 1 };
+
+/* status codes (negative = validation) */
+enum {
+  FRNN_OK = 0,
+  FRNN_ERR_NULL = -1,          /* a required pointer is NULL */
+  FRNN_ERR_CELL = -2,          /* unknown cell id */
+  FRNN_ERR_SHAPE = -3,         /* B,T,N,D out of range / head_dim not supported */
+  FRNN_ERR_DTYPE = -4,         /* unsupported dtype combination */
+  FRNN_ERR_ALIGN = -5,         /* a pointer is not 16-byte aligned */
+  FRNN_ERR_PLAN = -6,          /* plan does not belong to this problem / ABI version mismatch */
+  FRNN_ERR_TRAINING = -7,      /* backward requested but the forward ran without a cache */
+  FRNN_ERR_DEVICE = -8,        /* device is not sm_100 / kernel image missing */
+  FRNN_ERR_TOO_LARGE = -9      /* size beyond a fixed limit of the entry point */
+};
+
+/* What to compute.  Replaces the shape/dtype part of the reference's FlashRNNConfig
+ * (flashrnn/flashrnn/flashrnn.py:124-207) and the constructor arguments of the pybind class
+ * FlashRNNFuncFused(training, batch_size, hidden_size, num_heads) (flashrnn/flashrnn/fused/flashrnn.cc:55-66). */
+typedef struct frnn_problem {
+  int32_t cell;          /* FRNN_CELL_*                                             */
+  int32_t B, T, N, D;    /* batch, time steps, heads, head dim                     */
+  int32_t dtype_io;      /* dtype of Wx, R, b, dWx, dR, db : FRNN_DTYPE_BF16        */
+  int32_t dtype_state;   /* dtype of s0, states, dstates, ds0 : BF16 or F32         */
+  int32_t training;      /* 1: forward writes the activation cache for backward     */
+  float forward_clip;    /* > 0: clamp the new h to [-v, v]   (forward_clipval)     */
+  float grad_clip;       /* > 0: clamp the recurrent dh to [-v, v] (gradient_recurrent_clipval) */
+} frnn_problem;
+
+/* Launch plan chosen by frnn_query from the measured sm_100a tile table.  Replaces the reference's
+ * compile-time tiling macros solved by flashrnn/autotune/constrint.py and bisected in
+ * flashrnn/flashrnn/cuda_init_parametric.py:92-358.  Treat as opaque; sizes are for the caller. */
+typedef struct frnn_plan {
+  int32_t abi_version;
+  frnn_problem prob;
+  int32_t cluster_size;    /* CTAs that share one (head, batch tile); exchange h through DSMEM */
+  int32_t units_per_cta;   /* hidden units of the head owned by one CTA                      */
+  int32_t batch_tile;      /* batch rows per CTA (8, 16 or 32)                               */
+  int32_t threads;         /* threads per CTA of the time-loop kernels                       */
+  int32_t wx_stages;       /* time steps of Wx prefetched ahead into shared memory           */
+  int32_t cache_slots;     /* activation values cached per (b,t,n,d) in training             */
+  int32_t reserved[6];
+  uint64_t cache_bytes;     /* size of the activation cache [B,T,cache_slots,N,D] (dtype_io)  */
+  uint64_t workspace_bytes; /* size of the scratch workspace                                  */
+  uint64_t grads_offset;    /* byte offset, inside the workspace, of the fp32 gradients dR || db */
+  uint64_t grads_count;     /* number of fp32 values there: Gr*N*D*D + Gt*N*D                 */
+} frnn_plan;
+
+/* Forward arguments.  Replaces FlashRNNFuncFused::forward(training, x, s0, R, b) -> {states, g_r, g_i}
+ * (flashrnn/flashrnn/fused/flashrnn.cc:68-144); unlike the reference the tensors keep the user layouts, so the
+ * permute + .contiguous() copies of flashrnn/flashrnn/flashrnn.py:1049-1057 disappear. */
+typedef struct frnn_fwd_args {
+  const void* Wx;      /* [B,T,Gw,N,D] dtype_io                      */
+  const void* R;       /* [Gr,N,D,D]   dtype_io                      */
+  const void* b;       /* [Gt,N,D]     dtype_io                      */
+  const void* s0;      /* [S,B,1,N,D]  dtype_state                   */
+  void* states;        /* [S,B,T,N,D]  dtype_state (output)          */
+  void* cache;         /* cache_bytes, output; may be NULL when training == 0 */
+  void* workspace;     /* workspace_bytes                            */
+} frnn_fwd_args;
+
+/* Backward arguments.  Replaces FlashRNNFuncFused::backward(R_t, b, s, g_r, g_i, ds_new) ->
+ * {dWx, ds, dR, db} (flashrnn/flashrnn/fused/flashrnn.cc:146-246), including the post-loop cuBLAS dR GEMM and the
+ * bias aggregation kernel (flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:1049-1069, 626-665).
+ * dR || db are produced in fp32 inside the workspace (plan.grads_offset); frnn_finalize_grads casts them. */
+typedef struct frnn_bwd_args {
+  const void* R;        /* [Gr,N,D,D]  dtype_io                                      */
+  const void* s0;       /* [S,B,1,N,D] dtype_state                                   */
+  const void* states;   /* [S,B,T,N,D] dtype_state, as written by frnn_forward       */
+  const void* cache;    /* as written by frnn_forward (training == 1)                */
+  const void* dstates;  /* [S,B,T,N,D] dtype_state: cotangent of `states`            */
+  void* dWx;            /* [B,T,Gw,N,D] dtype_io (output)                            */
+  void* ds0;            /* [S,B,1,N,D] dtype_state (output)                          */
+  void* workspace;      /* workspace_bytes; holds fp32 dR || db on return            */
+} frnn_bwd_args;
+
+/* One word of device-side status per workspace: 0 = clean. */
+typedef struct frnn_dev_status {
+  uint32_t code;   /* 0 ok; 1 = a bounded device-side wait expired */
+  uint32_t where;  /* kernel-specific location (time step)          */
+  uint32_t cta;    /* linear CTA index that reported it            */
+  uint32_t pad;
+} frnn_dev_status;
+
+/* ABI version of the loaded library (compare with FRNN_ABI_VERSION). */
+int frnn_abi_version(void);
+
+/* Pure host function: validates the problem and fills `out` (tile choice, cache/workspace sizes).
+ * Replaces _FlashRNNCUDAFused.instance(config) (flashrnn/flashrnn/flashrnn.py:386-676): no JIT, no solver. */
+int frnn_query(const frnn_problem* problem, frnn_plan* out);
+
+/* Same as frnn_query but with the tile forced by the caller (used to measure the tile table);
+ * any of the three may be 0 = "use the table's value".  Invalid combinations return FRNN_ERR_PLAN. */
+int frnn_query_tile(const frnn_problem* problem, int cluster_size, int batch_tile, int wx_stages, frnn_plan* out);
+
+/* Whole-sequence forward: one persistent launch (plus a small weight-repack launch).
+ * Replaces ForwardPass::Run (flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:772-975). */
+int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* args, void* stream);
+
+/* Whole-sequence backward: reverse time loop + dR + db.  Replaces BackwardPass::Run
+ * (flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:768-1086), without its host synchronisation. */
+int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* args, void* stream);
+
+/* Casts the fp32 gradients held in the workspace to dtype_io: dR[Gr,N,D,D], db[Gt,N,D].
+ * `grads_f32` is workspace + plan->grads_offset (or a buffer of the same layout, e.g. after an all-reduce).
+ * Replaces the reference's "accumulate in the parameter dtype" outputs (fused/flashrnn.cc:187-215). */
+int frnn_finalize_grads(const frnn_plan* plan, const void* grads_f32, void* dR, void* db, void* stream);
+
+/* Copies the device status word of a workspace to the host (synchronises `stream` first).
+ * Replaces the int return + fprintf(stderr) error reporting of the reference's Run() functions
+ * (flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:935-969). */
+int frnn_read_device_status(const void* workspace, void* stream, frnn_dev_status* out);
+
+/* Human-readable text of a return code of this library (negative codes) or of CUDA (positive codes).
+ * Replaces the TORCH_CHECK message strings of flashrnn/flashrnn/fused/flashrnn.cc:140-142, 238-240. */
+const char* frnn_status_string(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRNN_H_ */

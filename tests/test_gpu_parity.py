@@ -1,0 +1,130 @@
+"""GPU: the CUDA path (through the public API -> C ABI) against the fp64 oracle on identical seeded,
+bf16-rounded inputs.  Shapes follow the reference's test grids (tests/test_lstm.py:9-46: small B, T in
+{1,3}, several heads, plus a longer sequence) reduced to what the oracle finishes in seconds."""
+import numpy as np
+import pytest
+import torch
+
+from tests.util import assert_parity, make_inputs, run_native, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+CELLS = ["lstm", "gru", "elman", "slstm"]
+# (B, T, N, D)
+SHAPES = [(2, 1, 1, 32), (2, 3, 2, 32), (8, 3, 4, 64), (16, 5, 2, 128), (3, 7, 2, 96), (5, 4, 1, 192), (16, 6, 2, 256),
+          (64, 3, 2, 64), (19, 33, 3, 64)]
+
+
+@pytest.mark.parametrize("function", CELLS)
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "B%dT%dN%dD%d" % s)
+def test_parity_default_tile(cuda_device, function, shape):
+    B, T, N, D = shape
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=B * 131 + T * 17 + D)
+    got = run_native(function, Wx, R, b, s0)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=f"{function}{shape}")
+
+
+@pytest.mark.parametrize("function", CELLS)
+@pytest.mark.parametrize("cs,bt", [(1, 8), (2, 16), (4, 8), (8, 16), (1, 32), (2, 32)])
+def test_parity_every_cluster_size(cuda_device, function, cs, bt):
+    """Same answer whatever tile the plan uses (cluster exchange through DSMEM vs single CTA)."""
+    B, T, N, D = 20, 12, 2, 128
+    if function in ("lstm", "slstm") and cs == 1:
+        pytest.skip("one CTA cannot hold 4 gates x 128 units")
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=7, random_init=True)
+    got = run_native(function, Wx, R, b, s0, cluster_size=cs, batch_tile=bt)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=f"{function} cs{cs} bt{bt}")
+
+
+@pytest.mark.parametrize("function", CELLS)
+def test_parity_random_cotangent_and_initial_state(cuda_device, function):
+    """Random cotangent on the states (h only for sLSTM, as the reference's tests do) + random initial states."""
+    B, T, N, D = 6, 9, 2, 64
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=11, random_init=True)
+    S = s0.shape[0]
+    g = torch.Generator().manual_seed(3)
+    cot = torch.randn(S, B, T, N, D, generator=g, dtype=torch.float64)
+    if function == "slstm":
+        cot[1:] = 0
+    got = run_native(function, Wx, R, b, s0, cot=cot)
+    ref = run_oracle(function, Wx, R, b, s0, cot=cot)
+    assert_parity(function, got, ref, tag=function)
+
+
+@pytest.mark.parametrize("function", ["lstm", "slstm", "gru"])
+def test_parity_fp32_states(cuda_device, function):
+    """bf16 Wx/R/b with float32 states (the sLSTM benchmark configuration's dtype mix)."""
+    B, T, N, D = 8, 40, 2, 192 if function == "slstm" else 64
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=13, random_init=(function != "slstm"), state_f32=True)
+    got = run_native(function, Wx, R, b, s0, state_f32=True)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=function)
+
+
+@pytest.mark.parametrize("function", CELLS)
+def test_long_sequence_drift(cuda_device, function):
+    """Error stays inside the tolerance over a long sequence (the recurrence runs in fp32 on chip)."""
+    B, T, N, D = 4, 512, 1, 64
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=21)
+    got = run_native(function, Wx, R, b, s0)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=function)
+
+
+def test_deterministic_forward(cuda_device):
+    """Two runs give bit-identical states (no race in the h exchange)."""
+    from flashrnn_b200 import flashrnn
+
+    Wx, R, b, s0 = make_inputs("lstm", 16, 64, 4, 256, seed=1)
+    a = [t.to("cuda", torch.bfloat16) for t in (Wx, R, b, s0)]
+    with torch.no_grad():
+        s1, _ = flashrnn(a[0], a[1], a[2], a[3], function="lstm")
+        s2, _ = flashrnn(a[0], a[1], a[2], a[3], function="lstm")
+    assert torch.equal(s1, s2)
+
+
+def test_inference_matches_training_forward(cuda_device):
+    from flashrnn_b200 import flashrnn
+
+    Wx, R, b, s0 = make_inputs("gru", 8, 16, 2, 64, seed=4)
+    a = [t.to("cuda", torch.bfloat16) for t in (Wx, R, b, s0)]
+    with torch.no_grad():
+        s_inf, last_inf = flashrnn(*a[:3], a[3], function="gru")
+    a[0].requires_grad_(True)
+    s_tr, _ = flashrnn(*a[:3], a[3], function="gru")
+    assert torch.equal(s_inf, s_tr.detach())
+    assert torch.equal(last_inf, s_inf[:, :, -1:])
+
+
+def test_chunked_sequence_equals_whole(cuda_device):
+    """Feeding `last` back as `states` continues the sequence (the reference's only long-T mechanism)."""
+    from flashrnn_b200 import flashrnn
+
+    Wx, R, b, s0 = make_inputs("lstm", 4, 32, 2, 64, seed=9)
+    Wx_d, R_d, b_d = (t.to("cuda", torch.bfloat16) for t in (Wx, R, b))
+    s_d = s0.to("cuda", torch.float32)
+    with torch.no_grad():
+        whole, _ = flashrnn(Wx_d, R_d, b_d, s_d, function="lstm")
+        first, last = flashrnn(Wx_d[:, :16], R_d, b_d, s_d, function="lstm")
+        second, _ = flashrnn(Wx_d[:, 16:].contiguous(), R_d, b_d, last, function="lstm")
+    assert torch.allclose(torch.cat([first, second], dim=2), whole, atol=2e-2)
+
+
+def test_error_paths(cuda_device):
+    from flashrnn_b200 import flashrnn
+
+    Wx = torch.zeros(2, 3, 4, 1, 32, device="cuda", dtype=torch.bfloat16)
+    R = torch.zeros(4, 1, 32, 32, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(4, 1, 32, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        flashrnn(Wx, R, b, function="lstm", backend="triton_fused")
+    with pytest.raises(ValueError):
+        flashrnn(Wx, R, b, function="lstm", backend="nope")
+    with pytest.raises(AssertionError):
+        flashrnn(Wx, R, b, function="mgu")
+    with pytest.raises(ValueError):
+        flashrnn(Wx, R[:3], b, function="lstm")
+    out, last = flashrnn(Wx[:, :0], R, b, function="lstm")
+    assert out.shape == (2, 2, 0, 1, 32) and last.shape == (2, 2, 1, 1, 32)

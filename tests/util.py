@@ -1,0 +1,101 @@
+"""Shared helpers of the parity tests: seeded inputs in the distributions the benchmark configs name,
+bf16 rounding policy and the tolerance rules.
+
+Tolerances (bf16 kernels vs the fp64 oracle run on the SAME bf16-rounded inputs):
+  * h (= states[0], bounded by 1):            max-abs <= 2e-2
+  * other states (c, n, m; unbounded):        max-abs <= 2e-2 * max(1, max|state|)
+  * gradients dWx, dR, db, ds0:               rel-L2  <= 1e-2
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from oracle import cell_dims, oracle_fwbw
+
+H_MAX_ABS = 2e-2
+GRAD_REL_L2 = 1e-2
+
+
+def bf16_round(x: torch.Tensor) -> torch.Tensor:
+    return x.to(torch.bfloat16).to(torch.float64)
+
+
+def make_inputs(function, B, T, N, D, seed=0, random_init=False, bias_scale=0.1, state_f32=False):
+    """fp64 tensors already rounded to bf16 values (states rounded to bf16 unless ``state_f32``)."""
+    Gr, Gw, Gt, S = cell_dims(function)
+    g = torch.Generator().manual_seed(seed)
+    Wx = bf16_round(torch.randn(B, T, Gw, N, D, generator=g, dtype=torch.float64))
+    R = bf16_round(torch.randn(Gr, N, D, D, generator=g, dtype=torch.float64) / D ** 0.5)
+    b = bias_scale * torch.randn(Gt, N, D, generator=g, dtype=torch.float64)
+    if function == "slstm":
+        b[1] = 3.0 + 3.0 * torch.rand(N, D, generator=g, dtype=torch.float64)
+    b = bf16_round(b)
+    s0 = torch.zeros(S, B, 1, N, D, dtype=torch.float64)
+    if random_init:
+        s0 = 0.1 * torch.randn(S, B, 1, N, D, generator=g, dtype=torch.float64)
+        if function == "slstm":
+            s0[2] = s0[2].abs() + 1.0
+        s0 = s0.to(torch.float32).to(torch.float64) if state_f32 else bf16_round(s0)
+    return Wx, R, b, s0
+
+
+def rel_l2(a, ref) -> float:
+    a = np.asarray(a, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    den = np.linalg.norm(ref.ravel())
+    return float(np.linalg.norm((a - ref).ravel()) / (den if den > 0 else 1.0))
+
+
+def max_abs(a, ref) -> float:
+    return float(np.max(np.abs(np.asarray(a, dtype=np.float64) - np.asarray(ref, dtype=np.float64)))) if np.size(ref) else 0.0
+
+
+def run_native(function, Wx, R, b, s0, cot=None, state_f32=False, device="cuda", **cfg_kw):
+    """Runs the CUDA path through the public API; returns numpy float64 dict like oracle_fwbw."""
+    from flashrnn_b200 import FlashRNNConfig, flashrnn
+
+    sdt = torch.float32 if state_f32 else torch.bfloat16
+    Wx_d = Wx.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    R_d = R.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    b_d = b.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    s_d = s0.to(device=device, dtype=sdt).requires_grad_(True)
+    B, T, _, N, D = Wx.shape
+    cfg = FlashRNNConfig(function=function, head_dim=D, num_heads=N, batch_size=B, dtype="bfloat16",
+                         dtype_s="float32" if state_f32 else "bfloat16", **cfg_kw)
+    states, last = flashrnn(Wx_d, R_d, b_d, s_d, function=function, config=cfg)
+    if cot is None:
+        loss = states[0].float().sum()
+    else:
+        loss = (states.float() * cot.to(device=device, dtype=torch.float32)).sum()
+    loss.backward()
+    torch.cuda.synchronize()
+    f = lambda t: t.detach().to(torch.float64).cpu().numpy()
+    return dict(states=f(states), last=f(last), dWx=f(Wx_d.grad), dR=f(R_d.grad), db=f(b_d.grad), ds0=f(s_d.grad))
+
+
+def run_oracle(function, Wx, R, b, s0, cot=None, clip=0.0):
+    return oracle_fwbw(function, Wx.numpy(), R.numpy(), b.numpy(), s0.numpy(),
+                       dstates=None if cot is None else cot.numpy(), dtype=np.float64, clip=clip,
+                       slstm_global_rule=False)
+
+
+def assert_parity(function, got, ref, check_ds0=True, tag=""):
+    S = ref["states"].shape[0]
+    errs = {}
+    errs["h"] = max_abs(got["states"][0], ref["states"][0])
+    assert errs["h"] <= H_MAX_ABS, f"{tag} h max-abs {errs['h']:.3e} > {H_MAX_ABS}"
+    for s in range(1, S):
+        scale = max(1.0, float(np.abs(ref["states"][s]).max()))
+        e = max_abs(got["states"][s], ref["states"][s])
+        errs[f"s{s}"] = e
+        assert e <= H_MAX_ABS * scale, f"{tag} state {s} max-abs {e:.3e} > {H_MAX_ABS * scale:.3e}"
+    for k in ("dWx", "dR", "db"):
+        errs[k] = rel_l2(got[k], ref[k])
+        assert errs[k] <= GRAD_REL_L2, f"{tag} {k} rel-L2 {errs[k]:.3e} > {GRAD_REL_L2}"
+    if check_ds0:
+        n_chk = 3 if function == "slstm" else S  # the stabiliser m has no closed-form cotangent
+        e = rel_l2(got["ds0"][:n_chk], ref["ds0"][:n_chk])
+        errs["ds0"] = e
+        assert e <= GRAD_REL_L2, f"{tag} ds0 rel-L2 {e:.3e} > {GRAD_REL_L2}"
+    return errs
