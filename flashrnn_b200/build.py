@@ -52,9 +52,19 @@ def _compile(src: Path, headers: list[Path], force: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, jobs: int | None = None) -> Path:
-    """Compile every .cu under csrc/ for sm_100a and link the shared library next to the package."""
-    OBJ.mkdir(exist_ok=True)
+def build(force: bool = False, jobs: int | None = None, extra_flags: tuple[str, ...] = (), lib: Path | None = None,
+          obj_dir: Path | None = None) -> Path:
+    """Compile every .cu under csrc/ for sm_100a and link the shared library next to the package.
+    ``extra_flags`` / ``lib`` / ``obj_dir`` build a variant (e.g. with development macros) somewhere else."""
+    global OBJ, LIB, NVCC_FLAGS
+    if extra_flags or lib or obj_dir:
+        saved = (OBJ, LIB, NVCC_FLAGS)
+        OBJ, LIB, NVCC_FLAGS = Path(obj_dir or OBJ), Path(lib or LIB), [*NVCC_FLAGS, *extra_flags]
+        try:
+            return build(force, jobs)
+        finally:
+            OBJ, LIB, NVCC_FLAGS = saved
+    OBJ.mkdir(exist_ok=True, parents=True)
     headers = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "frnn.h"]
     srcs = _sources()
     jobs = jobs or min(len(srcs), os.cpu_count() or 4)

@@ -63,7 +63,7 @@ static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) 
   const int D = pr.D;
   if (cs < 1 || cs > 8 || D % cs) return false;
   const int U = D / cs;
-  if (U % 16) return false;
+  if (U % 16 || ((U / 16) & (U / 16 - 1))) return false;  // 16 * power of two
   if (bt != 8 && bt != 16 && bt != 32) return false;
   const int kt = D / 16, nt = bt / 8, threads = 2 * cd.Gr * U;
   const LoopKernel f = get_fwd_kernel(pr.cell, kt, nt), b = get_bwd_kernel(pr.cell, kt, nt);
@@ -77,9 +77,8 @@ static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) 
 // the head is spread over as many SMs as a portable cluster allows; large-batch problems already fill the
 // GPU with (head, batch tile) pairs and take the smallest cluster (no cross-CTA exchange when it is 1).
 static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs, int want_bt, int* cs_out, int* bt_out) {
-  int bt_pref[3];
-  if (pr.B <= 8) { bt_pref[0] = 8; bt_pref[1] = 16; bt_pref[2] = 32; }
-  else { bt_pref[0] = 16; bt_pref[1] = 8; bt_pref[2] = 32; }
+  // measured on B200: 8-row batch tiles win for every benchmark configuration (more CTAs, shorter steps)
+  const int bt_pref[3] = {8, 16, 32};
   for (int bi = 0; bi < 3; ++bi) {
     const int bt = want_bt ? want_bt : bt_pref[bi];
     const long long pairs = (long long)((pr.B + bt - 1) / bt) * pr.N;
@@ -129,7 +128,9 @@ static int fill_plan(const frnn_problem* pr, int cs, int bt, int stages, frnn_pl
   pl.threads = 2 * cd.Gr * pl.units_per_cta;
   pl.wx_stages = kStages;
   pl.cache_slots = cd.GC;
-  pl.cache_bytes = (uint64_t)pr->B * pr->T * cd.GC * pr->N * pr->D * 2;
+  // one bf16 pair per (item, slot, step) in the time loops' own order; batch rows padded to whole tiles
+  const uint64_t rows = (uint64_t)((pr->B + cbt - 1) / cbt) * cbt;
+  pl.cache_bytes = rows * pr->T * cd.GC * pr->N * pr->D * 2;
   const WsLayout w = workspace_layout(*pr, cd);
   pl.workspace_bytes = w.total;
   pl.grads_offset = w.grads;
@@ -237,6 +238,10 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
 }
 
 int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_) {
+  return frnn_backward_parts(plan, a, stream_, FRNN_PART_LOOP | FRNN_PART_DR);
+}
+
+int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_, int parts) {
   CellDims cd;
   int rc = check_plan(plan, &cd);
   if (rc) return rc;
@@ -253,12 +258,15 @@ int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_) 
   float* grads = reinterpret_cast<float*>(ws + w.grads);
   const size_t nR = (size_t)cd.Gr * pr.N * pr.D * pr.D, nb = (size_t)cd.Gt * pr.N * pr.D;
 
-  cudaError_t e = cudaMemsetAsync(ws, 0, kStatusBytes, stream);
-  if (e != cudaSuccess) return (int)e;
-  e = cudaMemsetAsync(grads, 0, (nR + nb) * sizeof(float), stream);
-  if (e != cudaSuccess) return (int)e;
-  e = launch_pack_recurrent(a->R, ws + w.rpack_bwd, cd.Gr, pr.N, pr.D, 1, stream);
-  if (e != cudaSuccess) return (int)e;
+  cudaError_t e = cudaSuccess;
+  if (parts & FRNN_PART_LOOP) {
+    e = cudaMemsetAsync(ws, 0, kStatusBytes, stream);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaMemsetAsync(grads, 0, (nR + nb) * sizeof(float), stream);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pack_recurrent(a->R, ws + w.rpack_bwd, cd.Gr, pr.N, pr.D, 1, stream);
+    if (e != cudaSuccess) return (int)e;
+  }
 
   LoopParams lp = {};
   lp.Rpack = reinterpret_cast<const uint4*>(ws + w.rpack_bwd);
@@ -275,10 +283,13 @@ int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_) 
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip;
-  const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8);
-  e = launch_loop(k, *plan, lp, stream);
-  if (e != cudaSuccess) return (int)e;
-  e = launch_recurrent_grad(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
+  if (parts & FRNN_PART_LOOP) {
+    const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8);
+    e = launch_loop(k, *plan, lp, stream);
+    if (e != cudaSuccess) return (int)e;
+  }
+  if (parts & FRNN_PART_DR)
+    e = launch_recurrent_grad(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
                             a->s0, grads, sm_count_cached(), stream);
   return (int)e;
 }

@@ -7,10 +7,12 @@
 //   phase B  every thread owns fixed (unit pair, batch row) items: total dh = external cotangent +
 //            recurrent part (sum of the Gr partial products left in shared memory by phase A of the
 //            previous iteration, optionally clipped); closed-form cell backward in fp32 gives the gate
-//            deltas; the deltas of the R-connected gates are pushed (bf16) into the delta buffer of EVERY
-//            CTA of the cluster through distributed shared memory; dWx goes to global memory; db and
-//            the carried cotangents (dc, dn, GRU's z*dh) stay in registers;
-//   one cluster barrier;
+//            deltas; the deltas of the R-connected gates go (bf16) into this CTA's slice of the delta
+//            buffer; dWx goes to global memory; db and the carried cotangents (dc, dn, GRU's z*dh) stay
+//            in registers;
+//   push     one thread per peer CTA starts a bulk async copy of the slice into the peer's delta buffer,
+//            completing on the peer's mbarrier (no cluster barrier, no fence);
+//   wait     for the slices of the other CTAs (bounded mbarrier wait);
 //   phase A  dh_{t-1}[p] partials = R^T slice x deltas (BT x Gr*D) on the tensor cores -> shared memory.
 // Cache / state / cotangent values are prefetched kStages steps ahead with cp.async.
 //
@@ -80,21 +82,25 @@ __host__ __device__ constexpr size_t bwd_smem_bytes(int U, int threads) {
   constexpr int D = KT * 16, BT = NT * 8;
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
   constexpr int GCA = C::GC > 0 ? C::GC : 1;
-  return (size_t)2 * BT * (C::Gr * D + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 +
-         (size_t)kStages * GCA * IPT * threads * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * threads * 8;
+  const int CS = D / U;
+  return (size_t)2 * CS * BT * (C::Gr * U + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 +
+         (size_t)kStages * GCA * IPT * threads * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * threads * 8 + 16;
 }
 
 template <int CELL, int KT, int NT>
 __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, NNEED = C::NNEED, NEXT = C::NEXT;
-  constexpr int D = KT * 16, BT = NT * 8, GS = Gr * D + 8;
+  constexpr int D = KT * 16, BT = NT * 8;
   constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);
   constexpr int GCA = GC > 0 ? GC : 1;
   constexpr int NSS = NNEED + NEXT;  // 8-byte slots per item and stage in the state ring
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
   const int U = p.U, CS = p.CS, T = p.T, N = p.N, B = p.B;
+  const int GS = Gr * U + 8;        // row pitch (elements) inside a delta slice: [b][g*U + u]
+  const int SL = BT * GS;           // elements per slice
+  const int ushift = 31 - __clz(U >> 4);
   const int PS = U + 4;
   const int n = blockIdx.z, bt0 = blockIdx.y * BT;
   const uint32_t crank = (CS > 1) ? cluster_ctarank() : 0u;
@@ -103,10 +109,11 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   const int f32 = p.state_f32;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* dgbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                      // [2][BT][GS]
-  float* part = reinterpret_cast<float*>(smem_raw + (size_t)2 * BT * GS * 2);             // [Gr][BT][PS]
+  __nv_bfloat16* dgbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                      // [2][CS][BT][GS]
+  float* part = reinterpret_cast<float*>(smem_raw + (size_t)2 * CS * SL * 2);             // [Gr][BT][PS]
   uint32_t* ringc = reinterpret_cast<uint32_t*>(part + (size_t)Gr * BT * PS);             // [kStages][GCA][IPT][nthr]
   uint2* rings = reinterpret_cast<uint2*>(ringc + (size_t)kStages * GCA * IPT * nthr);    // [kStages][NSS][IPT][nthr]
+  uint64_t* full = reinterpret_cast<uint64_t*>(rings + (size_t)kStages * NSS * IPT * nthr);  // [2]
 
   // ---- R^T slice: rows p = 16 units of this CTA, columns = gate g_w's D output units
   const int nUT = U >> 4;
@@ -120,23 +127,39 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
 
   // ---- items
   const int half_u = U >> 1, nitems = half_u * BT;
-  int it_bl[IPT], it_up[IPT];
+  const size_t cta_lin = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  const size_t st_esz = f32 ? 4 : 2;
+  const size_t st_sstride = (size_t)B * T * ND * st_esz;
+  const size_t ch_step = (size_t)gridDim.x * gridDim.y * gridDim.z * GCA * nitems;
   bool it_on[IPT], it_ok[IPT];
-  size_t wx_off[IPT], st_off[IPT], ch_off[IPT], s0_off[IPT];
+  const float* part_it[IPT];            // &part[0][bl][2*up]
+  uint32_t dloc_it[IPT];                // element offset of (bl, gate 0, 2*up) inside this CTA's slice
+  const uint32_t* ch_pf[IPT];           // cache of the next step to prefetch
+  const unsigned char* st_pf[IPT];      // states[0][b][t-1] of the next step to prefetch
+  const unsigned char* ds_pf[IPT];      // dstates[0][b][t]  of the next step to prefetch
+  const unsigned char* s0_it[IPT];      // s0[0][b]
+  __nv_bfloat16* dwx_ptr[IPT];          // dWx[b][t][0][n][d] of the current step
+  __nv_bfloat16* dg0_ptr[IPT];
+  size_t s0_off[IPT];
   float car[IPT][S][2], cur[IPT][NNEED][2], dbacc[IPT][Gt][2];
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int q = tid + i * nthr;
     it_on[i] = q < nitems;
     const int bl = it_on[i] ? q / half_u : 0, up = it_on[i] ? q - bl * half_u : 0;
-    it_bl[i] = bl; it_up[i] = up;
     const int bg = bt0 + bl, d = unit0 + 2 * up;
     it_ok[i] = it_on[i] && bg < B;
     const int bgc = bg < B ? bg : B - 1;
-    wx_off[i] = ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d;
-    st_off[i] = ((size_t)bgc * T) * ND + (size_t)n * D + d;
-    ch_off[i] = ((size_t)bgc * T * GCA) * ND + (size_t)n * D + d;
+    part_it[i] = part + (size_t)bl * PS + 2 * up;
+    dloc_it[i] = (uint32_t)(bl * GS + 2 * up);
+    const size_t st_off = ((size_t)bgc * T) * ND + (size_t)n * D + d;
     s0_off[i] = ((size_t)bgc) * ND + (size_t)n * D + d;  // + s*B*ND
+    ch_pf[i] = reinterpret_cast<const uint32_t*>(p.cache) + cta_lin * GCA * nitems + (it_on[i] ? q : 0) + (size_t)(T - 1) * ch_step;
+    st_pf[i] = static_cast<const unsigned char*>(p.states) + (st_off + (size_t)(T - 2) * ND) * st_esz;  // valid for T >= 2
+    ds_pf[i] = static_cast<const unsigned char*>(p.dstates) + (st_off + (size_t)(T - 1) * ND) * st_esz;
+    s0_it[i] = static_cast<const unsigned char*>(p.s0) + s0_off[i] * st_esz;
+    dwx_ptr[i] = p.dWx + ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d + (size_t)(T - 1) * Gw * ND;
+    dg0_ptr[i] = p.dg0 + st_off + (size_t)(T - 1) * ND;
 #pragma unroll
     for (int s = 0; s < S; ++s) { car[i][s][0] = 0.f; car[i][s][1] = 0.f; }
 #pragma unroll
@@ -144,13 +167,14 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
 #pragma unroll
     for (int k = 0; k < NNEED; ++k) {
       float2 v = make_float2(0.f, 0.f);
-      if (it_ok[i]) v = load_state2(p.states, st_off[i] + ((size_t)C::need(k) * B * T + (T - 1)) * ND, f32);
+      if (it_ok[i]) v = load_state2(p.states, st_off + ((size_t)C::need(k) * B * T + (T - 1)) * ND, f32);
       cur[i][k][0] = v.x; cur[i][k][1] = v.y;
     }
   }
   for (int idx = tid; idx < Gr * BT * PS; idx += nthr) part[idx] = 0.f;
 
-  // ---- prefetch ring: everything step t needs except what is carried in registers
+  // ---- prefetch ring: everything step t needs except what is carried in registers.  Issued in step order
+  // T-1, T-2, ...; `t` is the step being prefetched.
   auto issue = [&](int t, int stage) {
     if (t >= 0) {
 #pragma unroll
@@ -158,24 +182,23 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
         if (!it_ok[i]) continue;
 #pragma unroll
         for (int k = 0; k < GC; ++k)
-          cp_async4(ringc + ((size_t)(stage * GCA + k) * IPT + i) * nthr + tid,
-                    p.cache + ch_off[i] + ((size_t)t * GC + k) * ND);
+          cp_async4(ringc + ((size_t)(stage * GCA + k) * IPT + i) * nthr + tid, ch_pf[i] + (size_t)k * nitems);
+        ch_pf[i] -= ch_step;
 #pragma unroll
         for (int k = 0; k < NNEED; ++k) {  // state at t-1 (initial state for t == 0)
           uint2* dst = rings + ((size_t)(stage * NSS + k) * IPT + i) * nthr + tid;
-          const size_t off = (t > 0) ? st_off[i] + ((size_t)C::need(k) * B * T + (t - 1)) * ND
-                                     : s0_off[i] + (size_t)C::need(k) * B * ND;
-          const void* base = (t > 0) ? p.states : p.s0;
-          if (f32) cp_async8(dst, static_cast<const float*>(base) + off);
-          else cp_async4(dst, static_cast<const __nv_bfloat16*>(base) + off);
+          const unsigned char* src = (t > 0) ? st_pf[i] + (size_t)C::need(k) * st_sstride
+                                             : s0_it[i] + (size_t)C::need(k) * B * ND * st_esz;
+          if (f32) cp_async8(dst, src); else cp_async4(dst, src);
         }
 #pragma unroll
         for (int k = 0; k < NEXT; ++k) {  // external cotangent of state k at t
           uint2* dst = rings + ((size_t)(stage * NSS + NNEED + k) * IPT + i) * nthr + tid;
-          const size_t off = st_off[i] + ((size_t)k * B * T + t) * ND;
-          if (f32) cp_async8(dst, static_cast<const float*>(p.dstates) + off);
-          else cp_async4(dst, static_cast<const __nv_bfloat16*>(p.dstates) + off);
+          const unsigned char* src = ds_pf[i] + (size_t)k * st_sstride;
+          if (f32) cp_async8(dst, src); else cp_async4(dst, src);
         }
+        st_pf[i] -= ND * st_esz;
+        ds_pf[i] -= ND * st_esz;
       }
     }
     cp_async_commit();
@@ -192,9 +215,26 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
 #pragma unroll
   for (int s = 0; s < kStages; ++s) issue(T - 1 - s, s);
 
-  if (CS > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
-
-  const uint32_t dg_u32 = smem_u32(dgbuf);
+  // ---- cluster set-up
+  const uint32_t slice_bytes = (uint32_t)(SL * 2);
+  const uint32_t expect_bytes = (uint32_t)(CS - 1) * slice_bytes;
+  bool poisoned = false;
+  if (CS > 1) {
+    if (tid == 0) {
+      mbar_init(&full[0], 1);
+      mbar_init(&full[1], 1);
+      fence_mbar_init();
+      mbar_arrive_expect_tx(&full[0], expect_bytes);             // deltas of step index 0 (t = T-1)
+      if (T > 1) mbar_arrive_expect_tx(&full[1], expect_bytes);  // step index 1
+    }
+    cluster_arrive();
+    cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  const uint32_t my_slice0 = smem_u32(dgbuf + (size_t)crank * SL);
+  const uint32_t buf_bytes = (uint32_t)(CS * SL * 2);
+  const uint32_t full_u32 = smem_u32(&full[0]);
   auto ring_state = [&](int stage, int slot, int i) -> float2 {
     const uint2 w = rings[((size_t)(stage * NSS + slot) * IPT + i) * nthr + tid];
     if (f32) return make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
@@ -202,18 +242,22 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   };
 
   int stage = 0;
-  for (int t = T - 1; t >= 0; --t) {
-    const int buf = t & 1;
+  FRNN_PROF_DECL;
+  for (int j = 0; j < T; ++j) {  // j-th step of the reverse loop, time index t = T-1-j
+    const int t = T - 1 - j, buf = j & 1;
+    FRNN_PROF_MARK(0);
     cp_async_wait<kStages - 1>();
+    FRNN_PROF_MARK(1);
     float dwv[IPT][Gw][2], dg0v[IPT][2];
-    // ---------------- phase B: pointwise backward, push the R-gate deltas to every CTA of the cluster
+    __nv_bfloat16* ddst = dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
+    // ---------------- phase B: pointwise backward; R-gate deltas into this CTA's slice
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_on[i]) continue;
       float rec[2] = {car[i][0][0], car[i][0][1]};
 #pragma unroll
       for (int g = 0; g < Gr; ++g) {
-        const float2 v = *reinterpret_cast<const float2*>(part + ((size_t)g * BT + it_bl[i]) * PS + 2 * it_up[i]);
+        const float2 v = *reinterpret_cast<const float2*>(part_it[i] + (size_t)g * BT * PS);
         rec[0] += v.x; rec[1] += v.y;
       }
       float prvv[NNEED][2], extv[NEXT][2], chv[GCA][2];
@@ -256,34 +300,44 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
       }
       dg0v[i][0] = dRv[0][0]; dg0v[i][1] = dRv[1][0];
 #pragma unroll
-      for (int g = 0; g < Gr; ++g) {
-        const uint32_t v = pack_bf16x2(dRv[0][g], dRv[1][g]);
-        const uint32_t local = dg_u32 + (uint32_t)((buf * BT * GS + it_bl[i] * GS + g * D + unit0 + 2 * it_up[i]) * 2);
-        if (CS > 1) {
-          for (int c = 0; c < CS; ++c) st_cluster_u32(map_to_cta(local, (uint32_t)c), v);
-        } else {
-          *reinterpret_cast<uint32_t*>(dgbuf + buf * BT * GS + it_bl[i] * GS + g * D + unit0 + 2 * it_up[i]) = v;
-        }
-      }
+      for (int g = 0; g < Gr; ++g)
+        *reinterpret_cast<uint32_t*>(ddst + dloc_it[i] + g * U) = pack_bf16x2(dRv[0][g], dRv[1][g]);
     }
-    if (CS > 1) cluster_arrive();
+    if (CS > 1) fence_proxy_async_smem();
+    FRNN_PROF_MARK(2);
+    __syncthreads();
+    // ---------------- push this CTA's delta slice to every other CTA of the cluster
+    if (CS > 1)  // uniform branch; inside, one elected lane per warp issues a copy
+      push_slice_to_peers(my_slice0 + buf * buf_bytes, slice_bytes, full_u32 + buf * 8, crank, (uint32_t)CS,
+                          (uint32_t)warp, (uint32_t)(nthr >> 5));
     // ---------------- off the critical path: dWx to global memory, next prefetch
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_ok[i]) continue;
 #pragma unroll
       for (int g = 0; g < Gw; ++g)
-        *reinterpret_cast<uint32_t*>(p.dWx + wx_off[i] + ((size_t)t * Gw + g) * ND) = pack_bf16x2(dwv[i][g][0], dwv[i][g][1]);
-      if (CELL == CELL_GRU)
-        *reinterpret_cast<uint32_t*>(p.dg0 + st_off[i] + (size_t)t * ND) = pack_bf16x2(dg0v[i][0], dg0v[i][1]);
+        *reinterpret_cast<uint32_t*>(dwx_ptr[i] + (size_t)g * ND) = pack_bf16x2(dwv[i][g][0], dwv[i][g][1]);
+      dwx_ptr[i] -= (size_t)Gw * ND;
+      if (CELL == CELL_GRU) {
+        *reinterpret_cast<uint32_t*>(dg0_ptr[i]) = pack_bf16x2(dg0v[i][0], dg0v[i][1]);
+        dg0_ptr[i] -= ND;
+      }
     }
     issue(t - kStages, stage);
     stage = (stage + 1 == kStages) ? 0 : stage + 1;
-    if (CS > 1) cluster_wait(); else __syncthreads();
+    FRNN_PROF_MARK(3);
+    if (CS > 1) {
+      if (!poisoned && !mbar_wait_bounded(&full[buf], (j >> 1) & 1)) {
+        poisoned = true;
+        report_timeout(p.status, t);
+      }
+      if (tid == 0 && j + 2 < T) mbar_arrive_expect_tx(&full[buf], expect_bytes);
+    }
+    FRNN_PROF_MARK(4);
     // ---------------- phase A: part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
     {
       float acc[NT][4];
-      warp_mma_rows<KT, NT>(Rreg, dgbuf + buf * BT * GS, GS, g_w * D, lane, acc);
+      warp_mma_rows<KT, NT>(Rreg, dgbuf + (size_t)buf * CS * SL, GS, g_w * U, ushift, SL, lane, acc);
       const int gid = lane >> 2, tig = lane & 3;
       float* dst = part + (size_t)g_w * BT * PS + ug_w * 16 + gid;
 #pragma unroll
@@ -295,9 +349,12 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
         dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
       }
     }
+    FRNN_PROF_MARK(5);
     __syncthreads();
+    FRNN_PROF_MARK(6);
   }
   cp_async_wait<0>();
+  FRNN_PROF_DUMP(p.status);
 
   // ---- cotangent of the initial states, bias gradient
 #pragma unroll
@@ -306,19 +363,20 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
     float rec[2] = {car[i][0][0], car[i][0][1]};
 #pragma unroll
     for (int g = 0; g < Gr; ++g) {
-      const float2 v = *reinterpret_cast<const float2*>(part + ((size_t)g * BT + it_bl[i]) * PS + 2 * it_up[i]);
+      const float2 v = *reinterpret_cast<const float2*>(part_it[i] + (size_t)g * BT * PS);
       rec[0] += v.x; rec[1] += v.y;
     }
     store_state2(p.ds0, s0_off[i], f32, rec[0], rec[1]);
 #pragma unroll
     for (int s = 1; s < S; ++s) store_state2(p.ds0, s0_off[i] + (size_t)s * B * ND, f32, car[i][s][0], car[i][s][1]);
-    const int d = unit0 + 2 * it_up[i];
+    const int d = (int)(s0_off[i] % D);
 #pragma unroll
     for (int g = 0; g < Gt; ++g) {
       atomicAdd(p.dbias + ((size_t)g * N + n) * D + d, dbacc[i][g][0]);
       atomicAdd(p.dbias + ((size_t)g * N + n) * D + d + 1, dbacc[i][g][1]);
     }
   }
+  if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight
 }
 
 }  // namespace frnn

@@ -104,15 +104,93 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v
   asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
+// ---- mbarrier + bulk async copy between the shared memories of a cluster
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Waits for a phase of `bar`, but never longer than ~2 s: on expiry the caller records the failure in
+// the status block and stops waiting for the rest of the kernel (results are then invalid, the kernel ends).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > 2000000000ull) return false;
+  }
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// copies `bytes` (multiple of 16) from this CTA's shared memory to the same offset space of another CTA of the
+// cluster; completion is signalled as transaction bytes on the destination CTA's mbarrier
+__device__ __forceinline__ void bulk_copy_to_cta(uint32_t dst_cluster_addr, uint32_t src_cta_addr, uint32_t bytes,
+                                                 uint32_t mbar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(mbar_cluster_addr) : "memory");
+}
+// true in exactly one lane of a fully converged warp
+__device__ __forceinline__ bool elect_one_sync() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred)::"memory");
+  return pred != 0;
+}
+// Warp-collective: one elected lane of the calling (converged) warp starts the bulk copies of this CTA's slice
+// [src_cta_addr, +bytes) to the same address in every other CTA of the cluster; each copy completes on the
+// destination CTA's mbarrier at `bar_cta_addr`.
+// Called by EVERY warp of the CTA (`warp`, `nwarps`): warp w serves the peers w, w + nwarps, ... so that the
+// copies are issued in parallel.
+__device__ __forceinline__ void push_slice_to_peers(uint32_t src_cta_addr, uint32_t bytes, uint32_t bar_cta_addr,
+                                                    uint32_t my_rank, uint32_t cluster_size, uint32_t warp,
+                                                    uint32_t nwarps) {
+  __syncwarp();
+#pragma unroll 1
+  for (uint32_t c = warp; c < cluster_size; c += nwarps) {
+    if (c == my_rank) continue;
+    const uint32_t dst = map_to_cta(src_cta_addr, c), bar = map_to_cta(bar_cta_addr, c);
+    if (elect_one_sync()) bulk_copy_to_cta(dst, src_cta_addr, bytes, bar);
+  }
+}
+__device__ __forceinline__ void report_timeout(unsigned* status, int where) {
+  if (atomicCAS(status, 0u, 1u) == 0u) {
+    status[1] = (unsigned)where;
+    status[2] = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ math
-__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// Gate nonlinearities.  Default: the hardware tanh (one MUFU op, max error ~5e-4, an order of magnitude
+// below the bf16 rounding of the stored results); sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5.
+// -DFRNN_EXACT_ACT switches to exp-based forms accurate to ~1e-6.
 __device__ __forceinline__ float fast_tanh(float x) {
-#ifdef FRNN_APPROX_TANH
+#ifndef FRNN_EXACT_ACT
   float y;
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 #else
   return __fdividef(2.f, 1.f + __expf(-2.f * x)) - 1.f;
+#endif
+}
+__device__ __forceinline__ float fast_sigmoid(float x) {
+#ifndef FRNN_EXACT_ACT
+  return fmaf(0.5f, fast_tanh(0.5f * x), 0.5f);
+#else
+  return __fdividef(1.f, 1.f + __expf(-x));
 #endif
 }
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
@@ -141,9 +219,13 @@ __device__ __forceinline__ void store_state2(void* base, size_t elem_off, int f3
 // acc[nt][.] (16 rows x 8*NT batch columns, fp32) = Areg (16 x 16*KT, fragments in registers) times the
 // operand tile held in shared memory as `opnd[batch row][k]` (k contiguous, `stride` elements per row),
 // columns kofs .. kofs+16*KT.  Independent accumulator sets keep the dependent-MMA chains short.
+//
+// The operand is stored as one slice per producing CTA: slice c holds, for every batch row, the `1 << ushift`
+// * 16 k-columns that CTA c produces: element (b, k) sits at  (k16 >> ushift) * slice_elems + b * stride +
+// kofs + (k & (16 << ushift) - 1)  where k16 = k / 16.
 template <int KT, int NT>
 __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __nv_bfloat16* opnd, int stride, int kofs,
-                                              int lane, float (&out)[NT][4]) {
+                                              int ushift, int slice_elems, int lane, float (&out)[NT][4]) {
   constexpr int NACC = (NT >= 4) ? 1 : (4 / NT);
   float acc[NACC][NT][4];
 #pragma unroll
@@ -155,23 +237,27 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
   const int j = lane >> 3, r = lane & 7;
   if constexpr (NT == 1) {
     // one ldmatrix.x4 covers two k-steps of the single 8-row batch tile
-    const uint32_t base = smem_u32(opnd + r * stride + kofs + (j >> 1) * 16 + (j & 1) * 8);
+    const uint32_t base = smem_u32(opnd + r * stride + kofs + (j & 1) * 8);
+    const int kmask = (1 << ushift) - 1;
 #pragma unroll
     for (int k = 0; k < KT; k += 2) {
       uint32_t b0, b1, b2, b3;
-      ldmatrix_x4(base + k * 32, b0, b1, b2, b3);
+      const int kk = k + (j >> 1);
+      ldmatrix_x4(base + (uint32_t)(((kk >> ushift) * slice_elems + (kk & kmask) * 16) * 2), b0, b1, b2, b3);
       mma_bf16_16816(acc[k % NACC][0], Areg[k], b0, b1);
       mma_bf16_16816(acc[(k + 1) % NACC][0], Areg[k + 1], b2, b3);
     }
   } else {
     // one ldmatrix.x4 covers one k-step of two 8-row batch tiles
     const uint32_t base = smem_u32(opnd + ((j >> 1) * 8 + r) * stride + kofs + (j & 1) * 8);
+    const int kmask = (1 << ushift) - 1;
 #pragma unroll
     for (int k = 0; k < KT; ++k) {
+      const uint32_t koff = (uint32_t)(((k >> ushift) * slice_elems + (k & kmask) * 16) * 2);
 #pragma unroll
       for (int np = 0; np < NT / 2; ++np) {
         uint32_t b0, b1, b2, b3;
-        ldmatrix_x4(base + (np * 16 * stride + k * 16) * 2, b0, b1, b2, b3);
+        ldmatrix_x4(base + koff + (uint32_t)(np * 16 * stride * 2), b0, b1, b2, b3);
         mma_bf16_16816(acc[k % NACC][2 * np], Areg[k], b0, b1);
         mma_bf16_16816(acc[k % NACC][2 * np + 1], Areg[k], b2, b3);
       }
@@ -187,6 +273,23 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
       out[nt][c] = s;
     }
 }
+
+// Development aid (off in the shipped library): with -DFRNN_PROFILE thread 0 of CTA 0 sums the SM clock
+// between up to 7 marks of the step loop and leaves the 7 sums (u64) at byte 64 of the status block.
+#ifdef FRNN_PROFILE
+#define FRNN_PROF_DECL                                                                         \
+  const bool prof_on = (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0); \
+  long long prof_sum[7] = {0, 0, 0, 0, 0, 0, 0};                                               \
+  long long prof_last = clock64()
+#define FRNN_PROF_MARK(i)                                                                      \
+  do { if (prof_on) { const long long c_ = clock64(); prof_sum[i] += c_ - prof_last; prof_last = c_; } } while (0)
+#define FRNN_PROF_DUMP(status)                                                                 \
+  do { if (prof_on) { for (int i_ = 0; i_ < 7; ++i_) reinterpret_cast<long long*>(status)[8 + i_] = prof_sum[i_]; } } while (0)
+#else
+#define FRNN_PROF_DECL do { } while (0)
+#define FRNN_PROF_MARK(i) do { } while (0)
+#define FRNN_PROF_DUMP(status) do { } while (0)
+#endif
 
 // Threads per CTA the kernels are compiled for, by k-steps held in registers per warp.
 template <int KT> struct MaxThreads { static constexpr int v = (KT >= 12) ? 384 : 512; };

@@ -3,13 +3,16 @@
 // Work split.  A cluster of CS CTAs owns one (head, batch tile of BT rows); CTA `c` of the cluster owns the
 // hidden units [c*U, (c+1)*U).  Its slice of the recurrent matrix (Gr*U gate rows x D) lives in registers
 // as warp-MMA A fragments for the whole sequence: warp (g, ug) holds gate g of 16 units.  Per step
+//   wait     (CS > 1) for the h_{t-1} slices of the other CTAs: an mbarrier counts the bytes their bulk
+//            copies deliver into this CTA's shared memory -- no cluster-wide barrier, no memory fence;
 //   phase A  every warp multiplies its 16 x D slice with h_{t-1} (BT x D, bf16, shared memory) on the
 //            tensor cores and drops the fp32 pre-activations into shared memory;
 //   phase B  every thread owns fixed (unit pair, batch row) items: it adds Wx_t (prefetched kStages steps
 //            ahead with cp.async) and the bias, runs the cell in fp32 with the non-h states carried in
-//            registers, and pushes the new h (bf16) into the h_t buffer of EVERY CTA of the cluster
-//            through distributed shared memory; states / activation cache go straight to global memory;
-//   one cluster barrier (or __syncthreads when CS == 1) ends the step.  No relaunch, no grid-wide sync.
+//            registers and writes the new h (bf16) into this CTA's slice of the h_t buffer;
+//   push     one thread per peer CTA starts a bulk async copy (cp.async.bulk, shared::cta -> shared::cluster)
+//            of the whole slice into the peer's h_t buffer, completing on the peer's mbarrier;
+//   states / activation cache go straight to global memory, off the critical path.
 //
 // Replaces FLASHRNNCellFusedForward (reference flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:146-659)
 // and the per-cell FLASHRNNPointwiseForward functions (fused/{lstm,gru,elman,slstm}_fused_pointwise.cuh).
@@ -65,30 +68,36 @@ __host__ __device__ constexpr size_t fwd_smem_bytes(int U, int threads) {
   using C = Cell<CELL>;
   constexpr int D = KT * 16, BT = NT * 8;
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
-  return (size_t)2 * BT * (D + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
-         (size_t)kStages * C::Gw * IPT * threads * 4;
+  const int CS = D / U;
+  return (size_t)2 * CS * BT * (U + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
+         (size_t)kStages * C::Gw * IPT * threads * 4 + 16;
 }
 
 template <int CELL, int KT, int NT>
 __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC;
-  constexpr int D = KT * 16, BT = NT * 8, HS = D + 8;
+  constexpr int D = KT * 16, BT = NT * 8;
   constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);  // items (unit pair x batch row) per thread
   constexpr int GCA = GC > 0 ? GC : 1;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
   const int U = p.U, CS = p.CS, T = p.T, N = p.N, B = p.B;
-  const int PS = Gr * U + 4;  // row pitch of the pre-activation tile; == 4 (mod 16) keeps the stores conflict-free
+  const int US = U + 8;             // row pitch (elements) inside an h slice: 16 B of padding keeps ldmatrix conflict-free
+  const int SL = BT * US;           // elements per slice
+  const int ushift = 31 - __clz(U >> 4);
+  const int PS = Gr * U + 4;        // row pitch of the pre-activation tile; == 4 (mod 16) keeps the stores conflict-free
   const int n = blockIdx.z, bt0 = blockIdx.y * BT;
   const uint32_t crank = (CS > 1) ? cluster_ctarank() : 0u;
   const int unit0 = (int)crank * U;
   const size_t ND = (size_t)N * D;
+  const int f32 = p.state_f32;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* hbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [2][BT][HS]
-  float* pre = reinterpret_cast<float*>(smem_raw + (size_t)2 * BT * HS * 2);     // [BT][PS]
-  uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);           // [kStages][Gw][IPT][nthr]
+  __nv_bfloat16* hbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                   // [2][CS][BT][US]
+  float* pre = reinterpret_cast<float*>(smem_raw + (size_t)2 * CS * SL * 2);          // [BT][PS]
+  uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);                // [kStages][Gw][IPT][nthr]
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)kStages * Gw * IPT * nthr);  // [2]
 
   // ---- this warp's slice of R: gate g_w of units [unit0 + 16*ug_w, +16), all D inputs, as A fragments
   const int nUT = U >> 4;
@@ -100,24 +109,32 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __
     for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(src + k * 32);
   }
 
-  // ---- this thread's items
+  // ---- this thread's items: everything that does not change over time is computed once
   const int half_u = U >> 1, nitems = half_u * BT;
-  int it_bl[IPT], it_up[IPT];
+  const size_t cta_lin = ((size_t)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
   bool it_on[IPT], it_ok[IPT];
-  size_t wx_off[IPT], st_off[IPT], ch_off[IPT];
+  const float* pre_it[IPT];            // &pre[bl][2*up]
+  uint32_t hloc_it[IPT];               // element offset of (bl, 2*up) inside this CTA's slice
+  const __nv_bfloat16* wx_pf[IPT];     // Wx of the next step to prefetch
+  unsigned char* st_ptr[IPT];          // states[0][b][t][n][d] of the current step (bytes)
+  uint32_t* ch_ptr[IPT];               // activation cache of the current step
   float bias[IPT][Gt][2], st[IPT][S][2];
+  const size_t st_esz = f32 ? 4 : 2;
+  const size_t st_sstride = (size_t)B * T * ND * st_esz;        // bytes between states s and s+1
+  const size_t ch_step = (size_t)gridDim.x * gridDim.y * gridDim.z * GCA * nitems;  // uint32 per time step
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int q = tid + i * nthr;
     it_on[i] = q < nitems;
     const int bl = it_on[i] ? q / half_u : 0, up = it_on[i] ? q - bl * half_u : 0;
-    it_bl[i] = bl; it_up[i] = up;
     const int bg = bt0 + bl, d = unit0 + 2 * up;
     it_ok[i] = it_on[i] && bg < B;
     const int bgc = bg < B ? bg : B - 1;
-    wx_off[i] = ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d;         // + (t*Gw + g)*ND
-    st_off[i] = ((size_t)bgc * T) * ND + (size_t)n * D + d;              // + (s*B*T + t)*ND
-    ch_off[i] = ((size_t)bgc * T * GCA) * ND + (size_t)n * D + d;        // + (t*GC + k)*ND
+    pre_it[i] = pre + (size_t)bl * PS + 2 * up;
+    hloc_it[i] = (uint32_t)(bl * US + 2 * up);
+    wx_pf[i] = p.Wx + ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d;
+    st_ptr[i] = static_cast<unsigned char*>(p.states) + (((size_t)bgc * T) * ND + (size_t)n * D + d) * st_esz;
+    ch_ptr[i] = reinterpret_cast<uint32_t*>(p.cache) + cta_lin * GCA * nitems + (it_on[i] ? q : 0);
 #pragma unroll
     for (int g = 0; g < Gt; ++g) {
       const float2 bv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.bias + ((size_t)g * N + n) * D + d));
@@ -126,30 +143,30 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __
 #pragma unroll
     for (int s = 0; s < S; ++s) {
       float2 v = make_float2(0.f, 0.f);
-      if (it_ok[i]) v = load_state2(p.s0, ((size_t)s * B + bg) * ND + (size_t)n * D + d, p.state_f32);
+      if (it_ok[i]) v = load_state2(p.s0, ((size_t)s * B + bg) * ND + (size_t)n * D + d, f32);
       st[i][s][0] = v.x; st[i][s][1] = v.y;
     }
   }
 
-  // ---- h_{-1} of the whole head for this batch tile -> hbuf[0]
+  // ---- h_{-1} of the whole head for this batch tile -> hbuf[0] (all slices, read straight from global)
   for (int idx = tid; idx < BT * (D / 2); idx += nthr) {
     const int bl = idx / (D / 2), dp = idx - bl * (D / 2);
-    const int bg = bt0 + bl;
+    const int bg = bt0 + bl, k = 2 * dp;
     float2 v = make_float2(0.f, 0.f);
-    if (bg < B) v = load_state2(p.s0, ((size_t)bg) * ND + (size_t)n * D + 2 * dp, p.state_f32);
-    *reinterpret_cast<uint32_t*>(hbuf + bl * HS + 2 * dp) = pack_bf16x2(v.x, v.y);
+    if (bg < B) v = load_state2(p.s0, ((size_t)bg) * ND + (size_t)n * D + k, f32);
+    *reinterpret_cast<uint32_t*>(hbuf + (size_t)(k / U) * SL + bl * US + (k % U)) = pack_bf16x2(v.x, v.y);
   }
 
   // ---- Wx prefetch ring: stage s <- step s
-  auto issue_wx = [&](int t, int stage) {
-    if (t < T) {
+  auto issue_wx = [&](bool live, int stage) {
+    if (live) {
 #pragma unroll
       for (int i = 0; i < IPT; ++i) {
         if (it_ok[i]) {
 #pragma unroll
           for (int g = 0; g < Gw; ++g)
-            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * nthr + tid,
-                      p.Wx + wx_off[i] + ((size_t)t * Gw + g) * ND);
+            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * nthr + tid, wx_pf[i] + (size_t)g * ND);
+          wx_pf[i] += (size_t)Gw * ND;
         }
       }
     }
@@ -162,19 +179,45 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __
 #pragma unroll
         for (int g = 0; g < Gw; ++g) ring[((size_t)(s * Gw + g) * IPT + i) * nthr + tid] = 0u;
 #pragma unroll
-  for (int s = 0; s < kStages; ++s) issue_wx(s, s);
+  for (int s = 0; s < kStages; ++s) issue_wx(s < T, s);
 
-  // every CTA of the cluster must be resident (and its hbuf[0] written) before remote stores start
-  if (CS > 1) { cluster_arrive(); cluster_wait(); } else { __syncthreads(); }
-
-  const uint32_t hbuf_u32 = smem_u32(hbuf);
+  // ---- cluster set-up: mbarriers that count the bytes delivered into hbuf[x]
+  const uint32_t slice_bytes = (uint32_t)(SL * 2);
+  const uint32_t expect_bytes = (uint32_t)(CS - 1) * slice_bytes;
+  bool poisoned = false;
+  if (CS > 1) {
+    if (tid == 0) {
+      mbar_init(&full[0], 1);
+      mbar_init(&full[1], 1);
+      fence_mbar_init();
+      if (T > 1) mbar_arrive_expect_tx(&full[1], expect_bytes);  // h_0, consumed at step 1
+      if (T > 2) mbar_arrive_expect_tx(&full[0], expect_bytes);  // h_1, consumed at step 2
+    }
+    cluster_arrive();
+    cluster_wait();  // every CTA of the cluster is resident, its barriers initialised and hbuf[0] written
+  } else {
+    __syncthreads();
+  }
+  const uint32_t my_slice0 = smem_u32(hbuf + (size_t)crank * SL);   // this CTA's slice in buffer 0
+  const uint32_t buf_bytes = (uint32_t)(CS * SL * 2);               // distance to the same slice in buffer 1
+  const uint32_t full_u32 = smem_u32(&full[0]);
+  FRNN_PROF_DECL;
 
   for (int t = 0; t < T; ++t) {
     const int cur = t & 1, nxt = cur ^ 1, stage = t % kStages;
-    // ---------------- phase A: pre[b][g*U + u] = sum_p R[g][u][p] * h_{t-1}[b][p]
+    FRNN_PROF_MARK(0);
+    if (CS > 1 && t > 0) {
+      if (!poisoned && !mbar_wait_bounded(&full[cur], ((t - 1) >> 1) & 1)) {
+        poisoned = true;
+        report_timeout(p.status, t);
+      }
+      if (tid == 0 && t + 2 < T) mbar_arrive_expect_tx(&full[cur], expect_bytes);  // re-arm for h_{t+1}
+    }
+    FRNN_PROF_MARK(1);
+    // ---------------- phase A: pre[b][g*U + u] = sum_k R[g][u][k] * h_{t-1}[b][k]
     {
       float acc[NT][4];
-      warp_mma_rows<KT, NT>(Rreg, hbuf + cur * BT * HS, HS, 0, lane, acc);
+      warp_mma_rows<KT, NT>(Rreg, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
       const int gid = lane >> 2, tig = lane & 3;
       float* dst = pre + g_w * U + ug_w * 16 + gid;
 #pragma unroll
@@ -186,17 +229,20 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __
         dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
       }
     }
+    FRNN_PROF_MARK(2);
     __syncthreads();
-    // ---------------- phase B: cell update of this thread's items, push h_t to every CTA of the cluster
+    // ---------------- phase B: cell update of this thread's items; new h into this CTA's slice of hbuf[nxt]
     cp_async_wait<kStages - 1>();
-    float hnew[IPT][2], cch[IPT][GCA][2];
+    FRNN_PROF_MARK(3);
+    float cch[IPT][GCA][2];
+    __nv_bfloat16* hdst = hbuf + (size_t)nxt * CS * SL + (size_t)crank * SL;
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_on[i]) continue;
       float prv[2][Gr], wxv[2][Gw];
 #pragma unroll
       for (int g = 0; g < Gr; ++g) {
-        const float2 v = *reinterpret_cast<const float2*>(pre + (size_t)it_bl[i] * PS + g * U + 2 * it_up[i]);
+        const float2 v = *reinterpret_cast<const float2*>(pre_it[i] + g * U);
         prv[0][g] = v.x; prv[1][g] = v.y;
       }
 #pragma unroll
@@ -221,37 +267,42 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __
         for (int s = 0; s < S; ++s) st[i][s][e] = sv[s];
 #pragma unroll
         for (int k = 0; k < GC; ++k) cch[i][k][e] = cv[k];
-        hnew[i][e] = sv[0];
       }
-      const uint32_t hv = pack_bf16x2(hnew[i][0], hnew[i][1]);
+      const uint32_t hv = pack_bf16x2(st[i][0][0], st[i][0][1]);
       // the recurrence continues from the bf16-rounded h, the value every consumer of `states` sees
-      if (!p.state_f32) { const float2 r = unpack_bf16x2(hv); st[i][0][0] = r.x; st[i][0][1] = r.y; }
-      const uint32_t local = hbuf_u32 + (uint32_t)((nxt * BT * HS + it_bl[i] * HS + unit0 + 2 * it_up[i]) * 2);
-      if (CS > 1) {
-        for (int c = 0; c < CS; ++c) st_cluster_u32(map_to_cta(local, (uint32_t)c), hv);
-      } else {
-        *reinterpret_cast<uint32_t*>(hbuf + nxt * BT * HS + it_bl[i] * HS + unit0 + 2 * it_up[i]) = hv;
-      }
+      if (!f32) { const float2 r = unpack_bf16x2(hv); st[i][0][0] = r.x; st[i][0][1] = r.y; }
+      *reinterpret_cast<uint32_t*>(hdst + hloc_it[i]) = hv;
     }
-    if (CS > 1) cluster_arrive();
+    if (CS > 1) fence_proxy_async_smem();  // make the slice visible to the bulk-copy engine
+    FRNN_PROF_MARK(4);
+    __syncthreads();
+    // ---------------- push: this CTA's slice of h_t -> hbuf[nxt] of every other CTA of the cluster
+    if (CS > 1 && t + 1 < T)  // uniform branch; inside, one elected lane per warp issues a copy
+      push_slice_to_peers(my_slice0 + nxt * buf_bytes, slice_bytes, full_u32 + nxt * 8, crank, (uint32_t)CS,
+                          (uint32_t)warp, (uint32_t)(nthr >> 5));
+    FRNN_PROF_MARK(5);
     // ---------------- off the critical path: results to global memory, next Wx prefetch
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_ok[i]) continue;
 #pragma unroll
-      for (int s = 0; s < S; ++s)
-        store_state2(p.states, st_off[i] + ((size_t)s * B * T + t) * ND, p.state_f32, st[i][s][0], st[i][s][1]);
+      for (int s = 0; s < S; ++s) {
+        if (f32) *reinterpret_cast<float2*>(st_ptr[i] + s * st_sstride) = make_float2(st[i][s][0], st[i][s][1]);
+        else *reinterpret_cast<uint32_t*>(st_ptr[i] + s * st_sstride) = pack_bf16x2(st[i][s][0], st[i][s][1]);
+      }
+      st_ptr[i] += ND * st_esz;
       if (GC > 0 && p.cache != nullptr) {
 #pragma unroll
-        for (int k = 0; k < GC; ++k)
-          *reinterpret_cast<uint32_t*>(p.cache + ch_off[i] + ((size_t)t * GC + k) * ND) =
-              pack_bf16x2(cch[i][k][0], cch[i][k][1]);
+        for (int k = 0; k < GC; ++k) ch_ptr[i][(size_t)k * nitems] = pack_bf16x2(cch[i][k][0], cch[i][k][1]);
+        ch_ptr[i] += ch_step;
       }
     }
-    issue_wx(t + kStages, stage);
-    if (CS > 1) cluster_wait(); else __syncthreads();
+    issue_wx(t + kStages < T, stage);
+    FRNN_PROF_MARK(6);
   }
   cp_async_wait<0>();
+  if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight
+  FRNN_PROF_DUMP(p.status);
 }
 
 }  // namespace frnn

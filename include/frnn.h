@@ -73,7 +73,7 @@ typedef struct frnn_plan {
   int32_t wx_stages;       /* time steps of Wx prefetched ahead into shared memory           */
   int32_t cache_slots;     /* activation values cached per (b,t,n,d) in training             */
   int32_t reserved[6];
-  uint64_t cache_bytes;     /* size of the activation cache [B,T,cache_slots,N,D] (dtype_io)  */
+  uint64_t cache_bytes;     /* size of the activation cache (opaque layout, tied to this plan) */
   uint64_t workspace_bytes; /* size of the scratch workspace                                  */
   uint64_t grads_offset;    /* byte offset, inside the workspace, of the fp32 gradients dR || db */
   uint64_t grads_count;     /* number of fp32 values there: Gr*N*D*D + Gt*N*D                 */
@@ -133,6 +133,14 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* args, void* stream)
 /* Whole-sequence backward: reverse time loop + dR + db.  Replaces BackwardPass::Run
  * (flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:768-1086), without its host synchronisation. */
 int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* args, void* stream);
+
+/* The two halves of frnn_backward, for callers that want to time or overlap them separately:
+ * FRNN_PART_LOOP = zero the fp32 gradients, repack R^T, run the reverse time loop (dWx, ds0, db);
+ * FRNN_PART_DR   = the dR reduction over all (b,t), which needs the loop's dWx.  frnn_backward = both, in order.
+ * Same reference counterpart as frnn_backward (the reference also runs these as separate launches,
+ * flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:947-1000 and 1049-1058). */
+enum { FRNN_PART_LOOP = 1, FRNN_PART_DR = 2 };
+int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* args, void* stream, int parts);
 
 /* Casts the fp32 gradients held in the workspace to dtype_io: dR[Gr,N,D,D], db[Gt,N,D].
  * `grads_f32` is workspace + plan->grads_offset (or a buffer of the same layout, e.g. after an all-reduce).

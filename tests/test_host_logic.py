@@ -1,0 +1,115 @@
+"""CPU: host-side logic -- the C-ABI library loads and exports every symbol include/frnn.h declares, the
+planner validates problems and picks tiles, the front end mirrors the reference's config/API.  No kernel runs."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from flashrnn_b200 import FlashRNNConfig, _native, flashrnn
+from flashrnn_b200.flashrnn import _zero_state, rnn_function_registry
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "frnn.h").read_text()
+    declared = set(re.findall(r"\b(frnn_[a-z_]+)\s*\(", header))
+    assert declared == set(_native.EXPORTS), declared ^ set(_native.EXPORTS)
+    L = _native.lib()
+    for sym in declared:
+        assert getattr(L, sym) is not None
+    assert L.frnn_abi_version() == _native.ABI_VERSION
+
+
+def test_struct_sizes_match_header():
+    # int32 x 8 + float x 2; plan = 4 + 40 + 6*4 + 6*4 (reserved) padded to 8 + 4 * 8
+    assert ctypes.sizeof(_native.FrnnProblem) == 40
+    assert ctypes.sizeof(_native.FrnnPlan) == 128
+    assert ctypes.sizeof(_native.FrnnFwdArgs) == 7 * 8 and ctypes.sizeof(_native.FrnnBwdArgs) == 8 * 8
+
+
+@pytest.mark.parametrize("function,B,T,N,D,f32", [
+    ("lstm", 4, 256, 2, 64, False), ("lstm", 16, 1024, 4, 256, False), ("gru", 32, 2048, 8, 128, False),
+    ("slstm", 8, 4096, 4, 192, True), ("elman", 1024, 2048, 16, 64, False)])
+def test_plan_for_benchmark_configs(function, B, T, N, D, f32):
+    Gr, Gw, Gi, Gt, S = rnn_function_registry[function]["gates_states"]
+    plan = _native.query(_native.make_problem(function, B, T, N, D, f32, True))
+    assert plan.cluster_size * plan.units_per_cta == D
+    assert plan.units_per_cta % 16 == 0 and plan.threads == 2 * Gr * plan.units_per_cta
+    assert plan.batch_tile in (8, 16, 32) and 1 <= plan.cluster_size <= 8
+    assert plan.grads_count == Gr * N * D * D + Gt * N * D
+    assert plan.workspace_bytes >= plan.grads_offset + 4 * plan.grads_count
+    rows = -(-B // plan.batch_tile) * plan.batch_tile
+    assert plan.cache_bytes == rows * T * plan.cache_slots * N * D * 2
+
+
+def test_small_batch_spreads_head_large_batch_does_not():
+    small = _native.query(_native.make_problem("lstm", 16, 64, 4, 256, False, True))
+    large = _native.query(_native.make_problem("elman", 1024, 64, 16, 64, False, True))
+    assert small.cluster_size == 8 and large.cluster_size == 1
+
+
+def test_query_rejects_bad_problems():
+    mk = _native.make_problem
+    for prob, code in [(mk("lstm", 2, 3, 1, 40, False, True), -3), (mk("lstm", 0, 3, 1, 32, False, True), -3),
+                       (mk("lstm", 2, 3, 1, 512, False, True), -3)]:
+        with pytest.raises(_native.FrnnError) as e:
+            _native.query(prob)
+        assert e.value.code == code
+    bad = mk("lstm", 2, 3, 1, 32, False, True)
+    bad.cell = 9
+    with pytest.raises(_native.FrnnError) as e:
+        _native.query(bad)
+    assert e.value.code == -2
+    with pytest.raises(_native.FrnnError) as e:  # tile that does not exist: 4 gates x 256 units in one CTA
+        _native.query(mk("lstm", 16, 8, 1, 256, False, True), cluster_size=1, batch_tile=16)
+    assert e.value.code == -6
+
+
+def test_null_and_alignment_checks_happen_before_any_launch():
+    L = _native.lib()
+    plan = _native.query(_native.make_problem("elman", 2, 3, 1, 32, False, True))
+    args = _native.FrnnFwdArgs()  # all NULL
+    assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) == -1
+    for i, name in enumerate(("Wx", "R", "b", "s0", "states", "cache", "workspace")):
+        setattr(args, name, 4096 + 8 if name == "Wx" else 4096)
+    assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) == -5
+    inf = _native.query(_native.make_problem("elman", 2, 3, 1, 32, False, False))
+    assert L.frnn_backward(ctypes.byref(inf), ctypes.byref(_native.FrnnBwdArgs()), None) == -7
+    plan.abi_version = 99
+    assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) == -6
+    assert b"16-byte" in L.frnn_status_string(-5)
+
+
+def test_config_mirrors_reference_registry():
+    for fn, ref in {"lstm": (4, 4, 4, 4, 2), "slstm": (4, 4, 4, 4, 4), "gru": (3, 3, 4, 4, 1), "elman": (1, 1, 1, 1, 1)}.items():
+        c = FlashRNNConfig(function=fn, head_dim=64, num_heads=2, batch_size=3)
+        assert (c.num_gates_r, c.num_gates_w, c.num_gates_i, c.num_gates_t, c.num_states) == ref
+        assert c.hidden_dim == 128 and c.dtype_s == "bfloat16"
+    with pytest.raises(AssertionError):
+        FlashRNNConfig(function="mgu")
+    c = FlashRNNConfig(function="slstm", head_dim=8, num_heads=2)
+    z = _zero_state(c, torch.zeros(3, 5, 4, 2, 8, dtype=torch.bfloat16))
+    assert z.shape == (4, 3, 1, 2, 8) and z.dtype == torch.bfloat16 and float(z.abs().sum()) == 0.0
+
+
+def test_no_cpu_fallback_and_removed_backends():
+    Wx, R, b = torch.zeros(2, 3, 4, 1, 32), torch.zeros(4, 1, 32, 32), torch.zeros(4, 1, 32)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        flashrnn(Wx.bfloat16(), R.bfloat16(), b.bfloat16(), function="lstm")
+    for backend in ("cuda", "triton_fused", "vanilla", "vanilla_fwbw"):
+        with pytest.raises(NotImplementedError):
+            flashrnn(Wx, R, b, function="lstm", backend=backend)
+    with pytest.raises(ValueError):
+        flashrnn(Wx, R, b, function="lstm", backend="tpu")
+    with pytest.raises(NotImplementedError):
+        flashrnn(Wx, R, b, function="lstm", dtype="float16")
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_native, "_lib", None)
+    monkeypatch.setattr(_native, "LIB_PATH", tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _native.lib()
