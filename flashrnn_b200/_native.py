@@ -15,12 +15,14 @@ PKG = Path(__file__).resolve().parent
 LIB_PATH = Path(os.environ.get("FRNN_B200_LIB") or PKG / "libfrnn_b200.so")
 
 ABI_VERSION = 1
+NOALLOC_MAX_SCRATCH_BYTES = 8 << 20  # FRNN_NOALLOC_MAX_SCRATCH_BYTES
 CELL_IDS = {"lstm": 0, "gru": 1, "elman": 2, "slstm": 3}
 DTYPE_BF16, DTYPE_F32 = 0, 1
 
 # every symbol include/frnn.h declares
 EXPORTS = (
     "frnn_abi_version", "frnn_query", "frnn_query_tile", "frnn_forward", "frnn_backward", "frnn_backward_parts",
+    "frnn_forward_noalloc",
     "frnn_finalize_grads", "frnn_read_device_status", "frnn_status_string",
 )
 
@@ -83,6 +85,8 @@ def lib() -> ctypes.CDLL:
         L.frnn_backward.argtypes = [ctypes.POINTER(FrnnPlan), ctypes.POINTER(FrnnBwdArgs), ctypes.c_void_p]
         L.frnn_backward_parts.argtypes = [ctypes.POINTER(FrnnPlan), ctypes.POINTER(FrnnBwdArgs), ctypes.c_void_p, ctypes.c_int]
         L.frnn_backward_parts.restype = ctypes.c_int
+        L.frnn_forward_noalloc.argtypes = [ctypes.POINTER(FrnnProblem), ctypes.POINTER(FrnnFwdArgs), ctypes.c_void_p]
+        L.frnn_forward_noalloc.restype = ctypes.c_int
         L.frnn_finalize_grads.argtypes = [ctypes.POINTER(FrnnPlan), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                           ctypes.c_void_p]
         L.frnn_read_device_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(FrnnDevStatus)]

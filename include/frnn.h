@@ -142,6 +142,26 @@ int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* args, void* stream
 enum { FRNN_PART_LOOP = 1, FRNN_PART_DR = 2 };
 int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* args, void* stream, int parts);
 
+/* Forward pass WITHOUT a caller-provided workspace (args->workspace is ignored and may be NULL).
+ * No counterpart in the reference.  Meant for callers that must not allocate device memory where they call the
+ * library (a fixed arena handed out at start-up, a hot path on which cudaMalloc's device synchronisation is not
+ * acceptable): the forward's scratch -- status block + R repacked into tensor-core fragments -- lives in a
+ * file-scope device array of FRNN_NOALLOC_MAX_SCRATCH_BYTES inside the library, which every GPU that loads the
+ * library holds until the process exits.  Nothing is allocated or freed, by the CUDA runtime or any other library.
+ *   - The plan is chosen as by frnn_query(problem).  Inputs, `states` and (training == 1) the activation `cache`
+ *     of plan.cache_bytes (use frnn_query to size it) are still the caller's buffers.
+ *   - Limit: 256 + Gr*N*D*D*2 bytes (rounded up to 256) must fit FRNN_NOALLOC_MAX_SCRATCH_BYTES, else
+ *     FRNN_ERR_TOO_LARGE is returned and nothing is launched.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on one device share the array.  It keeps the previous call's contents; each call clears the status
+ *     block and rewrites the fragments before use.  Two calls whose GPU work overlaps (different streams, or
+ *     different host threads without ordering) race on it: order them on one stream or with events.
+ *   - Launch errors come back through the return value.  The device-side status block of such a call sits in
+ *     the internal array and cannot be read back; use frnn_forward with a workspace where that matters. */
+#define FRNN_NOALLOC_MAX_SCRATCH_BYTES (8u << 20)
+int frnn_forward_noalloc(const frnn_problem* problem, const frnn_fwd_args* args, void* stream);
+
 /* Casts the fp32 gradients held in the workspace to dtype_io: dR[Gr,N,D,D], db[Gt,N,D].
  * `grads_f32` is workspace + plan->grads_offset (or a buffer of the same layout, e.g. after an all-reduce).
  * Replaces the reference's "accumulate in the parameter dtype" outputs (fused/flashrnn.cc:187-215). */
