@@ -288,7 +288,12 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
     e = launch_loop(k, *plan, lp, stream);
     if (e != cudaSuccess) return (int)e;
   }
-  if (parts & FRNN_PART_DR)
+  // measured on B200: the tcgen05 kernel wins from head_dim 128 up (C2 0.167 vs 0.212 ms, C3 0.263 vs 0.304 ms); below,
+  // the problem is HBM-bound and the warp-MMA kernel with its many small CTAs streams faster (C5 1.55 vs 3.1 ms)
+  if ((parts & FRNN_PART_DR) && pr.D >= 128)
+    e = launch_recurrent_grad_tc(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
+                                 a->s0, grads, reinterpret_cast<unsigned*>(ws), sm_count_cached(), stream);
+  else if (parts & FRNN_PART_DR)
     e = launch_recurrent_grad(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
                             a->s0, grads, sm_count_cached(), stream);
   return (int)e;

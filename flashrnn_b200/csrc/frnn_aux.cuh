@@ -33,6 +33,9 @@ cudaError_t launch_pack_recurrent(const void* R, void* out, int Gr, int N, int D
 cudaError_t launch_recurrent_grad(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,
                                   const void* dg0, const void* states, const void* s0, float* dR, int sm_count,
                                   cudaStream_t stream);
+cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,
+                                     const void* dg0, const void* states, const void* s0, float* dR, unsigned* status,
+                                     int sm_count, cudaStream_t stream);
 cudaError_t launch_cast_grads(const float* src, void* dR, void* db, size_t nR, size_t nb, cudaStream_t stream);
 
 }  // namespace frnn

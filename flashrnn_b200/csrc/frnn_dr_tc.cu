@@ -1,0 +1,295 @@
+// dR on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+//   dR[g,n,d,p] = sum_{b,t} delta_g[b,t,n,d] * h_{t-1}[b,n,p]
+//
+// is, per head n, one GEMM  C[(g,d), p] = A^T B  with  A[k, (g,d)] = delta rows and B[k, p] = h_{t-1} rows,
+// k = b*T + t.  Both operands arrive "MN-major" (k is the slow index of the tensors the time loops wrote), which the
+// UMMA shared-memory descriptors consume directly: no transposition anywhere.
+//
+// One CTA owns a 128-row tile of (g,d) x all D columns of p and a contiguous range of k (split-K over gridDim.z):
+//   * cp.async (16 B) streams 64-row k-chunks of A and B into a 3-stage ring laid out as UMMA core matrices
+//     (8 k-rows x 16 B, no swizzle);
+//   * one thread issues 4 x tcgen05.mma (M128, N = D, K16, bf16 -> fp32) per chunk, accumulating in TMEM;
+//     tcgen05.commit signals an mbarrier per stage so that the ring slot can be refilled;
+//   * after the last chunk the 4 warps read their 32 TMEM lanes (tcgen05.ld) and add the tile into the fp32
+//     gradient workspace with atomics (the k-splits and the batch shards of other calls meet there).
+// Every mbarrier wait is bounded; on expiry the CTA records it in the status block and leaves the loop.
+//
+// Replaces the post-loop cublasGemmStridedBatchedEx of the reference (flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:
+// 1049-1058; util/blas.cu:199-219).
+#include "frnn_aux.cuh"
+
+namespace frnn {
+
+namespace {
+
+constexpr int TC_M = 128;            // rows of (g,d) per CTA = UMMA M
+constexpr int TC_KC = 64;            // k rows per ring stage (4 MMAs of K = 16)
+constexpr int TC_STAGES = 3;
+constexpr int TC_THREADS = 256;       // 8 loader warps; warps 0-3 also drain TMEM
+constexpr int TC_KG = TC_KC / 8;     // 8-row k groups per stage
+constexpr int TC_LBO = 128;          // bytes between core matrices adjacent in k
+constexpr int TC_SBO = TC_KG * 128 + 16;  // bytes between core matrices adjacent in (g,d) / p; +16 spreads the banks
+
+struct DrTcParams {
+  const __nv_bfloat16* dWx;  // [B,T,Gw,N,D]
+  const __nv_bfloat16* dg0;  // [B,T,N,D] (GRU)
+  const void* states;        // [S,B,T,N,D]; only s = 0 is read
+  const void* s0;            // [S,B,1,N,D]
+  float* dR;                 // [Gr,N,D,D] fp32
+  unsigned* status;
+  int cell, T, N, D, Gr, Gw, state_f32;
+  long long K;               // B*T
+  int chunks_per_split;
+  int tmem_cols;             // power of two >= D, >= 32
+};
+
+// ---- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// shared-memory matrix descriptor, no swizzle: start address, leading (k-group) and stride (row-group) byte offsets
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+  return d;
+}
+// instruction descriptor of kind::f16: fp32 accumulate, bf16 A and B, both MN-major, N and M
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+size_t tc_smem_bytes(int D) {
+  return (size_t)TC_STAGES * ((size_t)(TC_M / 8) * TC_SBO + (size_t)(D / 8) * TC_SBO) + 64;
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const DrTcParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int D = p.D, N = p.N, T = p.T, Gr = p.Gr;
+  const int mtile = blockIdx.x, n = blockIdx.y;
+  const size_t ND = (size_t)N * D;
+  const uint32_t a_bytes = (uint32_t)(TC_M / 8) * TC_SBO, b_bytes = (uint32_t)(D / 8) * TC_SBO;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)TC_STAGES * stage_bytes);  // [TC_STAGES]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + TC_STAGES);
+
+  const long long k_begin = (long long)blockIdx.z * p.chunks_per_split * TC_KC;
+  long long k_end = k_begin + (long long)p.chunks_per_split * TC_KC;
+  if (k_end > p.K) k_end = p.K;
+  if (k_begin >= k_end) return;  // uniform for the CTA
+  const int nchunks = (int)((k_end - k_begin + TC_KC - 1) / TC_KC);
+
+  if (warp == 0) tmem_alloc(tmem_slot, (uint32_t)p.tmem_cols);
+  if (tid == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) mbar_init(&bars[s], 1);
+    fence_mbar_init();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // rows of this tile: m = mtile*128 + r  ->  (g, d) = (m / D, m % D); rows beyond Gr*D are zero padding
+  const int rows_total = Gr * D;
+  // Loader mapping (no divisions in the loop): thread -> k-row kr = tid / 4 of the chunk and a 64-byte quad of
+  // 32 consecutive rows (A) / columns (B): quad `sub` of A, quads `sub`, `sub + 4`, ... of B.
+  const int kr = tid >> 2, sub = tid & 3;
+  const uint32_t kr_off = (uint32_t)(kr >> 3) * TC_LBO + (uint32_t)(kr & 7) * 16;
+  const __nv_bfloat16* a_src[1];   // delta row of quad `sub` at k = 0
+  size_t a_stride[1];
+#pragma unroll
+  for (int j = 0; j < 1; ++j) {
+    const int m = mtile * TC_M + sub * 32;
+    a_src[j] = nullptr; a_stride[j] = 0;
+    if (m < rows_total) {
+      const int g = m / D, d = m - g * D;
+      if (p.cell == CELL_GRU && g == 0) { a_src[j] = p.dg0 + (size_t)n * D + d; a_stride[j] = ND; }
+      else {
+        const int gw = (p.cell == CELL_GRU) ? g - 1 : g;
+        a_src[j] = p.dWx + (size_t)gw * ND + (size_t)n * D + d; a_stride[j] = (size_t)p.Gw * ND;
+      }
+    }
+  }
+  const int nquads = D / 32;
+  // time index of this thread's k-row in the current chunk, kept incrementally (h_{t-1} of t = 0 is the initial state)
+  long long kk = k_begin + kr;           // k of this thread's row in chunk 0
+  long long bb = kk / T;
+  int tt = (int)(kk - bb * T);
+  const size_t esz = F32 ? 4 : 2;
+  auto load_chunk = [&](int stage) {  // loads the NEXT chunk in sequence (chunks are requested in order)
+    unsigned char* abase = smem + (size_t)stage * stage_bytes;
+    unsigned char* bbase = abase + a_bytes;
+    const bool krow = kk < k_end;
+#pragma unroll
+    for (int j = 0; j < 1; ++j) {
+      unsigned char* dst = abase + (size_t)(sub * 4) * TC_SBO + kr_off;
+      if (krow && a_src[j] != nullptr) {
+        const __nv_bfloat16* src = a_src[j] + (size_t)kk * a_stride[j];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) cp_async16(dst + (size_t)q * TC_SBO, src + q * 8);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + (size_t)q * TC_SBO) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    const unsigned char* hrow = (tt > 0)
+        ? static_cast<const unsigned char*>(p.states) + ((size_t)(kk - 1) * ND + (size_t)n * D) * esz
+        : static_cast<const unsigned char*>(p.s0) + ((size_t)bb * ND + (size_t)n * D) * esz;
+    for (int quad = sub; quad < nquads; quad += 4) {
+      unsigned char* dst = bbase + (size_t)(quad * 4) * TC_SBO + kr_off;
+      if (krow) {
+        if constexpr (F32) {
+          const float4* src = reinterpret_cast<const float4*>(hrow) + quad * 8;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 v0 = src[2 * q], v1 = src[2 * q + 1];
+            uint4 w;
+            w.x = pack_bf16x2(v0.x, v0.y); w.y = pack_bf16x2(v0.z, v0.w);
+            w.z = pack_bf16x2(v1.x, v1.y); w.w = pack_bf16x2(v1.z, v1.w);
+            *reinterpret_cast<uint4*>(dst + (size_t)q * TC_SBO) = w;
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) cp_async16(dst + (size_t)q * TC_SBO, hrow + (size_t)(quad * 4 + q) * 16);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + (size_t)q * TC_SBO) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    cp_async_commit();
+    kk += TC_KC;
+    tt += TC_KC;
+    while (tt >= T) { tt -= T; ++bb; }
+  };
+
+  const uint32_t idesc = instr_desc(TC_M, D);
+  const uint32_t smem_base = smem_u32(smem);
+  bool poisoned = false;
+
+  load_chunk(0);
+  if (nchunks > 1) load_chunk(1); else cp_async_commit();
+  for (int c = 0; c < nchunks; ++c) {
+    const int s = c % TC_STAGES;
+    if (c + 2 < nchunks) {
+      const int s2 = (c + 2) % TC_STAGES;  // last read by the MMAs of chunk c-1
+      if (c >= 1 && !poisoned && !mbar_wait_bounded(&bars[s2], (uint32_t)(((c - 1) / TC_STAGES) & 1))) {
+        poisoned = true;
+        report_timeout(p.status, c);
+      }
+      load_chunk(s2);
+    } else {
+      cp_async_commit();
+    }
+    cp_async_wait<2>();        // chunk c has landed (at most the two younger groups are pending)
+    fence_proxy_async_smem();  // generic-proxy writes (cp.async, zero fill) -> visible to the tensor core
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+      const uint32_t a0 = smem_base + (uint32_t)s * stage_bytes, b0 = a0 + a_bytes;
+#pragma unroll
+      for (int i = 0; i < TC_KC / 16; ++i) {
+        const uint64_t ad = smem_desc(a0 + i * 2 * TC_LBO, TC_LBO, TC_SBO);
+        const uint64_t bd = smem_desc(b0 + i * 2 * TC_LBO, TC_LBO, TC_SBO);
+        umma_bf16(tmem_base, ad, bd, idesc, (c > 0 || i > 0) ? 1u : 0u);
+      }
+      umma_commit(&bars[s]);
+    }
+  }
+  // ---- all MMAs done -> TMEM -> global
+  {
+    const int last = nchunks - 1;
+    if (!poisoned && !mbar_wait_bounded(&bars[last % TC_STAGES], (uint32_t)((last / TC_STAGES) & 1))) {
+      poisoned = true;
+      report_timeout(p.status, nchunks);
+    }
+  }
+  tc_fence_after();
+  const int m = mtile * TC_M + (warp & 3) * 32 + lane;
+  const bool row_ok = m < rows_total && warp < 4;
+  const int g = row_ok ? m / D : 0, d = row_ok ? m - g * D : 0;
+  float* out = p.dR + (((size_t)g * N + n) * D + d) * D;
+  for (int col0 = 0; col0 < D; col0 += 32) {
+    uint32_t r[32];
+    if (warp < 4) tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, r);
+    if (row_ok && !poisoned) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < D) atomicAdd(out + col0 + j, __uint_as_float(r[j]));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+}
+
+}  // namespace
+
+cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,
+                                     const void* dg0, const void* states, const void* s0, float* dR, unsigned* status,
+                                     int sm_count, cudaStream_t stream) {
+  DrTcParams p;
+  p.dWx = static_cast<const __nv_bfloat16*>(dWx);
+  p.dg0 = static_cast<const __nv_bfloat16*>(dg0);
+  p.states = states; p.s0 = s0; p.dR = dR; p.status = status;
+  p.cell = cell; p.T = T; p.N = N; p.D = D; p.Gr = Gr; p.Gw = Gw; p.state_f32 = state_f32;
+  p.K = (long long)B * T;
+  int cols = 32;
+  while (cols < D) cols *= 2;
+  p.tmem_cols = cols;
+  const int mtiles = (Gr * D + TC_M - 1) / TC_M;
+  const long long chunks = (p.K + TC_KC - 1) / TC_KC;
+  const long long base_ctas = (long long)mtiles * N;
+  long long splits = sm_count / base_ctas;  // one CTA per SM (shared memory): stay within a single wave
+  if (splits > (chunks + 3) / 4) splits = (chunks + 3) / 4;    // at least 4 chunks per split
+  if (splits < 1) splits = 1;
+  if (splits > 65535) splits = 65535;
+  p.chunks_per_split = (int)((chunks + splits - 1) / splits);
+  splits = (chunks + p.chunks_per_split - 1) / p.chunks_per_split;
+  const size_t smem = tc_smem_bytes(D);
+  cudaError_t e;
+  if (state_f32) {
+    e = cudaFuncSetAttribute(recurrent_grad_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    recurrent_grad_tc_kernel<true><<<dim3((unsigned)mtiles, (unsigned)N, (unsigned)splits), TC_THREADS, smem, stream>>>(p);
+  } else {
+    e = cudaFuncSetAttribute(recurrent_grad_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    recurrent_grad_tc_kernel<false><<<dim3((unsigned)mtiles, (unsigned)N, (unsigned)splits), TC_THREADS, smem, stream>>>(p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace frnn
