@@ -29,12 +29,12 @@ LoopKernel get_fwd_kernel(int cell, int kt, int nt) {
   }
   return LoopKernel{nullptr, 0, nullptr};
 }
-LoopKernel get_bwd_kernel(int cell, int kt, int nt) {
+LoopKernel get_bwd_kernel(int cell, int kt, int nt, int mpw) {
   switch (cell) {
-    case CELL_LSTM: return get_bwd_kernel_lstm(kt, nt);
-    case CELL_GRU: return get_bwd_kernel_gru(kt, nt);
-    case CELL_ELMAN: return get_bwd_kernel_elman(kt, nt);
-    case CELL_SLSTM: return get_bwd_kernel_slstm(kt, nt);
+    case CELL_LSTM: return get_bwd_kernel_lstm(kt, nt, mpw);
+    case CELL_GRU: return get_bwd_kernel_gru(kt, nt, mpw);
+    case CELL_ELMAN: return get_bwd_kernel_elman(kt, nt, mpw);
+    case CELL_SLSTM: return get_bwd_kernel_slstm(kt, nt, mpw);
   }
   return LoopKernel{nullptr, 0, nullptr};
 }
@@ -57,6 +57,16 @@ static WsLayout workspace_layout(const frnn_problem& pr, const CellDims& cd) {
   return w;
 }
 
+// Backward exchange scheme of a tile: reduce-scatter (returns MPW = CS / Gr) where that kernel exists and fits,
+// else all-gather (0).
+static int bwd_mpw(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
+  if (cs <= 1 || cs % cd.Gr) return 0;
+  const int U = pr.D / cs, threads = 2 * cd.Gr * U, mpw = cs / cd.Gr;
+  const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, bt / 8, mpw);
+  if (!k.fn || threads > k.max_threads || k.smem_bytes(U, threads) > kMaxDynSmem) return 0;
+  return mpw;
+}
+
 // A tile (cluster size, batch tile) is usable when both loop kernels exist for it, the CTA fits the
 // instantiation's thread bound and the shared-memory budget.
 static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
@@ -66,7 +76,7 @@ static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) 
   if (U % 16 || ((U / 16) & (U / 16 - 1))) return false;  // 16 * power of two
   if (bt != 8 && bt != 16 && bt != 32) return false;
   const int kt = D / 16, nt = bt / 8, threads = 2 * cd.Gr * U;
-  const LoopKernel f = get_fwd_kernel(pr.cell, kt, nt), b = get_bwd_kernel(pr.cell, kt, nt);
+  const LoopKernel f = get_fwd_kernel(pr.cell, kt, nt), b = get_bwd_kernel(pr.cell, kt, nt, 0);
   if (!f.fn || !b.fn) return false;
   if (threads > f.max_threads || threads > b.max_threads || threads < 32) return false;
   if (f.smem_bytes(U, threads) > kMaxDynSmem || b.smem_bytes(U, threads) > kMaxDynSmem) return false;
@@ -284,7 +294,8 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip;
   if (parts & FRNN_PART_LOOP) {
-    const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8);
+    const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8,
+                                        bwd_mpw(pr, cd, plan->cluster_size, plan->batch_tile));
     e = launch_loop(k, *plan, lp, stream);
     if (e != cudaSuccess) return (int)e;
   }

@@ -19,15 +19,15 @@ struct LoopKernel {
 
 // defined once per (cell, direction) in frnn_inst_*.cu; returns fn == nullptr when not instantiated
 LoopKernel get_fwd_kernel(int cell, int kt, int nt);
-LoopKernel get_bwd_kernel(int cell, int kt, int nt);
+LoopKernel get_bwd_kernel(int cell, int kt, int nt, int mpw);  // mpw = 0: all-gather exchange, > 0: reduce-scatter
 LoopKernel get_fwd_kernel_lstm(int kt, int nt);
 LoopKernel get_fwd_kernel_gru(int kt, int nt);
 LoopKernel get_fwd_kernel_elman(int kt, int nt);
 LoopKernel get_fwd_kernel_slstm(int kt, int nt);
-LoopKernel get_bwd_kernel_lstm(int kt, int nt);
-LoopKernel get_bwd_kernel_gru(int kt, int nt);
-LoopKernel get_bwd_kernel_elman(int kt, int nt);
-LoopKernel get_bwd_kernel_slstm(int kt, int nt);
+LoopKernel get_bwd_kernel_lstm(int kt, int nt, int mpw);
+LoopKernel get_bwd_kernel_gru(int kt, int nt, int mpw);
+LoopKernel get_bwd_kernel_elman(int kt, int nt, int mpw);
+LoopKernel get_bwd_kernel_slstm(int kt, int nt, int mpw);
 
 cudaError_t launch_pack_recurrent(const void* R, void* out, int Gr, int N, int D, int transpose, cudaStream_t stream);
 cudaError_t launch_recurrent_grad(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,

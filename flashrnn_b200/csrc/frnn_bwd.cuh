@@ -14,6 +14,15 @@
 //            completing on the peer's mbarrier (no cluster barrier, no fence);
 //   wait     for the slices of the other CTAs (bounded mbarrier wait);
 //   phase A  dh_{t-1}[p] partials = R^T slice x deltas (BT x Gr*D) on the tensor cores -> shared memory.
+//
+// Two ways to organise the cross-CTA part of dh_{t-1} = R^T delta (template parameter MPW):
+//   MPW == 0  "all-gather": every CTA receives the deltas of all CTAs (bf16, Gr*U values per row and CTA) and
+//             multiplies them with its rows p of R^T.  Works for every cluster size.
+//   MPW  > 0  "reduce-scatter": every CTA multiplies ONLY ITS OWN deltas with all D rows of R^T restricted to its
+//             columns (each warp: MPW row tiles x all local k-steps) right after phase B -- no wait in between --
+//             and sends each peer the fp32 partial sums of that peer's rows; the owner adds the CS partials in its
+//             next phase B.  A cluster moves 2-4x fewer bytes per step this way (the exchange is bound by the
+//             ~120 B/clk a cluster's shared-memory network sustains).  Needs CS == MPW * Gr.
 // Cache / state / cotangent values are prefetched kStages steps ahead with cp.async.
 //
 // Replaces FLASHRNNCellFusedBackward (reference flashrnn/flashrnn/fused/flashrnn_fused_backward.cu:129-624),
@@ -76,18 +85,30 @@ __device__ __forceinline__ void cell_backward(float dh, const float* dext, float
   }
 }
 
-template <int CELL, int KT, int NT>
+// U and CS implied by a reduce-scatter instantiation: all Gr*U/16 local k-steps per warp, MPW row tiles per warp
+template <int CELL, int KT, int MPW> struct RsGeom {
+  static constexpr int KPW = MPW > 0 ? KT / MPW : 0;              // local k-steps = Gr * U / 16
+  static constexpr int NUT = MPW > 0 ? KPW / Cell<CELL>::Gr : 0;  // 16-unit tiles per CTA
+  static constexpr int U = NUT * 16;
+  static constexpr int CS = MPW * Cell<CELL>::Gr;
+  static constexpr bool valid = MPW > 0 && KT % MPW == 0 && KPW % Cell<CELL>::Gr == 0 && NUT >= 1 &&
+                                (NUT & (NUT - 1)) == 0 && CS <= 8 && CS * U == KT * 16;
+};
+
+template <int CELL, int KT, int NT, int MPW>
 __host__ __device__ constexpr size_t bwd_smem_bytes(int U, int threads) {
   using C = Cell<CELL>;
   constexpr int D = KT * 16, BT = NT * 8;
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
   constexpr int GCA = C::GC > 0 ? C::GC : 1;
   const int CS = D / U;
-  return (size_t)2 * CS * BT * (C::Gr * U + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 +
-         (size_t)kStages * GCA * IPT * threads * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * threads * 8 + 16;
+  const size_t rings = (size_t)kStages * GCA * IPT * threads * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * threads * 8 + 16;
+  if (MPW > 0)  // delta tile + double-buffered send and receive slices of fp32 partials
+    return (size_t)BT * (C::Gr * U + 8) * 2 + (size_t)4 * CS * BT * (U + 4) * 4 + rings;
+  return (size_t)2 * CS * BT * (C::Gr * U + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 + rings;
 }
 
-template <int CELL, int KT, int NT>
+template <int CELL, int KT, int NT, int MPW>
 __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, NNEED = C::NNEED, NEXT = C::NEXT;
@@ -95,31 +116,47 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);
   constexpr int GCA = GC > 0 ? GC : 1;
   constexpr int NSS = NNEED + NEXT;  // 8-byte slots per item and stage in the state ring
+  constexpr bool RS = MPW > 0;
+  constexpr int KPW = RS ? KT / (RS ? MPW : 1) : KT;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nthr = blockDim.x;
   const int U = p.U, CS = p.CS, T = p.T, N = p.N, B = p.B;
-  const int GS = Gr * U + 8;        // row pitch (elements) inside a delta slice: [b][g*U + u]
-  const int SL = BT * GS;           // elements per slice
+  const int GS = Gr * U + 8;        // row pitch (elements) of a delta tile: [b][g*U + u]
+  const int SL = BT * GS;           // elements per delta slice
   const int ushift = 31 - __clz(U >> 4);
-  const int PS = U + 4;
+  const int PS = U + 4;             // row pitch (floats) of a partial-sum tile [b][u]; == 4 (mod 16): conflict-free stores
+  const int PSL = BT * PS;          // floats per partial-sum slice
   const int n = blockIdx.z, bt0 = blockIdx.y * BT;
   const uint32_t crank = (CS > 1) ? cluster_ctarank() : 0u;
   const int unit0 = (int)crank * U;
   const size_t ND = (size_t)N * D;
   const int f32 = p.state_f32;
+  const int nUT = U >> 4;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* dgbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                      // [2][CS][BT][GS]
-  float* part = reinterpret_cast<float*>(smem_raw + (size_t)2 * CS * SL * 2);             // [Gr][BT][PS]
-  uint32_t* ringc = reinterpret_cast<uint32_t*>(part + (size_t)Gr * BT * PS);             // [kStages][GCA][IPT][nthr]
+  // all-gather:      dgbuf [2][CS][BT][GS] bf16 | part [Gr][BT][PS] f32
+  // reduce-scatter:  dgbuf [BT][GS] bf16        | stage [2][CS][BT][PS] f32 | recv [2][CS][BT][PS] f32
+  __nv_bfloat16* dgbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  float* part = reinterpret_cast<float*>(smem_raw + (RS ? (size_t)SL * 2 : (size_t)2 * CS * SL * 2));
+  float* stage_buf = part;                                  // RS only
+  float* recv_buf = part + (size_t)2 * CS * PSL;            // RS only
+  uint32_t* ringc = reinterpret_cast<uint32_t*>(part + (RS ? (size_t)4 * CS * PSL : (size_t)Gr * BT * PS));  // [kStages][GCA][IPT][nthr]
   uint2* rings = reinterpret_cast<uint2*>(ringc + (size_t)kStages * GCA * IPT * nthr);    // [kStages][NSS][IPT][nthr]
   uint64_t* full = reinterpret_cast<uint64_t*>(rings + (size_t)kStages * NSS * IPT * nthr);  // [2]
 
-  // ---- R^T slice: rows p = 16 units of this CTA, columns = gate g_w's D output units
-  const int nUT = U >> 4;
-  const int g_w = warp / nUT, ug_w = warp - g_w * nUT;
+  // ---- this warp's fragments of R^T (rows p, columns = gate rows), resident for the whole sequence
+  const int g_w = warp / nUT, ug_w = warp - g_w * nUT;  // all-gather: gate / unit tile of this warp
   uint4 Rreg[KT];
-  {
+  if constexpr (RS) {
+    // rows p: tiles warp*MPW + mi (all D rows are covered by the CTA's warps); columns: the CTA's own (g, u)
+#pragma unroll
+    for (int mi = 0; mi < MPW; ++mi)
+#pragma unroll
+      for (int ks = 0; ks < KPW; ++ks) {
+        const int g = ks / nUT, ul = ks - g * nUT;
+        Rreg[mi * KPW + ks] = __ldg(p.Rpack + ((((size_t)n * Gr + g) * (D / 16) + (warp * MPW + mi)) * KT + (unit0 / 16 + ul)) * 32 + lane);
+      }
+  } else {
     const uint4* src = p.Rpack + ((((size_t)n * Gr + g_w) * (D / 16) + (unit0 / 16 + ug_w)) * KT) * 32 + lane;
 #pragma unroll
     for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(src + k * 32);
@@ -132,8 +169,8 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   const size_t st_sstride = (size_t)B * T * ND * st_esz;
   const size_t ch_step = (size_t)gridDim.x * gridDim.y * gridDim.z * GCA * nitems;
   bool it_on[IPT], it_ok[IPT];
-  const float* part_it[IPT];            // &part[0][bl][2*up]
-  uint32_t dloc_it[IPT];                // element offset of (bl, gate 0, 2*up) inside this CTA's slice
+  uint32_t part_it[IPT];                // float offset of (bl, 2*up) inside a partial-sum tile
+  uint32_t dloc_it[IPT];                // element offset of (bl, gate 0, 2*up) inside a delta tile
   const uint32_t* ch_pf[IPT];           // cache of the next step to prefetch
   const unsigned char* st_pf[IPT];      // states[0][b][t-1] of the next step to prefetch
   const unsigned char* ds_pf[IPT];      // dstates[0][b][t]  of the next step to prefetch
@@ -150,7 +187,7 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
     const int bg = bt0 + bl, d = unit0 + 2 * up;
     it_ok[i] = it_on[i] && bg < B;
     const int bgc = bg < B ? bg : B - 1;
-    part_it[i] = part + (size_t)bl * PS + 2 * up;
+    part_it[i] = (uint32_t)(bl * PS + 2 * up);
     dloc_it[i] = (uint32_t)(bl * GS + 2 * up);
     const size_t st_off = ((size_t)bgc * T) * ND + (size_t)n * D + d;
     s0_off[i] = ((size_t)bgc) * ND + (size_t)n * D + d;  // + s*B*ND
@@ -171,7 +208,8 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
       cur[i][k][0] = v.x; cur[i][k][1] = v.y;
     }
   }
-  for (int idx = tid; idx < Gr * BT * PS; idx += nthr) part[idx] = 0.f;
+  // no recurrent cotangent flows into the last time step: the partial sums read by the first phase B are zero
+  for (int idx = tid; idx < (RS ? 4 * CS * PSL : Gr * BT * PS); idx += nthr) part[idx] = 0.f;
 
   // ---- prefetch ring: everything step t needs except what is carried in registers.  Issued in step order
   // T-1, T-2, ...; `t` is the step being prefetched.
@@ -215,8 +253,8 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
 #pragma unroll
   for (int s = 0; s < kStages; ++s) issue(T - 1 - s, s);
 
-  // ---- cluster set-up
-  const uint32_t slice_bytes = (uint32_t)(SL * 2);
+  // ---- cluster set-up.  full[x] counts the bytes delivered into buffer x (x = step index & 1)
+  const uint32_t slice_bytes = RS ? (uint32_t)(PSL * 4) : (uint32_t)(SL * 2);
   const uint32_t expect_bytes = (uint32_t)(CS - 1) * slice_bytes;
   bool poisoned = false;
   if (CS > 1) {
@@ -224,7 +262,7 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
       mbar_init(&full[0], 1);
       mbar_init(&full[1], 1);
       fence_mbar_init();
-      mbar_arrive_expect_tx(&full[0], expect_bytes);             // deltas of step index 0 (t = T-1)
+      mbar_arrive_expect_tx(&full[0], expect_bytes);             // exchange of step index 0 (t = T-1)
       if (T > 1) mbar_arrive_expect_tx(&full[1], expect_bytes);  // step index 1
     }
     cluster_arrive();
@@ -232,13 +270,36 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   } else {
     __syncthreads();
   }
-  const uint32_t my_slice0 = smem_u32(dgbuf + (size_t)crank * SL);
-  const uint32_t buf_bytes = (uint32_t)(CS * SL * 2);
   const uint32_t full_u32 = smem_u32(&full[0]);
   auto ring_state = [&](int stage, int slot, int i) -> float2 {
     const uint2 w = rings[((size_t)(stage * NSS + slot) * IPT + i) * nthr + tid];
     if (f32) return make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
     return unpack_bf16x2(w.x);
+  };
+  // recurrent part of dh for item i: sum of the partial products of the previous step (`pbuf` = its buffer index)
+  auto recurrent_sum = [&](int i, int pbuf, float (&rec)[2]) {
+    if constexpr (RS) {
+      const float* src = recv_buf + (size_t)pbuf * CS * PSL + part_it[i];
+      for (int c = 0; c < CS; ++c) {
+        const float2 v = *reinterpret_cast<const float2*>(src + (size_t)c * PSL);
+        rec[0] += v.x; rec[1] += v.y;
+      }
+    } else {
+#pragma unroll
+      for (int g = 0; g < Gr; ++g) {
+        const float2 v = *reinterpret_cast<const float2*>(part + (size_t)g * BT * PS + part_it[i]);
+        rec[0] += v.x; rec[1] += v.y;
+      }
+    }
+  };
+  auto wait_exchange = [&](int buf, int j, int t) {  // data of step index j has landed in buffer `buf`
+    if (CS > 1) {
+      if (!poisoned && !mbar_wait_bounded(&full[buf], (uint32_t)((j >> 1) & 1))) {
+        poisoned = true;
+        report_timeout(p.status, t);
+      }
+      if (tid == 0 && j + 2 < T) mbar_arrive_expect_tx(&full[buf], expect_bytes);  // re-arm for step index j + 2
+    }
   };
 
   int stage = 0;
@@ -247,19 +308,16 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
     const int t = T - 1 - j, buf = j & 1;
     FRNN_PROF_MARK(0);
     cp_async_wait<kStages - 1>();
+    if constexpr (RS) { if (j > 0) wait_exchange(buf ^ 1, j - 1, t); }  // partial sums produced in step j-1
     FRNN_PROF_MARK(1);
     float dwv[IPT][Gw][2], dg0v[IPT][2];
-    __nv_bfloat16* ddst = dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
-    // ---------------- phase B: pointwise backward; R-gate deltas into this CTA's slice
+    __nv_bfloat16* ddst = RS ? dgbuf : dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
+    // ---------------- phase B: pointwise backward; R-gate deltas (bf16) into the delta tile
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_on[i]) continue;
       float rec[2] = {car[i][0][0], car[i][0][1]};
-#pragma unroll
-      for (int g = 0; g < Gr; ++g) {
-        const float2 v = *reinterpret_cast<const float2*>(part_it[i] + (size_t)g * BT * PS);
-        rec[0] += v.x; rec[1] += v.y;
-      }
+      recurrent_sum(i, buf ^ 1, rec);
       float prvv[NNEED][2], extv[NEXT][2], chv[GCA][2];
 #pragma unroll
       for (int k = 0; k < NNEED; ++k) { const float2 v = ring_state(stage, k, i); prvv[k][0] = v.x; prvv[k][1] = v.y; }
@@ -303,13 +361,51 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
       for (int g = 0; g < Gr; ++g)
         *reinterpret_cast<uint32_t*>(ddst + dloc_it[i] + g * U) = pack_bf16x2(dRv[0][g], dRv[1][g]);
     }
-    if (CS > 1) fence_proxy_async_smem();
+    if (!RS && CS > 1) fence_proxy_async_smem();
     FRNN_PROF_MARK(2);
     __syncthreads();
-    // ---------------- push this CTA's delta slice to every other CTA of the cluster
-    if (CS > 1)  // uniform branch; inside, one elected lane per warp issues a copy
-      push_slice_to_peers(my_slice0 + buf * buf_bytes, slice_bytes, full_u32 + buf * 8, crank, (uint32_t)CS,
-                          (uint32_t)warp, (uint32_t)(nthr >> 5));
+    if constexpr (RS) {
+      // ---------------- phase A (reduce-scatter): partial dh_{t-1}[all p] from this CTA's deltas only
+      float* sbuf = stage_buf + (size_t)buf * CS * PSL;
+      float* rbuf = recv_buf + (size_t)buf * CS * PSL;
+      const int gid = lane >> 2, tig = lane & 3;
+#pragma unroll
+      for (int mi = 0; mi < MPW; ++mi) {
+        float acc[NT][4];
+        warp_mma_rows<KPW, NT>(reinterpret_cast<const uint4(&)[KPW]>(Rreg[mi * KPW]), dgbuf, GS, 0, 30, 0, lane, acc);  // one slice: columns k*16
+        const int mt = warp * MPW + mi;                 // row tile of p: owner CTA = mt / nUT
+        const int dest = mt >> ushift, ul = mt & (nUT - 1);
+        float* dst = ((uint32_t)dest == crank ? rbuf : sbuf) + (size_t)dest * PSL + ul * 16 + gid;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int b0 = nt * 8 + 2 * tig;
+          dst[(size_t)b0 * PS] = acc[nt][0];
+          dst[(size_t)(b0 + 1) * PS] = acc[nt][1];
+          dst[(size_t)b0 * PS + 8] = acc[nt][2];
+          dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
+        }
+      }
+      if (CS > 1) fence_proxy_async_smem();
+      FRNN_PROF_MARK(3);
+      __syncthreads();
+      // ---------------- push the partial sums of every peer's rows into that peer's receive slice [buf][me]
+      if (CS > 1) {
+        __syncwarp();
+        const uint32_t s0a = smem_u32(sbuf), r0a = smem_u32(rbuf) + crank * slice_bytes;
+#pragma unroll 1
+        for (uint32_t c = (uint32_t)warp; c < (uint32_t)CS; c += (uint32_t)(nthr >> 5)) {
+          if (c == crank) continue;
+          const uint32_t dsta = map_to_cta(r0a, c), bara = map_to_cta(full_u32 + buf * 8, c);
+          if (elect_one_sync()) bulk_copy_to_cta(dsta, s0a + c * slice_bytes, slice_bytes, bara);
+        }
+      }
+      FRNN_PROF_MARK(4);
+    } else {
+      // ---------------- push this CTA's delta slice to every other CTA of the cluster
+      if (CS > 1)  // uniform branch; inside, one elected lane per warp issues a copy
+        push_slice_to_peers(smem_u32(ddst), slice_bytes, full_u32 + buf * 8, crank, (uint32_t)CS, (uint32_t)warp,
+                            (uint32_t)(nthr >> 5));
+    }
     // ---------------- off the critical path: dWx to global memory, next prefetch
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
@@ -325,17 +421,11 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
     }
     issue(t - kStages, stage);
     stage = (stage + 1 == kStages) ? 0 : stage + 1;
-    FRNN_PROF_MARK(3);
-    if (CS > 1) {
-      if (!poisoned && !mbar_wait_bounded(&full[buf], (j >> 1) & 1)) {
-        poisoned = true;
-        report_timeout(p.status, t);
-      }
-      if (tid == 0 && j + 2 < T) mbar_arrive_expect_tx(&full[buf], expect_bytes);
-    }
-    FRNN_PROF_MARK(4);
-    // ---------------- phase A: part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
-    {
+    if constexpr (!RS) {
+      FRNN_PROF_MARK(3);
+      wait_exchange(buf, j, t);
+      FRNN_PROF_MARK(4);
+      // ---------------- phase A (all-gather): part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
       float acc[NT][4];
       warp_mma_rows<KT, NT>(Rreg, dgbuf + (size_t)buf * CS * SL, GS, g_w * U, ushift, SL, lane, acc);
       const int gid = lane >> 2, tig = lane & 3;
@@ -348,12 +438,13 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
         dst[(size_t)b0 * PS + 8] = acc[nt][2];
         dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
       }
+      FRNN_PROF_MARK(5);
+      __syncthreads();
     }
-    FRNN_PROF_MARK(5);
-    __syncthreads();
     FRNN_PROF_MARK(6);
   }
   cp_async_wait<0>();
+  if constexpr (RS) { if (T > 0) wait_exchange((T - 1) & 1, T - 1, -1); }
   FRNN_PROF_DUMP(p.status);
 
   // ---- cotangent of the initial states, bias gradient
@@ -361,11 +452,7 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   for (int i = 0; i < IPT; ++i) {
     if (!it_ok[i]) continue;
     float rec[2] = {car[i][0][0], car[i][0][1]};
-#pragma unroll
-    for (int g = 0; g < Gr; ++g) {
-      const float2 v = *reinterpret_cast<const float2*>(part_it[i] + (size_t)g * BT * PS);
-      rec[0] += v.x; rec[1] += v.y;
-    }
+    recurrent_sum(i, (T - 1) & 1, rec);
     store_state2(p.ds0, s0_off[i], f32, rec[0], rec[1]);
 #pragma unroll
     for (int s = 1; s < S; ++s) store_state2(p.ds0, s0_off[i] + (size_t)s * B * ND, f32, car[i][s][0], car[i][s][1]);

@@ -245,7 +245,7 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
       const int kk = k + (j >> 1);
       ldmatrix_x4(base + (uint32_t)(((kk >> ushift) * slice_elems + (kk & kmask) * 16) * 2), b0, b1, b2, b3);
       mma_bf16_16816(acc[k % NACC][0], Areg[k], b0, b1);
-      mma_bf16_16816(acc[(k + 1) % NACC][0], Areg[k + 1], b2, b3);
+      if (k + 1 < KT) mma_bf16_16816(acc[(k + 1) % NACC][0], Areg[k + 1], b2, b3);  // odd KT: second half unused
     }
   } else {
     // one ldmatrix.x4 covers one k-step of two 8-row batch tiles

@@ -6,16 +6,43 @@
 
 namespace frnn {
 
+#if FRNN_INST_BWD
+
+template <int KT, int NT, int MPW>
+static LoopKernel make_entry() {
+  LoopKernel k;
+  k.fn = reinterpret_cast<const void*>(&frnn_bwd_kernel<FRNN_INST_CELL, KT, NT, MPW>);
+  k.smem_bytes = [](int U, int threads) -> size_t { return bwd_smem_bytes<FRNN_INST_CELL, KT, NT, MPW>(U, threads); };
+  k.max_threads = MaxThreads<KT>::v;
+  return k;
+}
+// reduce-scatter variants exist only where the geometry works out (CS = MPW * Gr <= 8, U a power of two times 16)
+template <int KT, int NT, int MPW, bool V = RsGeom<FRNN_INST_CELL, KT, MPW>::valid>
+struct RsEntry { static LoopKernel get() { return LoopKernel{nullptr, 0, nullptr}; } };
+template <int KT, int NT, int MPW>
+struct RsEntry<KT, NT, MPW, true> { static LoopKernel get() { return make_entry<KT, NT, MPW>(); } };
+
+LoopKernel FRNN_INST_NAME(int kt, int nt, int mpw) {
+#define FRNN_CASE(KT, NT) if (kt == KT && nt == NT && mpw == 0) return make_entry<KT, NT, 0>();
+#define FRNN_RS(KT, NT, MPW) if (kt == KT && nt == NT && mpw == MPW) return RsEntry<KT, NT, MPW>::get();
+#define FRNN_ROW(KT, unused)                                                                     \
+  FRNN_CASE(KT, 1) FRNN_CASE(KT, 2) FRNN_CASE(KT, 4)                                             \
+  FRNN_RS(KT, 1, 1) FRNN_RS(KT, 1, 2) FRNN_RS(KT, 1, 4) FRNN_RS(KT, 1, 8)                        \
+  FRNN_RS(KT, 2, 1) FRNN_RS(KT, 2, 2) FRNN_RS(KT, 2, 4) FRNN_RS(KT, 2, 8)
+  FRNN_FOREACH_KT(FRNN_ROW, 0)
+#undef FRNN_ROW
+#undef FRNN_RS
+#undef FRNN_CASE
+  return LoopKernel{nullptr, 0, nullptr};
+}
+
+#else
+
 template <int KT, int NT>
 static LoopKernel make_entry() {
   LoopKernel k;
-#if FRNN_INST_BWD
-  k.fn = reinterpret_cast<const void*>(&frnn_bwd_kernel<FRNN_INST_CELL, KT, NT>);
-  k.smem_bytes = [](int U, int threads) -> size_t { return bwd_smem_bytes<FRNN_INST_CELL, KT, NT>(U, threads); };
-#else
   k.fn = reinterpret_cast<const void*>(&frnn_fwd_kernel<FRNN_INST_CELL, KT, NT>);
   k.smem_bytes = [](int U, int threads) -> size_t { return fwd_smem_bytes<FRNN_INST_CELL, KT, NT>(U, threads); };
-#endif
   k.max_threads = MaxThreads<KT>::v;
   return k;
 }
@@ -28,5 +55,7 @@ LoopKernel FRNN_INST_NAME(int kt, int nt) {
 #undef FRNN_CASE
   return LoopKernel{nullptr, 0, nullptr};
 }
+
+#endif
 
 }  // namespace frnn
