@@ -32,6 +32,7 @@ class FrnnProblem(ctypes.Structure):
         ("cell", ctypes.c_int32), ("B", ctypes.c_int32), ("T", ctypes.c_int32), ("N", ctypes.c_int32),
         ("D", ctypes.c_int32), ("dtype_io", ctypes.c_int32), ("dtype_state", ctypes.c_int32),
         ("training", ctypes.c_int32), ("forward_clip", ctypes.c_float), ("grad_clip", ctypes.c_float),
+        ("grad_cut", ctypes.c_int32),
     ]
 
 
@@ -111,11 +112,11 @@ def check(what: str, code: int) -> None:
 
 
 def make_problem(function: str, B: int, T: int, N: int, D: int, state_f32: bool, training: bool,
-                 forward_clip: float | None = None, grad_clip: float | None = None) -> FrnnProblem:
+                 forward_clip: float | None = None, grad_clip: float | None = None, grad_cut: bool = False) -> FrnnProblem:
     if function not in CELL_IDS:
         raise AssertionError(f"RNN function {function} not in registry")
     return FrnnProblem(CELL_IDS[function], B, T, N, D, DTYPE_BF16, DTYPE_F32 if state_f32 else DTYPE_BF16,
-                       1 if training else 0, float(forward_clip or 0.0), float(grad_clip or 0.0))
+                       1 if training else 0, float(forward_clip or 0.0), float(grad_clip or 0.0), 1 if grad_cut else 0)
 
 
 def query(problem: FrnnProblem, cluster_size: int = 0, batch_tile: int = 0) -> FrnnPlan:

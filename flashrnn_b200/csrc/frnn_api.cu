@@ -14,7 +14,7 @@ static bool cell_dims(int cell, CellDims* d) {
   switch (cell) {
     case CELL_LSTM:  *d = {4, 4, 4, 2, 4}; return true;
     case CELL_GRU:   *d = {3, 3, 4, 1, 4}; return true;
-    case CELL_ELMAN: *d = {1, 1, 1, 1, 0}; return true;
+    case CELL_ELMAN: *d = {1, 1, 1, 1, 1}; return true;
     case CELL_SLSTM: *d = {4, 4, 4, 4, 5}; return true;
   }
   return false;
@@ -25,6 +25,7 @@ LoopKernel get_fwd_kernel(int cell, int kt, int nt) {
     case CELL_LSTM: return get_fwd_kernel_lstm(kt, nt);
     case CELL_GRU: return get_fwd_kernel_gru(kt, nt);
     case CELL_ELMAN: return get_fwd_kernel_elman(kt, nt);
+    case CELL_ELMAN_CLIP: return get_fwd_kernel_elmanc(kt, nt);
     case CELL_SLSTM: return get_fwd_kernel_slstm(kt, nt);
   }
   return LoopKernel{nullptr, 0, nullptr};
@@ -34,9 +35,15 @@ LoopKernel get_bwd_kernel(int cell, int kt, int nt, int mpw) {
     case CELL_LSTM: return get_bwd_kernel_lstm(kt, nt, mpw);
     case CELL_GRU: return get_bwd_kernel_gru(kt, nt, mpw);
     case CELL_ELMAN: return get_bwd_kernel_elman(kt, nt, mpw);
+    case CELL_ELMAN_CLIP: return get_bwd_kernel_elmanc(kt, nt, mpw);
     case CELL_SLSTM: return get_bwd_kernel_slstm(kt, nt, mpw);
   }
   return LoopKernel{nullptr, 0, nullptr};
+}
+
+// kernel family of a problem: the public cell id, except Elman with a forward clamp (caches its tanh output)
+static int kernel_cell(const frnn_problem& pr) {
+  return (pr.cell == CELL_ELMAN && pr.forward_clip > 0.f) ? (int)CELL_ELMAN_CLIP : pr.cell;
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -62,7 +69,7 @@ static WsLayout workspace_layout(const frnn_problem& pr, const CellDims& cd) {
 static int bwd_mpw(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
   if (cs <= 1 || cs % cd.Gr) return 0;
   const int U = pr.D / cs, threads = 2 * cd.Gr * U, mpw = cs / cd.Gr;
-  const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, bt / 8, mpw);
+  const LoopKernel k = get_bwd_kernel(kernel_cell(pr),pr.D / 16, bt / 8, mpw);
   if (!k.fn || threads > k.max_threads || k.smem_bytes(U, threads) > kMaxDynSmem) return 0;
   return mpw;
 }
@@ -76,7 +83,7 @@ static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) 
   if (U % 16 || ((U / 16) & (U / 16 - 1))) return false;  // 16 * power of two
   if (bt != 8 && bt != 16 && bt != 32) return false;
   const int kt = D / 16, nt = bt / 8, threads = 2 * cd.Gr * U;
-  const LoopKernel f = get_fwd_kernel(pr.cell, kt, nt), b = get_bwd_kernel(pr.cell, kt, nt, 0);
+  const LoopKernel f = get_fwd_kernel(kernel_cell(pr),kt, nt), b = get_bwd_kernel(kernel_cell(pr),kt, nt, 0);
   if (!f.fn || !b.fn) return false;
   if (threads > f.max_threads || threads > b.max_threads || threads < 32) return false;
   if (f.smem_bytes(U, threads) > kMaxDynSmem || b.smem_bytes(U, threads) > kMaxDynSmem) return false;
@@ -137,10 +144,11 @@ static int fill_plan(const frnn_problem* pr, int cs, int bt, int stages, frnn_pl
   pl.batch_tile = cbt;
   pl.threads = 2 * cd.Gr * pl.units_per_cta;
   pl.wx_stages = kStages;
-  pl.cache_slots = cd.GC;
+  // Elman needs its one cache slot (the tanh output) only when h is clamped afterwards; otherwise h itself serves
+  pl.cache_slots = (pr->cell == CELL_ELMAN && !(pr->forward_clip > 0.f)) ? 0 : cd.GC;
   // one bf16 pair per (item, slot, step) in the time loops' own order; batch rows padded to whole tiles
   const uint64_t rows = (uint64_t)((pr->B + cbt - 1) / cbt) * cbt;
-  pl.cache_bytes = rows * pr->T * cd.GC * pr->N * pr->D * 2;
+  pl.cache_bytes = rows * pr->T * pl.cache_slots * pr->N * pr->D * 2;
   const WsLayout w = workspace_layout(*pr, cd);
   pl.workspace_bytes = w.total;
   pl.grads_offset = w.grads;
@@ -241,8 +249,8 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   lp.B = pr.B; lp.T = pr.T; lp.N = pr.N; lp.D = pr.D;
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
-  lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip;
-  const LoopKernel k = get_fwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8);
+  lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
+  const LoopKernel k = get_fwd_kernel(kernel_cell(pr),pr.D / 16, plan->batch_tile / 8);
   e = launch_loop(k, *plan, lp, stream);
   return (int)e;
 }
@@ -292,9 +300,9 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   lp.B = pr.B; lp.T = pr.T; lp.N = pr.N; lp.D = pr.D;
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
-  lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip;
+  lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
   if (parts & FRNN_PART_LOOP) {
-    const LoopKernel k = get_bwd_kernel(pr.cell, pr.D / 16, plan->batch_tile / 8,
+    const LoopKernel k = get_bwd_kernel(kernel_cell(pr),pr.D / 16, plan->batch_tile / 8,
                                         bwd_mpw(pr, cd, plan->cluster_size, plan->batch_tile));
     e = launch_loop(k, *plan, lp, stream);
     if (e != cudaSuccess) return (int)e;

@@ -24,6 +24,8 @@ LoopKernel get_fwd_kernel_lstm(int kt, int nt);
 LoopKernel get_fwd_kernel_gru(int kt, int nt);
 LoopKernel get_fwd_kernel_elman(int kt, int nt);
 LoopKernel get_fwd_kernel_slstm(int kt, int nt);
+LoopKernel get_fwd_kernel_elmanc(int kt, int nt);
+LoopKernel get_bwd_kernel_elmanc(int kt, int nt, int mpw);
 LoopKernel get_bwd_kernel_lstm(int kt, int nt, int mpw);
 LoopKernel get_bwd_kernel_gru(int kt, int nt, int mpw);
 LoopKernel get_bwd_kernel_elman(int kt, int nt, int mpw);

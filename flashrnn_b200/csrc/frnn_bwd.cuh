@@ -65,8 +65,9 @@ __device__ __forceinline__ void cell_backward(float dh, const float* dext, float
     dW_[0] = dr; dW_[1] = dz; dW_[2] = dn;
     dB_[0] = dg; dB_[1] = dr; dB_[2] = dz; dB_[3] = dn;
     car[0] = zg * dh;
-  } else if constexpr (CELL == CELL_ELMAN) {  // fused/elman_fused_pointwise.cuh:62-93
-    const float dg = dh * (1.f - cur[0] * cur[0]);
+  } else if constexpr (CELL == CELL_ELMAN || CELL == CELL_ELMAN_CLIP) {  // fused/elman_fused_pointwise.cuh:62-93
+    const float hv = (CELL == CELL_ELMAN_CLIP) ? cache[0] : cur[0];  // the tanh output (before any forward clamp)
+    const float dg = dh * (1.f - hv * hv);
     dR_[0] = dg; dW_[0] = dg; dB_[0] = dg;
     car[0] = 0.f;
   } else {  // sLSTM, vanilla_fwbw/bw.py:136-189 (stabiliser m treated as a constant)
@@ -109,7 +110,7 @@ __host__ __device__ constexpr size_t bwd_smem_bytes(int U, int threads) {
 }
 
 template <int CELL, int KT, int NT, int MPW>
-__global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __grid_constant__ LoopParams p) {
+__global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<CELL, KT>::min_blocks) frnn_bwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, NNEED = C::NNEED, NEXT = C::NEXT;
   constexpr int D = KT * 16, BT = NT * 8;
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
     for (int i = 0; i < IPT; ++i) {
       if (!it_on[i]) continue;
       float rec[2] = {car[i][0][0], car[i][0][1]};
-      recurrent_sum(i, buf ^ 1, rec);
+      if (!p.grad_cut) recurrent_sum(i, buf ^ 1, rec);
       float prvv[NNEED][2], extv[NEXT][2], chv[GCA][2];
 #pragma unroll
       for (int k = 0; k < NNEED; ++k) { const float2 v = ring_state(stage, k, i); prvv[k][0] = v.x; prvv[k][1] = v.y; }
@@ -369,20 +370,20 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
       float* sbuf = stage_buf + (size_t)buf * CS * PSL;
       float* rbuf = recv_buf + (size_t)buf * CS * PSL;
       const int gid = lane >> 2, tig = lane & 3;
+      float acc[RS ? MPW : 1][NT][4];
+      warp_mma_tiles<(RS ? MPW : 1), KPW, NT>(Rreg, dgbuf, GS, lane, acc);
 #pragma unroll
       for (int mi = 0; mi < MPW; ++mi) {
-        float acc[NT][4];
-        warp_mma_rows<KPW, NT>(reinterpret_cast<const uint4(&)[KPW]>(Rreg[mi * KPW]), dgbuf, GS, 0, 30, 0, lane, acc);  // one slice: columns k*16
         const int mt = warp * MPW + mi;                 // row tile of p: owner CTA = mt / nUT
         const int dest = mt >> ushift, ul = mt & (nUT - 1);
         float* dst = ((uint32_t)dest == crank ? rbuf : sbuf) + (size_t)dest * PSL + ul * 16 + gid;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int b0 = nt * 8 + 2 * tig;
-          dst[(size_t)b0 * PS] = acc[nt][0];
-          dst[(size_t)(b0 + 1) * PS] = acc[nt][1];
-          dst[(size_t)b0 * PS + 8] = acc[nt][2];
-          dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
+          dst[(size_t)b0 * PS] = acc[mi][nt][0];
+          dst[(size_t)(b0 + 1) * PS] = acc[mi][nt][1];
+          dst[(size_t)b0 * PS + 8] = acc[mi][nt][2];
+          dst[(size_t)(b0 + 1) * PS + 8] = acc[mi][nt][3];
         }
       }
       if (CS > 1) fence_proxy_async_smem();
@@ -452,7 +453,7 @@ __global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_bwd_kernel(const __
   for (int i = 0; i < IPT; ++i) {
     if (!it_ok[i]) continue;
     float rec[2] = {car[i][0][0], car[i][0][1]};
-    recurrent_sum(i, (T - 1) & 1, rec);
+    if (!p.grad_cut) recurrent_sum(i, (T - 1) & 1, rec);
     store_state2(p.ds0, s0_off[i], f32, rec[0], rec[1]);
 #pragma unroll
     for (int s = 1; s < S; ++s) store_state2(p.ds0, s0_off[i] + (size_t)s * B * ND, f32, car[i][s][0], car[i][s][1]);

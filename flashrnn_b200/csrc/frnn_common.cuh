@@ -7,7 +7,9 @@
 
 namespace frnn {
 
-enum { CELL_LSTM = 0, CELL_GRU = 1, CELL_ELMAN = 2, CELL_SLSTM = 3 };
+// 0..3 are the public cell ids of the C ABI.  CELL_ELMAN_CLIP is internal: Elman with forward_clip, whose backward
+// needs the tanh output from before the clamp and therefore caches it (plain Elman re-reads h and caches nothing).
+enum { CELL_LSTM = 0, CELL_GRU = 1, CELL_ELMAN = 2, CELL_SLSTM = 3, CELL_ELMAN_CLIP = 4 };
 
 // Gate / state counts per cell (reference registry flashrnn/flashrnn/flashrnn.py:49-71) plus what this
 // implementation caches for the backward pass and which states the backward has to re-read.
@@ -25,6 +27,10 @@ template <> struct Cell<CELL_GRU> {
 };
 template <> struct Cell<CELL_ELMAN> {
   static constexpr int Gr = 1, Gw = 1, Gt = 1, S = 1, GC = 0, NNEED = 1, NEXT = 1;
+  __host__ __device__ static constexpr int need(int) { return 0; }
+};
+template <> struct Cell<CELL_ELMAN_CLIP> {
+  static constexpr int Gr = 1, Gw = 1, Gt = 1, S = 1, GC = 1, NNEED = 1, NEXT = 1;
   __host__ __device__ static constexpr int need(int) { return 0; }
 };
 template <> struct Cell<CELL_SLSTM> {
@@ -54,6 +60,7 @@ struct LoopParams {
   int CS;                    // CTAs per cluster = D / U
   int state_f32;             // states / dstates / s0 / ds0 are fp32 (else bf16)
   float fclip, gclip;        // <= 0: off
+  int grad_cut;              // backward: ignore the matrix part of the recurrent cotangent (truncated BPTT)
 };
 
 // ------------------------------------------------------------------------------------------------ PTX
@@ -274,6 +281,63 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
     }
 }
 
+// Same product for MT row tiles that share the operand: out[m] = A_m (16 x 16*KP, fragments Areg[m*KP + k]) times the
+// contiguous tile `opnd[batch row][k]`.  The operand fragments are loaded once per k-step and reused by all MT tiles.
+template <int MT, int KP, int NT>
+__device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const __nv_bfloat16* opnd, int stride, int lane,
+                                               float (&out)[MT][NT][4]) {
+  constexpr int NACC = (MT * NT >= 4) ? 1 : (4 / (MT * NT));
+  float acc[NACC][MT][NT][4];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a)
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[a][m][nt][c] = 0.f;
+  const int j = lane >> 3, r = lane & 7;
+  if constexpr (NT == 1) {
+    const uint32_t base = smem_u32(opnd + r * stride + (j >> 1) * 16 + (j & 1) * 8);
+#pragma unroll
+    for (int k = 0; k < KP; k += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(base + (uint32_t)(k * 32), b0, b1, b2, b3);  // k-steps k and k+1 (the latter unused when KP is odd)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        mma_bf16_16816(acc[k % NACC][m][0], Areg[m * KP + k], b0, b1);
+        if (k + 1 < KP) mma_bf16_16816(acc[(k + 1) % NACC][m][0], Areg[m * KP + k + 1], b2, b3);
+      }
+    }
+  } else {
+    const uint32_t base = smem_u32(opnd + ((j >> 1) * 8 + r) * stride + (j & 1) * 8);
+#pragma unroll
+    for (int k = 0; k < KP; ++k) {
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(base + (uint32_t)((np * 16 * stride + k * 16) * 2), b0, b1, b2, b3);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          mma_bf16_16816(acc[k % NACC][m][2 * np], Areg[m * KP + k], b0, b1);
+          mma_bf16_16816(acc[k % NACC][m][2 * np + 1], Areg[m * KP + k], b2, b3);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float s = acc[0][m][nt][c];
+#pragma unroll
+        for (int a = 1; a < NACC; ++a) s += acc[a][m][nt][c];
+        out[m][nt][c] = s;
+      }
+}
+
 // Development aid (off in the shipped library): with -DFRNN_PROFILE thread 0 of CTA 0 sums the SM clock
 // between up to 7 marks of the step loop and leaves the 7 sums (u64) at byte 64 of the status block.
 #ifdef FRNN_PROFILE
@@ -293,5 +357,14 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
 
 // Threads per CTA the kernels are compiled for, by k-steps held in registers per warp.
 template <int KT> struct MaxThreads { static constexpr int v = (KT >= 12) ? 384 : 512; };
+// Launch bounds per (cell, KT): a CTA never has more than 2*Gr*D threads (U <= D).  No minimum-blocks hint: capping
+// the registers of the small-head kernels to raise occupancy (6 instead of 4 CTAs per SM) made the Elman D=64
+// backward 70 % slower on B200 (measured), so the compiler is left free.
+template <int CELL, int KT> struct LaunchBounds {
+  static constexpr int cap = MaxThreads<KT>::v;
+  static constexpr int full = 32 * Cell<CELL>::Gr * KT;
+  static constexpr int threads = full < cap ? full : cap;
+  static constexpr int min_blocks = 1;
+};
 
 }  // namespace frnn

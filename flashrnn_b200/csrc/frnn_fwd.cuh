@@ -43,8 +43,9 @@ __device__ __forceinline__ void cell_forward(const float* pre, const float* wx, 
     const float nv = fast_tanh(wx[2] + bias[3] + rg * gr);   // input-only gate n
     st[0] = zg * st[0] + (1.f - zg) * nv;
     cache[0] = gr; cache[1] = rg; cache[2] = zg; cache[3] = nv;
-  } else if constexpr (CELL == CELL_ELMAN) {
+  } else if constexpr (CELL == CELL_ELMAN || CELL == CELL_ELMAN_CLIP) {
     st[0] = fast_tanh(pre[0] + wx[0] + bias[0]);
+    if constexpr (CELL == CELL_ELMAN_CLIP) cache[0] = st[0];  // h is clamped afterwards: keep the tanh output
   } else {  // sLSTM; "m' = i~ when n == 0" is applied per element (fused/slstm_fused_pointwise.cuh:53-62)
     const float ir = pre[0] + wx[0] + bias[0];
     const float fr = pre[1] + wx[1] + bias[1];
@@ -74,7 +75,7 @@ __host__ __device__ constexpr size_t fwd_smem_bytes(int U, int threads) {
 }
 
 template <int CELL, int KT, int NT>
-__global__ void __launch_bounds__(MaxThreads<KT>::v, 1) frnn_fwd_kernel(const __grid_constant__ LoopParams p) {
+__global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<CELL, KT>::min_blocks) frnn_fwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC;
   constexpr int D = KT * 16, BT = NT * 8;

@@ -13,7 +13,7 @@ static LoopKernel make_entry() {
   LoopKernel k;
   k.fn = reinterpret_cast<const void*>(&frnn_bwd_kernel<FRNN_INST_CELL, KT, NT, MPW>);
   k.smem_bytes = [](int U, int threads) -> size_t { return bwd_smem_bytes<FRNN_INST_CELL, KT, NT, MPW>(U, threads); };
-  k.max_threads = MaxThreads<KT>::v;
+  k.max_threads = LaunchBounds<FRNN_INST_CELL, KT>::threads;
   return k;
 }
 // reduce-scatter variants exist only where the geometry works out (CS = MPW * Gr <= 8, U a power of two times 16)
@@ -43,7 +43,7 @@ static LoopKernel make_entry() {
   LoopKernel k;
   k.fn = reinterpret_cast<const void*>(&frnn_fwd_kernel<FRNN_INST_CELL, KT, NT>);
   k.smem_bytes = [](int U, int threads) -> size_t { return fwd_smem_bytes<FRNN_INST_CELL, KT, NT>(U, threads); };
-  k.max_threads = MaxThreads<KT>::v;
+  k.max_threads = LaunchBounds<FRNN_INST_CELL, KT>::threads;
   return k;
 }
 

@@ -154,7 +154,7 @@ class _FrnnFunction(torch.autograd.Function):
         b_k = b.to(torch.bfloat16).contiguous()
         s0_k = s0.to(state_dtype).contiguous()
         prob = _native.make_problem(cfg.function, B, T, N, D, state_dtype == torch.float32, training,
-                                    cfg.forward_clipval, cfg.gradient_recurrent_clipval)
+                                    cfg.forward_clipval, cfg.gradient_recurrent_clipval, cfg.gradient_recurrent_cut)
         plan = _native.query(prob, cfg.cluster_size, cfg.batch_tile)
         dev = Wx.device
         states = torch.empty((cfg.num_states, B, T, N, D), dtype=state_dtype, device=dev)
@@ -226,8 +226,6 @@ def flashrnn(
         raise ValueError(f"Unknown backend {config.backend}")
     if config.dtype != "bfloat16":
         raise NotImplementedError(f"dtype '{config.dtype}': the sm_100a kernels compute in bfloat16 with fp32 accumulation")
-    if config.gradient_recurrent_cut:
-        raise NotImplementedError("gradient_recurrent_cut is not implemented")
     if config.input_shape != "BTGHD" or config.output_shape != "SBTHD" or config.recurrent_shape != "GHDP" \
             or config.bias_shape != "GHD":
         raise NotImplementedError("only the default user layouts BTGHD / SBTHD / GHDP / GHD are implemented")

@@ -58,6 +58,7 @@ typedef struct frnn_problem {
   int32_t training;      /* 1: forward writes the activation cache for backward     */
   float forward_clip;    /* > 0: clamp the new h to [-v, v]   (forward_clipval)     */
   float grad_clip;       /* > 0: clamp the recurrent dh to [-v, v] (gradient_recurrent_clipval) */
+  int32_t grad_cut;      /* 1: drop the R^T delta term of dh_{t-1} in backward (gradient_recurrent_cut) */
 } frnn_problem;
 
 /* Launch plan chosen by frnn_query from the measured sm_100a tile table.  Replaces the reference's

@@ -55,7 +55,8 @@ def _prep(a, dtype):
     return np.ascontiguousarray(np.asarray(a, dtype=dtype))
 
 
-def oracle_forward(function, Wx, R, b, s0=None, dtype=np.float64, with_cache=False, slstm_global_rule=True):
+def oracle_forward(function, Wx, R, b, s0=None, dtype=np.float64, with_cache=False, slstm_global_rule=True,
+                   forward_clip=0.0):
     """Forward of the reference's ``vanilla`` loop.  Returns (states[S,B,T,N,D], last[S,B,1,N,D][, cache])."""
     lib = _load()
     Gr, Gw, Gt, S = _DIMS[function]
@@ -71,10 +72,10 @@ def oracle_forward(function, Wx, R, b, s0=None, dtype=np.float64, with_cache=Fal
     cache = np.empty((B, T, 5, N, D), dtype=dtype) if with_cache else None
     sfx = "f64" if dtype == np.float64 else "f32"
     fwd = getattr(lib, f"frnn_oracle_forward_{sfx}")
-    fwd.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 6 + [ctypes.c_int]
+    fwd.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 6 + [ctypes.c_int, ctypes.c_double]
     rc = fwd(
         CELLS[function], B, T, N, D, _ptr(Wx), _ptr(R), _ptr(b), _ptr(s0), _ptr(states), _ptr(cache),
-        1 if slstm_global_rule else 0)
+        1 if slstm_global_rule else 0, float(forward_clip))
     if rc != 0:
         raise RuntimeError(f"frnn_oracle_forward failed: {rc}")
     last = states[:, :, T - 1:T].copy() if T > 0 else s0.reshape(S, B, 1, N, D).copy()
@@ -82,7 +83,7 @@ def oracle_forward(function, Wx, R, b, s0=None, dtype=np.float64, with_cache=Fal
 
 
 def oracle_fwbw(function, Wx, R, b, s0=None, dstates=None, dlast=None, dtype=np.float64, clip=0.0,
-                slstm_global_rule=True):
+                slstm_global_rule=True, forward_clip=0.0, cut=False):
     """Forward + closed-form backward.
 
     ``dstates`` is the cotangent of ``states`` ([S,B,T,N,D]; default: ones on states[0], i.e. loss = sum(h));
@@ -93,7 +94,7 @@ def oracle_fwbw(function, Wx, R, b, s0=None, dstates=None, dlast=None, dtype=np.
     lib = _load()
     Gr, Gw, Gt, S = _DIMS[function]
     states, last, cache = oracle_forward(function, Wx, R, b, s0, dtype, with_cache=True,
-                                         slstm_global_rule=slstm_global_rule)
+                                         slstm_global_rule=slstm_global_rule, forward_clip=forward_clip)
     _, B, T, N, D = states.shape
     R = _prep(R, dtype)
     if s0 is None:
@@ -111,9 +112,9 @@ def oracle_fwbw(function, Wx, R, b, s0=None, dstates=None, dlast=None, dtype=np.
     ds0 = np.empty((S, B, N, D), dtype=dtype)
     sfx = "f64" if dtype == np.float64 else "f32"
     fn = getattr(lib, f"frnn_oracle_backward_{sfx}")
-    fn.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 9 + [ctypes.c_double]
+    fn.argtypes = [ctypes.c_int] * 5 + [ctypes.c_void_p] * 9 + [ctypes.c_double, ctypes.c_int]
     rc = fn(CELLS[function], B, T, N, D, _ptr(R), _ptr(s0), _ptr(states), _ptr(cache), _ptr(dstates),
-            _ptr(dWx), _ptr(dR), _ptr(db), _ptr(ds0), float(clip))
+            _ptr(dWx), _ptr(dR), _ptr(db), _ptr(ds0), float(clip), 1 if cut else 0)
     if rc != 0:
         raise RuntimeError(f"frnn_oracle_backward failed: {rc}")
     return dict(states=states, last=last, dWx=dWx, dR=dR, db=db, ds0=ds0.reshape(S, B, 1, N, D))

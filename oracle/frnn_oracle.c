@@ -112,10 +112,11 @@ HOT static void recurrent_backward(const REAL* R, int Gr, int N, int D, int n, c
  * Forward.  `slstm_global_rule` != 0 selects the vanilla backend's rule "m' = i~ iff ALL entries of n
  * (whole [B,N,D] tensor) are zero" (vanilla/slstm.py:21-24); 0 selects the per-element rule of the
  * reference's CUDA kernels.  For all-zero initial states the two agree.
- * `cache` may be NULL (inference).  Returns 0, or -1 on a bad cell id / allocation failure.
+ * `fclip` > 0 clamps every new h to [-fclip, fclip] (the reference's forward_clipval,
+ * flashrnn/flashrnn/fused/lstm_fused_pointwise.cuh:75-80).  `cache` may be NULL (inference).  Returns 0, or -1 on a bad cell id / allocation failure.
  */
 int FN(frnn_oracle_forward)(int cell, int B, int T, int N, int D, const REAL* Wx, const REAL* R, const REAL* b,
-                            const REAL* s0, REAL* states, REAL* cache, int slstm_global_rule) {
+                            const REAL* s0, REAL* states, REAL* cache, int slstm_global_rule, double fclip) {
   int Gr, Gw, Gt, S;
   if (cell_dims(cell, &Gr, &Gw, &Gt, &S)) return -1;
   const size_t ND = (size_t)N * D;
@@ -188,6 +189,11 @@ int FN(frnn_oracle_forward)(int cell, int B, int T, int N, int D, const REAL* Wx
             st[d] = hn; st[D + d] = cn; st[2 * D + d] = n2; st[3 * D + d] = mn;
           }
         }
+        if (fclip > 0)
+          for (int d = 0; d < D; ++d) {
+            if (st[d] > (REAL)fclip) st[d] = (REAL)fclip;
+            if (st[d] < (REAL)-fclip) st[d] = (REAL)-fclip;
+          }
         for (int s = 0; s < S; ++s)
           memcpy(states + (((size_t)s * B + bb) * T + t) * ND + (size_t)n * D, st + (size_t)s * D, sizeof(REAL) * D);
       }
@@ -202,11 +208,13 @@ int FN(frnn_oracle_forward)(int cell, int B, int T, int N, int D, const REAL* Wx
  * The sLSTM stabiliser m is treated as a constant (as in the reference's CUDA and manual-PyTorch
  * backward); this equals full autograd for cotangents that reach the loss through h only.
  * `clip` > 0 clamps the recurrent part of dh to [-clip, clip] before use (gradient_recurrent_clipval).
+ * `cut` != 0 drops the R^T delta term of dh_{t-1} (the reference's gradient_recurrent_cut,
+ * flashrnn/flashrnn/fused/flashrnn_fused_backward_cut.cu:89-178); dR is still formed from the deltas.
  * dR, db are overwritten (not accumulated into).
  */
 int FN(frnn_oracle_backward)(int cell, int B, int T, int N, int D, const REAL* R, const REAL* s0, const REAL* states,
                              const REAL* cache, const REAL* dstates, REAL* dWx, REAL* dR, REAL* db, REAL* ds0,
-                             double clip) {
+                             double clip, int cut) {
   int Gr, Gw, Gt, S;
   if (cell_dims(cell, &Gr, &Gw, &Gt, &S)) return -1;
   const size_t ND = (size_t)N * D;
@@ -280,7 +288,8 @@ int FN(frnn_oracle_backward)(int cell, int B, int T, int N, int D, const REAL* R
         }
         memset(dhn, 0, sizeof(REAL) * D);
         recurrent_backward(R, Gr, N, D, n, delta, hprev, dhn, dRn);
-        for (int d = 0; d < D; ++d) carry[d] += dhn[d];
+        if (!cut)
+          for (int d = 0; d < D; ++d) carry[d] += dhn[d];
       }
       for (int s = 0; s < S; ++s)
         for (int d = 0; d < D; ++d) ds0[((size_t)s * B + bb) * ND + (size_t)n * D + d] = carry[(size_t)s * D + d];

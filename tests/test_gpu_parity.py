@@ -78,6 +78,34 @@ def test_long_sequence_drift(cuda_device, function):
     assert_parity(function, got, ref, tag=function)
 
 
+@pytest.mark.parametrize("function", CELLS)
+def test_clip_options(cuda_device, function):
+    """forward_clipval clamps the new h; gradient_recurrent_clipval clamps the recurrent cotangent
+    (reference flashrnn.py:131-136).  The bounds are chosen so that both clamps bite."""
+    B, T, N, D = 8, 12, 2, 64
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=17)
+    got = run_native(function, Wx, R, b, s0, forward_clipval=0.5, gradient_recurrent_clipval=0.05)
+    ref = run_oracle(function, Wx, R, b, s0, forward_clip=0.5, clip=0.05)
+    unclipped = run_oracle(function, Wx, R, b, s0, forward_clip=0.5)
+    assert np.abs(ref["dWx"] - unclipped["dWx"]).max() > 1e-4  # the gradient clamp is active too
+    assert float(np.abs(got["states"][0]).max()) <= 0.5 + 1e-6
+    assert float(np.abs(ref["states"][0]).max()) == pytest.approx(0.5)  # the clamp is active in this case
+    assert_parity(function, got, ref, tag=function)
+
+
+@pytest.mark.parametrize("function", CELLS)
+def test_gradient_recurrent_cut(cuda_device, function):
+    """gradient_recurrent_cut drops the R^T delta term of the backward recurrence (truncated BPTT of depth 1,
+    reference fused/flashrnn_fused_backward_cut.cu:89-178); dR/db are still formed from the deltas."""
+    B, T, N, D = 8, 10, 2, 64
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=19, random_init=True)
+    got = run_native(function, Wx, R, b, s0, gradient_recurrent_cut=True)
+    ref = run_oracle(function, Wx, R, b, s0, cut=True)
+    full = run_oracle(function, Wx, R, b, s0)
+    assert np.abs(ref["dWx"] - full["dWx"]).max() > 1e-3  # the option changes the gradients
+    assert_parity(function, got, ref, tag=function, zero_init=False)
+
+
 def test_deterministic_forward(cuda_device):
     """Two runs give bit-identical states (no race in the h exchange)."""
     from flashrnn_b200 import flashrnn

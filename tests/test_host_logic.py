@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_struct_sizes_match_header():
     # int32 x 8 + float x 2; plan = 4 + 40 + 6*4 + 6*4 (reserved) padded to 8 + 4 * 8
-    assert ctypes.sizeof(_native.FrnnProblem) == 40
+    assert ctypes.sizeof(_native.FrnnProblem) == 44
     assert ctypes.sizeof(_native.FrnnPlan) == 128
     assert ctypes.sizeof(_native.FrnnFwdArgs) == 7 * 8 and ctypes.sizeof(_native.FrnnBwdArgs) == 8 * 8
 

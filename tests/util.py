@@ -74,10 +74,10 @@ def run_native(function, Wx, R, b, s0, cot=None, state_f32=False, device="cuda",
     return dict(states=f(states), last=f(last), dWx=f(Wx_d.grad), dR=f(R_d.grad), db=f(b_d.grad), ds0=f(s_d.grad))
 
 
-def run_oracle(function, Wx, R, b, s0, cot=None, clip=0.0):
+def run_oracle(function, Wx, R, b, s0, cot=None, clip=0.0, forward_clip=0.0, cut=False):
     return oracle_fwbw(function, Wx.numpy(), R.numpy(), b.numpy(), s0.numpy(),
                        dstates=None if cot is None else cot.numpy(), dtype=np.float64, clip=clip,
-                       slstm_global_rule=False)
+                       slstm_global_rule=False, forward_clip=forward_clip, cut=cut)
 
 
 def assert_parity(function, got, ref, check_ds0=True, tag="", zero_init=True):
