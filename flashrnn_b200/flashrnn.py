@@ -111,10 +111,20 @@ class FlashRNNConfig:
         return DTYPE_DICT[self.dtype_s]
 
 
-def _zero_state(config: FlashRNNConfig, inp: torch.Tensor) -> torch.Tensor:
-    """Initial states [S,B,1,N,D] filled with ``initial_val``, in the dtype/device of ``inp``
-    (reference flashrnn.py:927-954)."""
-    B = inp.shape[config.input_shape.index("B")]
+def _to_layout(x: torch.Tensor, src: str, dst: str) -> torch.Tensor:
+    """View of ``x`` with its dimensions reordered from layout string ``src`` to ``dst`` (e.g. "TBGHD" -> "BTGHD")."""
+    if src == dst:
+        return x
+    if sorted(src) != sorted(dst) or len(set(src)) != len(src):
+        raise ValueError(f"layout '{src}' is not a permutation of '{dst}'")
+    return x.permute(tuple(src.index(c) for c in dst))
+
+
+def _zero_state(config: FlashRNNConfig, inp: torch.Tensor, batch: Optional[int] = None) -> torch.Tensor:
+    """Initial states filled with ``initial_val`` in the dtype/device of ``inp``: [S,B,1,N,D] reordered to
+    ``config.output_shape`` (reference flashrnn.py:927-954).  ``inp`` is in ``config.input_shape`` unless ``batch``
+    is given."""
+    B = batch if batch is not None else inp.shape[config.input_shape.index("B")]
     state = torch.zeros((config.num_states, B, 1, config.num_heads, config.head_dim), dtype=inp.dtype, device=inp.device)
     if isinstance(config.initial_val, (int, float)):
         if config.initial_val != 0.0:
@@ -122,7 +132,7 @@ def _zero_state(config: FlashRNNConfig, inp: torch.Tensor) -> torch.Tensor:
     else:
         for i in range(config.num_states):
             state[i] += config.initial_val[i]
-    return state
+    return _to_layout(state, "SBTHD", config.output_shape)
 
 
 def _get_config(Wx, R, b, function, backend, dtype) -> FlashRNNConfig:
@@ -226,23 +236,31 @@ def flashrnn(
         raise ValueError(f"Unknown backend {config.backend}")
     if config.dtype != "bfloat16":
         raise NotImplementedError(f"dtype '{config.dtype}': the sm_100a kernels compute in bfloat16 with fp32 accumulation")
-    if config.input_shape != "BTGHD" or config.output_shape != "SBTHD" or config.recurrent_shape != "GHDP" \
-            or config.bias_shape != "GHD":
-        raise NotImplementedError("only the default user layouts BTGHD / SBTHD / GHDP / GHD are implemented")
     if not Wx.is_cuda:
         raise RuntimeError("flashrnn_b200 runs on CUDA tensors only; there is no CPU fallback")
     if Wx.dim() != 5 or R.dim() != 4 or b.dim() != 3:
         raise ValueError("expected Wx[B,T,G,N,D], R[G,N,D,D], b[G,N,D]")
+    # other user layouts (reference flashrnn.py:165-173) are views of the native one; the kernels consume
+    # BTGHD / GHDP / GHD / SBTHD, so a non-default layout costs one copy of that tensor
+    Wx = _to_layout(Wx, config.input_shape, "BTGHD")
+    R = _to_layout(R, config.recurrent_shape, "GHDP")
+    b = _to_layout(b, config.bias_shape, "GHD")
+    if states is not None:
+        if states.dim() != 5:
+            raise ValueError("states must have 5 dimensions (S, B, 1, N, D in the order of output_shape)")
+        states = _to_layout(states, config.output_shape, "SBTHD")
     B, T, Gw, N, D = Wx.shape
     if Gw != config.num_gates_w or tuple(R.shape) != (config.num_gates_r, N, D, D) or tuple(b.shape) != (config.num_gates_t, N, D):
         raise ValueError(f"shape mismatch for function '{config.function}': Wx{tuple(Wx.shape)} R{tuple(R.shape)} b{tuple(b.shape)}")
     if states is None:
-        states = _zero_state(config, Wx).to(config.torch_dtype_s)
+        states = _to_layout(_zero_state(config, Wx, batch=B), config.output_shape, "SBTHD").to(config.torch_dtype_s)
     if tuple(states.shape) != (config.num_states, B, 1, N, D):
         raise ValueError(f"states must be [S,B,1,N,D] = {(config.num_states, B, 1, N, D)}, got {tuple(states.shape)}")
     if T == 0:
         out = torch.empty((config.num_states, B, 0, N, D), dtype=config.torch_dtype_s, device=Wx.device)
-        return out, states.to(config.torch_dtype_s)
+        return (_to_layout(out, "SBTHD", config.output_shape),
+                _to_layout(states.to(config.torch_dtype_s), "SBTHD", config.output_shape))
     training = torch.is_grad_enabled() and any(t.requires_grad for t in (Wx, R, b, states))
     all_states = _FrnnFunction.apply(Wx, R, b, states, config, training, grad_allreduce_group)
-    return all_states, all_states[:, :, -1:]
+    return (_to_layout(all_states, "SBTHD", config.output_shape),
+            _to_layout(all_states[:, :, -1:], "SBTHD", config.output_shape))

@@ -106,6 +106,29 @@ def test_gradient_recurrent_cut(cuda_device, function):
     assert_parity(function, got, ref, tag=function, zero_init=False)
 
 
+def test_alternative_user_layouts(cuda_device):
+    """input_shape / recurrent_shape / bias_shape / output_shape other than the defaults (reference flashrnn.py:165-173)
+    give the same numbers, delivered in the requested layouts, gradients included."""
+    from flashrnn_b200 import FlashRNNConfig, flashrnn
+
+    B, T, N, D = 4, 6, 2, 64
+    Wx, R, b, s0 = (t.to("cuda", torch.bfloat16) for t in make_inputs("lstm", B, T, N, D, seed=23, random_init=True))
+    base = [t.clone().requires_grad_(True) for t in (Wx, R, b, s0)]
+    ref_states, ref_last = flashrnn(*base[:3], base[3], function="lstm")
+    ref_states[0].float().sum().backward()
+    cfg = FlashRNNConfig(function="lstm", head_dim=D, num_heads=N, batch_size=B, input_shape="TBGHD",
+                         recurrent_shape="HGDP", bias_shape="HGD", output_shape="STBHD")
+    alt = [Wx.permute(1, 0, 2, 3, 4).contiguous().requires_grad_(True), R.permute(1, 0, 2, 3).contiguous().requires_grad_(True),
+           b.permute(1, 0, 2).contiguous().requires_grad_(True), s0.permute(0, 2, 1, 3, 4).contiguous().requires_grad_(True)]
+    states, last = flashrnn(alt[0], alt[1], alt[2], alt[3], function="lstm", config=cfg)
+    assert states.shape == (2, T, B, N, D) and last.shape == (2, 1, B, N, D)
+    assert torch.equal(states.permute(0, 2, 1, 3, 4), ref_states) and torch.equal(last.permute(0, 2, 1, 3, 4), ref_last)
+    states[0].float().sum().backward()
+    assert torch.equal(alt[0].grad.permute(1, 0, 2, 3, 4), base[0].grad)
+    assert torch.allclose(alt[1].grad.permute(1, 0, 2, 3).float(), base[1].grad.float(), atol=1e-2, rtol=1e-2)
+    assert torch.allclose(alt[2].grad.permute(1, 0, 2).float(), base[2].grad.float(), atol=1e-2, rtol=1e-2)
+
+
 def test_deterministic_forward(cuda_device):
     """Two runs give bit-identical states (no race in the h exchange)."""
     from flashrnn_b200 import flashrnn
