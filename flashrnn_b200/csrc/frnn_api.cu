@@ -66,11 +66,15 @@ static WsLayout workspace_layout(const frnn_problem& pr, const CellDims& cd) {
 
 // Backward exchange scheme of a tile: reduce-scatter (returns MPW = CS / Gr) where that kernel exists and fits,
 // else all-gather (0).
+// head dims above 256 take the streamed kernels (lookup key kt = 0)
+static bool streamed(const frnn_problem& pr) { return pr.D > 256; }
+static int kernel_kt(const frnn_problem& pr) { return streamed(pr) ? 0 : pr.D / 16; }
+
 static int bwd_mpw(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
-  if (cs <= 1 || cs % cd.Gr) return 0;
+  if (streamed(pr) || cs <= 1 || cs % cd.Gr) return 0;
   const int U = pr.D / cs, threads = 2 * cd.Gr * U, mpw = cs / cd.Gr;
-  const LoopKernel k = get_bwd_kernel(kernel_cell(pr),pr.D / 16, bt / 8, mpw);
-  if (!k.fn || threads > k.max_threads || k.smem_bytes(U, threads) > kMaxDynSmem) return 0;
+  const LoopKernel k = get_bwd_kernel(kernel_cell(pr), pr.D / 16, bt / 8, mpw);
+  if (!k.fn || threads > k.max_threads || k.smem_bytes(pr.D, U, threads) > kMaxDynSmem) return 0;
   return mpw;
 }
 
@@ -78,15 +82,16 @@ static int bwd_mpw(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
 // instantiation's thread bound and the shared-memory budget.
 static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
   const int D = pr.D;
-  if (cs < 1 || cs > 8 || D % cs) return false;
+  if (cs < 1 || D % cs) return false;
+  if (streamed(pr) ? (cs > 16 || D / cs != kStreamU) : cs > 8) return false;
   const int U = D / cs;
   if (U % 16 || ((U / 16) & (U / 16 - 1))) return false;  // 16 * power of two
   if (bt != 8 && bt != 16 && bt != 32) return false;
-  const int kt = D / 16, nt = bt / 8, threads = 2 * cd.Gr * U;
-  const LoopKernel f = get_fwd_kernel(kernel_cell(pr),kt, nt), b = get_bwd_kernel(kernel_cell(pr),kt, nt, 0);
+  const int kt = kernel_kt(pr), nt = bt / 8, threads = 2 * cd.Gr * U;
+  const LoopKernel f = get_fwd_kernel(kernel_cell(pr), kt, nt), b = get_bwd_kernel(kernel_cell(pr), kt, nt, 0);
   if (!f.fn || !b.fn) return false;
   if (threads > f.max_threads || threads > b.max_threads || threads < 32) return false;
-  if (f.smem_bytes(U, threads) > kMaxDynSmem || b.smem_bytes(U, threads) > kMaxDynSmem) return false;
+  if (f.smem_bytes(D, U, threads) > kMaxDynSmem || b.smem_bytes(D, U, threads) > kMaxDynSmem) return false;
   return true;
 }
 
@@ -104,9 +109,10 @@ static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs,
     const int order_small[8] = {8, 4, 2, 1, 6, 3, 7, 5};
     const int order_large[8] = {1, 2, 4, 8, 3, 6, 5, 7};
     for (int ci = 0; ci < 8; ++ci) {
-      const int cs = want_cs ? want_cs : (fill ? order_large[ci] : order_small[ci]);
+      int cs = want_cs ? want_cs : (fill ? order_large[ci] : order_small[ci]);
+      if (streamed(pr) && !want_cs) cs = pr.D / kStreamU;  // the streamed kernels have one geometry
       if (tile_ok(pr, cd, cs, bt)) { *cs_out = cs; *bt_out = bt; return true; }
-      if (want_cs) break;
+      if (want_cs || streamed(pr)) break;
     }
     if (want_bt) break;
   }
@@ -121,7 +127,7 @@ static int validate_problem(const frnn_problem* pr, CellDims* cd) {
   if (pr->B < 1 || pr->T < 1 || pr->N < 1 || pr->D < 1) return FRNN_ERR_SHAPE;
   if (pr->N > 65535) return FRNN_ERR_SHAPE;
   if (pr->D % 16) return FRNN_ERR_SHAPE;
-  bool kt_ok = false;
+  bool kt_ok = pr->D > 256 && pr->D <= kStreamMaxD && pr->D % kStreamU == 0;  // streamed kernels
   for (int i = 0; i < kNumKT; ++i) kt_ok = kt_ok || (kKTs[i] * 16 == pr->D);
   if (!kt_ok) return FRNN_ERR_SHAPE;
   return FRNN_OK;
@@ -172,9 +178,13 @@ static int check_plan(const frnn_plan* pl, CellDims* cd) {
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static cudaError_t launch_loop(const LoopKernel& k, const frnn_plan& pl, const LoopParams& lp, cudaStream_t stream) {
-  const size_t smem = k.smem_bytes(pl.units_per_cta, pl.threads);
+  const size_t smem = k.smem_bytes(pl.prob.D, pl.units_per_cta, pl.threads);
   cudaError_t e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
+  if (pl.cluster_size > 8) {  // clusters of more than 8 CTAs are a non-portable size: opt in
+    e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) return e;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)pl.cluster_size, (unsigned)((pl.prob.B + pl.batch_tile - 1) / pl.batch_tile), (unsigned)pl.prob.N);
   cfg.blockDim = dim3((unsigned)pl.threads, 1, 1);
@@ -250,7 +260,7 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
-  const LoopKernel k = get_fwd_kernel(kernel_cell(pr),pr.D / 16, plan->batch_tile / 8);
+  const LoopKernel k = get_fwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8);
   e = launch_loop(k, *plan, lp, stream);
   return (int)e;
 }
@@ -302,14 +312,15 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
   if (parts & FRNN_PART_LOOP) {
-    const LoopKernel k = get_bwd_kernel(kernel_cell(pr),pr.D / 16, plan->batch_tile / 8,
+    const LoopKernel k = get_bwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8,
                                         bwd_mpw(pr, cd, plan->cluster_size, plan->batch_tile));
     e = launch_loop(k, *plan, lp, stream);
     if (e != cudaSuccess) return (int)e;
   }
   // measured on B200: the tcgen05 kernel wins from head_dim 128 up (C2 0.167 vs 0.212 ms, C3 0.263 vs 0.304 ms); below,
   // the problem is HBM-bound and the warp-MMA kernel with its many small CTAs streams faster (C5 1.55 vs 3.1 ms)
-  if ((parts & FRNN_PART_DR) && pr.D >= 128)
+  // (the tcgen05 kernel keeps a whole row tile of dR, N = D <= 256 columns, in one TMEM allocation)
+  if ((parts & FRNN_PART_DR) && pr.D >= 128 && pr.D <= 256)
     e = launch_recurrent_grad_tc(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
                                  a->s0, grads, reinterpret_cast<unsigned*>(ws), sm_count_cached(), stream);
   else if (parts & FRNN_PART_DR)
@@ -341,7 +352,7 @@ const char* frnn_status_string(int code) {
     case FRNN_OK: return "ok";
     case FRNN_ERR_NULL: return "frnn: a required pointer is NULL";
     case FRNN_ERR_CELL: return "frnn: unknown cell (expected lstm, gru, elman or slstm)";
-    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256})";
+    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256} or a multiple of 64 up to 1024)";
     case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b must be bfloat16; states bfloat16 or float32)";
     case FRNN_ERR_ALIGN: return "frnn: tensor pointers must be 16-byte aligned";
     case FRNN_ERR_PLAN: return "frnn: invalid plan or tile for this problem";

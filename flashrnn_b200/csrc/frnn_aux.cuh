@@ -11,10 +11,16 @@ constexpr int kKTs[kNumKT] = {2, 4, 6, 8, 12, 16};
 constexpr int kNumNT = 3;
 constexpr int kNTs[kNumNT] = {1, 2, 4};
 
+// head dims above 256 (multiples of 64 up to kStreamMaxD) run the streamed kernels: kStreamKT k-steps of R per warp
+// in registers, U = kStreamU units per CTA, cluster size D / kStreamU (up to 16, non-portable above 8)
+constexpr int kStreamKT = 8;
+constexpr int kStreamU = 64;
+constexpr int kStreamMaxD = 1024;
+
 struct LoopKernel {
   const void* fn;      // kernel entry
   int max_threads;     // __launch_bounds__ of the instantiation
-  size_t (*smem_bytes)(int U, int threads);
+  size_t (*smem_bytes)(int D, int U, int threads);
 };
 
 // defined once per (cell, direction) in frnn_inst_*.cu; returns fn == nullptr when not instantiated

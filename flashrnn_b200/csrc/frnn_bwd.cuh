@@ -96,24 +96,30 @@ template <int CELL, int KT, int MPW> struct RsGeom {
                                 (NUT & (NUT - 1)) == 0 && CS <= 8 && CS * U == KT * 16;
 };
 
-template <int CELL, int KT, int NT, int MPW>
-__host__ __device__ constexpr size_t bwd_smem_bytes(int U, int threads) {
+template <int CELL, int NT, int MPW>
+__host__ __device__ constexpr size_t bwd_smem_bytes(int D, int U, int threads) {
   using C = Cell<CELL>;
-  constexpr int D = KT * 16, BT = NT * 8;
+  constexpr int BT = NT * 8;
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
   constexpr int GCA = C::GC > 0 ? C::GC : 1;
   const int CS = D / U;
-  const size_t rings = (size_t)kStages * GCA * IPT * threads * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * threads * 8 + 16;
+  const size_t rl = ring_row_len(U, BT, threads);
+  const size_t rings = (size_t)kStages * GCA * IPT * rl * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * rl * 8 + 16;
   if (MPW > 0)  // delta tile + double-buffered send and receive slices of fp32 partials
     return (size_t)BT * (C::Gr * U + 8) * 2 + (size_t)4 * CS * BT * (U + 4) * 4 + rings;
   return (size_t)2 * CS * BT * (C::Gr * U + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 + rings;
 }
 
-template <int CELL, int KT, int NT, int MPW>
+// KT / DYN as in the forward kernel: KT k-steps of R^T per warp stay in registers; with DYN the head dim is a run-time
+// value above 256 and the remaining k-steps are streamed from global memory every step (all-gather form only).
+template <int CELL, int KT, int NT, int MPW, bool DYN>
 __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<CELL, KT>::min_blocks) frnn_bwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
+  static_assert(!(DYN && MPW > 0), "the streamed form exists for the all-gather exchange only");
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, NNEED = C::NNEED, NEXT = C::NEXT;
-  constexpr int D = KT * 16, BT = NT * 8;
+  constexpr int BT = NT * 8;
+  const int D = DYN ? p.D : KT * 16;
+  const int ktot = DYN ? (p.D >> 4) : KT;  // k-steps per gate in a row of R^T
   constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);
   constexpr int GCA = GC > 0 ? GC : 1;
   constexpr int NSS = NNEED + NEXT;  // 8-byte slots per item and stage in the state ring
@@ -142,12 +148,14 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   float* stage_buf = part;                                  // RS only
   float* recv_buf = part + (size_t)2 * CS * PSL;            // RS only
   uint32_t* ringc = reinterpret_cast<uint32_t*>(part + (RS ? (size_t)4 * CS * PSL : (size_t)Gr * BT * PS));  // [kStages][GCA][IPT][nthr]
-  uint2* rings = reinterpret_cast<uint2*>(ringc + (size_t)kStages * GCA * IPT * nthr);    // [kStages][NSS][IPT][nthr]
-  uint64_t* full = reinterpret_cast<uint64_t*>(rings + (size_t)kStages * NSS * IPT * nthr);  // [2]
+  const int RL = ring_row_len(U, BT, nthr);  // threads that own items: the rings have one slot row per such thread
+  uint2* rings = reinterpret_cast<uint2*>(ringc + (size_t)kStages * GCA * IPT * RL);    // [kStages][NSS][IPT][RL]
+  uint64_t* full = reinterpret_cast<uint64_t*>(rings + (size_t)kStages * NSS * IPT * RL);  // [2]
 
   // ---- this warp's fragments of R^T (rows p, columns = gate rows), resident for the whole sequence
   const int g_w = warp / nUT, ug_w = warp - g_w * nUT;  // all-gather: gate / unit tile of this warp
   uint4 Rreg[KT];
+  const uint4* rsrc = p.Rpack + ((((size_t)n * Gr + g_w) * ktot + (unit0 / 16 + ug_w)) * ktot) * 32 + lane;  // all-gather row
   if constexpr (RS) {
     // rows p: tiles warp*MPW + mi (all D rows are covered by the CTA's warps); columns: the CTA's own (g, u)
 #pragma unroll
@@ -155,12 +163,11 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
 #pragma unroll
       for (int ks = 0; ks < KPW; ++ks) {
         const int g = ks / nUT, ul = ks - g * nUT;
-        Rreg[mi * KPW + ks] = __ldg(p.Rpack + ((((size_t)n * Gr + g) * (D / 16) + (warp * MPW + mi)) * KT + (unit0 / 16 + ul)) * 32 + lane);
+        Rreg[mi * KPW + ks] = __ldg(p.Rpack + ((((size_t)n * Gr + g) * ktot + (warp * MPW + mi)) * ktot + (unit0 / 16 + ul)) * 32 + lane);
       }
   } else {
-    const uint4* src = p.Rpack + ((((size_t)n * Gr + g_w) * (D / 16) + (unit0 / 16 + ug_w)) * KT) * 32 + lane;
 #pragma unroll
-    for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(src + k * 32);
+    for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(rsrc + k * 32);
   }
 
   // ---- items
@@ -221,18 +228,18 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         if (!it_ok[i]) continue;
 #pragma unroll
         for (int k = 0; k < GC; ++k)
-          cp_async4(ringc + ((size_t)(stage * GCA + k) * IPT + i) * nthr + tid, ch_pf[i] + (size_t)k * nitems);
+          cp_async4(ringc + ((size_t)(stage * GCA + k) * IPT + i) * RL + tid, ch_pf[i] + (size_t)k * nitems);
         ch_pf[i] -= ch_step;
 #pragma unroll
         for (int k = 0; k < NNEED; ++k) {  // state at t-1 (initial state for t == 0)
-          uint2* dst = rings + ((size_t)(stage * NSS + k) * IPT + i) * nthr + tid;
+          uint2* dst = rings + ((size_t)(stage * NSS + k) * IPT + i) * RL + tid;
           const unsigned char* src = (t > 0) ? st_pf[i] + (size_t)C::need(k) * st_sstride
                                              : s0_it[i] + (size_t)C::need(k) * B * ND * st_esz;
           if (f32) cp_async8(dst, src); else cp_async4(dst, src);
         }
 #pragma unroll
         for (int k = 0; k < NEXT; ++k) {  // external cotangent of state k at t
-          uint2* dst = rings + ((size_t)(stage * NSS + NNEED + k) * IPT + i) * nthr + tid;
+          uint2* dst = rings + ((size_t)(stage * NSS + NNEED + k) * IPT + i) * RL + tid;
           const unsigned char* src = ds_pf[i] + (size_t)k * st_sstride;
           if (f32) cp_async8(dst, src); else cp_async4(dst, src);
         }
@@ -244,12 +251,12 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   };
 #pragma unroll
   for (int i = 0; i < IPT; ++i)
-    if (!it_ok[i])
+    if (it_on[i] && !it_ok[i])  // rows beyond B: their inputs read as zero
       for (int s = 0; s < kStages; ++s) {
 #pragma unroll
-        for (int k = 0; k < GCA; ++k) ringc[((size_t)(s * GCA + k) * IPT + i) * nthr + tid] = 0u;
+        for (int k = 0; k < GCA; ++k) ringc[((size_t)(s * GCA + k) * IPT + i) * RL + tid] = 0u;
 #pragma unroll
-        for (int k = 0; k < NSS; ++k) rings[((size_t)(s * NSS + k) * IPT + i) * nthr + tid] = make_uint2(0u, 0u);
+        for (int k = 0; k < NSS; ++k) rings[((size_t)(s * NSS + k) * IPT + i) * RL + tid] = make_uint2(0u, 0u);
       }
 #pragma unroll
   for (int s = 0; s < kStages; ++s) issue(T - 1 - s, s);
@@ -273,7 +280,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   }
   const uint32_t full_u32 = smem_u32(&full[0]);
   auto ring_state = [&](int stage, int slot, int i) -> float2 {
-    const uint2 w = rings[((size_t)(stage * NSS + slot) * IPT + i) * nthr + tid];
+    const uint2 w = rings[((size_t)(stage * NSS + slot) * IPT + i) * RL + tid];
     if (f32) return make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
     return unpack_bf16x2(w.x);
   };
@@ -326,7 +333,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       for (int k = 0; k < NEXT; ++k) { const float2 v = ring_state(stage, NNEED + k, i); extv[k][0] = v.x; extv[k][1] = v.y; }
 #pragma unroll
       for (int k = 0; k < GC; ++k) {
-        const float2 v = unpack_bf16x2(ringc[((size_t)(stage * GCA + k) * IPT + i) * nthr + tid]);
+        const float2 v = unpack_bf16x2(ringc[((size_t)(stage * GCA + k) * IPT + i) * RL + tid]);
         chv[k][0] = v.x; chv[k][1] = v.y;
       }
       float dRv[2][Gr];
@@ -429,6 +436,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       // ---------------- phase A (all-gather): part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
       float acc[NT][4];
       warp_mma_rows<KT, NT>(Rreg, dgbuf + (size_t)buf * CS * SL, GS, g_w * U, ushift, SL, lane, acc);
+      if constexpr (DYN) warp_mma_stream<NT>(rsrc, KT, ktot, dgbuf + (size_t)buf * CS * SL, GS, g_w * U, ushift, SL, lane, acc);
       const int gid = lane >> 2, tig = lane & 3;
       float* dst = part + (size_t)g_w * BT * PS + ug_w * 16 + gid;
 #pragma unroll

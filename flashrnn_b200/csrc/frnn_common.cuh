@@ -281,6 +281,42 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
     }
 }
 
+// Continues such a product over the k-steps [k0, k1) whose A fragments do not fit the register file and are streamed
+// from global memory every time step (head dims above 256): fragment k of this warp's row tile sits at asrc[k * 32]
+// (lane offset already applied).  Accumulates into `acc`.  k1 - k0 must be even.
+template <int NT>
+__device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k1, const __nv_bfloat16* opnd, int stride,
+                                                int kofs, int ushift, int slice_elems, int lane, float (&acc)[NT][4]) {
+  const int j = lane >> 3, r = lane & 7;
+  const int kmask = (1 << ushift) - 1;
+  if constexpr (NT == 1) {
+    const uint32_t base = smem_u32(opnd + r * stride + kofs + (j & 1) * 8);
+#pragma unroll 2
+    for (int k = k0; k < k1; k += 2) {
+      const uint4 a0 = __ldg(asrc + (size_t)k * 32), a1 = __ldg(asrc + (size_t)(k + 1) * 32);
+      uint32_t b0, b1, b2, b3;
+      const int kk = k + (j >> 1);
+      ldmatrix_x4(base + (uint32_t)(((kk >> ushift) * slice_elems + (kk & kmask) * 16) * 2), b0, b1, b2, b3);
+      mma_bf16_16816(acc[0], a0, b0, b1);
+      mma_bf16_16816(acc[0], a1, b2, b3);
+    }
+  } else {
+    const uint32_t base = smem_u32(opnd + ((j >> 1) * 8 + r) * stride + kofs + (j & 1) * 8);
+#pragma unroll 2
+    for (int k = k0; k < k1; ++k) {
+      const uint4 a = __ldg(asrc + (size_t)k * 32);
+      const uint32_t koff = (uint32_t)(((k >> ushift) * slice_elems + (k & kmask) * 16) * 2);
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldmatrix_x4(base + koff + (uint32_t)(np * 16 * stride * 2), b0, b1, b2, b3);
+        mma_bf16_16816(acc[2 * np], a, b0, b1);
+        mma_bf16_16816(acc[2 * np + 1], a, b2, b3);
+      }
+    }
+  }
+}
+
 // Same product for MT row tiles that share the operand: out[m] = A_m (16 x 16*KP, fragments Areg[m*KP + k]) times the
 // contiguous tile `opnd[batch row][k]`.  The operand fragments are loaded once per k-step and reused by all MT tiles.
 template <int MT, int KP, int NT>
@@ -356,6 +392,12 @@ __device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const __nv_bfl
 #endif
 
 // Threads per CTA the kernels are compiled for, by k-steps held in registers per warp.
+// Slot rows of the per-thread prefetch rings: threads beyond the item count of the CTA own no items and no slots
+// (8-row batch tiles of the 4-gate cells keep only every second thread busy in the pointwise phase).
+__host__ __device__ constexpr int ring_row_len(int U, int BT, int threads) {
+  return (U / 2) * BT < threads ? (U / 2) * BT : threads;
+}
+
 template <int KT> struct MaxThreads { static constexpr int v = (KT >= 12) ? 384 : 512; };
 // Launch bounds per (cell, KT): a CTA never has more than 2*Gr*D threads (U <= D).  No minimum-blocks hint: capping
 // the registers of the small-head kernels to raise occupancy (6 instead of 4 CTAs per SM) made the Elman D=64

@@ -64,21 +64,26 @@ __device__ __forceinline__ void cell_forward(const float* pre, const float* wx, 
 }
 
 // dynamic shared memory of the forward kernel, in bytes
-template <int CELL, int KT, int NT>
-__host__ __device__ constexpr size_t fwd_smem_bytes(int U, int threads) {
+template <int CELL, int NT>
+__host__ __device__ constexpr size_t fwd_smem_bytes(int D, int U, int threads) {
   using C = Cell<CELL>;
-  constexpr int D = KT * 16, BT = NT * 8;
+  constexpr int BT = NT * 8;
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
   const int CS = D / U;
   return (size_t)2 * CS * BT * (U + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
-         (size_t)kStages * C::Gw * IPT * threads * 4 + 16;
+         (size_t)kStages * C::Gw * IPT * ring_row_len(U, BT, threads) * 4 + 16;
 }
 
-template <int CELL, int KT, int NT>
+// KT = k-steps (16 columns of R each) a warp keeps in registers.  DYN == false: that is the whole row, D = 16 * KT.
+// DYN == true (head dims above 256): D is a run-time value and the k-steps beyond KT are streamed from global memory
+// (L2) in every time step -- R no longer fits the registers of one cluster.
+template <int CELL, int KT, int NT, bool DYN>
 __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<CELL, KT>::min_blocks) frnn_fwd_kernel(const __grid_constant__ LoopParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC;
-  constexpr int D = KT * 16, BT = NT * 8;
+  constexpr int BT = NT * 8;
+  const int D = DYN ? p.D : KT * 16;
+  const int ktot = DYN ? (p.D >> 4) : KT;  // k-steps per row of R
   constexpr int IPT = (BT + 4 * Gr - 1) / (4 * Gr);  // items (unit pair x batch row) per thread
   constexpr int GCA = GC > 0 ? GC : 1;
 
@@ -97,18 +102,17 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* hbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                   // [2][CS][BT][US]
   float* pre = reinterpret_cast<float*>(smem_raw + (size_t)2 * CS * SL * 2);          // [BT][PS]
-  uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);                // [kStages][Gw][IPT][nthr]
-  uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)kStages * Gw * IPT * nthr);  // [2]
+  const int RL = ring_row_len(U, BT, nthr);  // threads that own items: the ring has one slot row per such thread
+  uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);                // [kStages][Gw][IPT][RL]
+  uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)kStages * Gw * IPT * RL);  // [2]
 
   // ---- this warp's slice of R: gate g_w of units [unit0 + 16*ug_w, +16), all D inputs, as A fragments
   const int nUT = U >> 4;
   const int g_w = warp / nUT, ug_w = warp - g_w * nUT;
   uint4 Rreg[KT];
-  {
-    const uint4* src = p.Rpack + ((((size_t)n * Gr + g_w) * (D / 16) + (unit0 / 16 + ug_w)) * KT) * 32 + lane;
+  const uint4* rsrc = p.Rpack + ((((size_t)n * Gr + g_w) * ktot + (unit0 / 16 + ug_w)) * ktot) * 32 + lane;
 #pragma unroll
-    for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(src + k * 32);
-  }
+  for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(rsrc + k * 32);
 
   // ---- this thread's items: everything that does not change over time is computed once
   const int half_u = U >> 1, nitems = half_u * BT;
@@ -166,7 +170,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         if (it_ok[i]) {
 #pragma unroll
           for (int g = 0; g < Gw; ++g)
-            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * nthr + tid, wx_pf[i] + (size_t)g * ND);
+            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * RL + tid, wx_pf[i] + (size_t)g * ND);
           wx_pf[i] += (size_t)Gw * ND;
         }
       }
@@ -175,10 +179,10 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   };
 #pragma unroll
   for (int i = 0; i < IPT; ++i)
-    if (!it_ok[i])
+    if (it_on[i] && !it_ok[i])  // rows beyond B: their inputs read as zero
       for (int s = 0; s < kStages; ++s)
 #pragma unroll
-        for (int g = 0; g < Gw; ++g) ring[((size_t)(s * Gw + g) * IPT + i) * nthr + tid] = 0u;
+        for (int g = 0; g < Gw; ++g) ring[((size_t)(s * Gw + g) * IPT + i) * RL + tid] = 0u;
 #pragma unroll
   for (int s = 0; s < kStages; ++s) issue_wx(s < T, s);
 
@@ -219,6 +223,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     {
       float acc[NT][4];
       warp_mma_rows<KT, NT>(Rreg, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
+      if constexpr (DYN) warp_mma_stream<NT>(rsrc, KT, ktot, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
       const int gid = lane >> 2, tig = lane & 3;
       float* dst = pre + g_w * U + ug_w * 16 + gid;
 #pragma unroll
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       }
 #pragma unroll
       for (int g = 0; g < Gw; ++g) {
-        const float2 v = unpack_bf16x2(ring[((size_t)(stage * Gw + g) * IPT + i) * nthr + tid]);
+        const float2 v = unpack_bf16x2(ring[((size_t)(stage * Gw + g) * IPT + i) * RL + tid]);
         wxv[0][g] = v.x; wxv[1][g] = v.y;
       }
 #pragma unroll

@@ -1,5 +1,8 @@
 // Instantiation helper: each frnn_inst_<dir>_<cell>.cu defines FRNN_INST_CELL / FRNN_INST_BWD / FRNN_INST_NAME
 // and includes this file, which emits the kernels for every (KT, NT) and the lookup function.
+//
+// Lookup key: kt = head_dim / 16 for the register-resident kernels (head_dim <= 256); kt = 0 selects the streamed
+// kernel for larger head dims (kStreamKT k-steps in registers, the rest re-read from L2 every step).
 #include "frnn_aux.cuh"
 #include "frnn_bwd.cuh"
 #include "frnn_fwd.cuh"
@@ -8,11 +11,11 @@ namespace frnn {
 
 #if FRNN_INST_BWD
 
-template <int KT, int NT, int MPW>
+template <int KT, int NT, int MPW, bool DYN>
 static LoopKernel make_entry() {
   LoopKernel k;
-  k.fn = reinterpret_cast<const void*>(&frnn_bwd_kernel<FRNN_INST_CELL, KT, NT, MPW>);
-  k.smem_bytes = [](int U, int threads) -> size_t { return bwd_smem_bytes<FRNN_INST_CELL, KT, NT, MPW>(U, threads); };
+  k.fn = reinterpret_cast<const void*>(&frnn_bwd_kernel<FRNN_INST_CELL, KT, NT, MPW, DYN>);
+  k.smem_bytes = [](int D, int U, int threads) -> size_t { return bwd_smem_bytes<FRNN_INST_CELL, NT, MPW>(D, U, threads); };
   k.max_threads = LaunchBounds<FRNN_INST_CELL, KT>::threads;
   return k;
 }
@@ -20,10 +23,15 @@ static LoopKernel make_entry() {
 template <int KT, int NT, int MPW, bool V = RsGeom<FRNN_INST_CELL, KT, MPW>::valid>
 struct RsEntry { static LoopKernel get() { return LoopKernel{nullptr, 0, nullptr}; } };
 template <int KT, int NT, int MPW>
-struct RsEntry<KT, NT, MPW, true> { static LoopKernel get() { return make_entry<KT, NT, MPW>(); } };
+struct RsEntry<KT, NT, MPW, true> { static LoopKernel get() { return make_entry<KT, NT, MPW, false>(); } };
 
 LoopKernel FRNN_INST_NAME(int kt, int nt, int mpw) {
-#define FRNN_CASE(KT, NT) if (kt == KT && nt == NT && mpw == 0) return make_entry<KT, NT, 0>();
+  if (kt == 0 && mpw == 0) {
+    if (nt == 1) return make_entry<kStreamKT, 1, 0, true>();
+    if (nt == 2) return make_entry<kStreamKT, 2, 0, true>();
+    return LoopKernel{nullptr, 0, nullptr};
+  }
+#define FRNN_CASE(KT, NT) if (kt == KT && nt == NT && mpw == 0) return make_entry<KT, NT, 0, false>();
 #define FRNN_RS(KT, NT, MPW) if (kt == KT && nt == NT && mpw == MPW) return RsEntry<KT, NT, MPW>::get();
 #define FRNN_ROW(KT, unused)                                                                     \
   FRNN_CASE(KT, 1) FRNN_CASE(KT, 2) FRNN_CASE(KT, 4)                                             \
@@ -38,17 +46,22 @@ LoopKernel FRNN_INST_NAME(int kt, int nt, int mpw) {
 
 #else
 
-template <int KT, int NT>
+template <int KT, int NT, bool DYN>
 static LoopKernel make_entry() {
   LoopKernel k;
-  k.fn = reinterpret_cast<const void*>(&frnn_fwd_kernel<FRNN_INST_CELL, KT, NT>);
-  k.smem_bytes = [](int U, int threads) -> size_t { return fwd_smem_bytes<FRNN_INST_CELL, KT, NT>(U, threads); };
+  k.fn = reinterpret_cast<const void*>(&frnn_fwd_kernel<FRNN_INST_CELL, KT, NT, DYN>);
+  k.smem_bytes = [](int D, int U, int threads) -> size_t { return fwd_smem_bytes<FRNN_INST_CELL, NT>(D, U, threads); };
   k.max_threads = LaunchBounds<FRNN_INST_CELL, KT>::threads;
   return k;
 }
 
 LoopKernel FRNN_INST_NAME(int kt, int nt) {
-#define FRNN_CASE(KT, NT) if (kt == KT && nt == NT) return make_entry<KT, NT>();
+  if (kt == 0) {
+    if (nt == 1) return make_entry<kStreamKT, 1, true>();
+    if (nt == 2) return make_entry<kStreamKT, 2, true>();
+    return LoopKernel{nullptr, 0, nullptr};
+  }
+#define FRNN_CASE(KT, NT) if (kt == KT && nt == NT) return make_entry<KT, NT, false>();
 #define FRNN_ROW(KT, unused) FRNN_CASE(KT, 1) FRNN_CASE(KT, 2) FRNN_CASE(KT, 4)
   FRNN_FOREACH_KT(FRNN_ROW, 0)
 #undef FRNN_ROW

@@ -79,6 +79,19 @@ def test_long_sequence_drift(cuda_device, function):
 
 
 @pytest.mark.parametrize("function", CELLS)
+@pytest.mark.parametrize("shape", [(8, 5, 1, 512), (2, 3, 2, 1024), (16, 4, 1, 384), (8, 3, 1, 768)],
+                         ids=lambda s: "B%dT%dN%dD%d" % s)
+def test_parity_large_head_dim(cuda_device, function, shape):
+    """Head dims above 256 (the reference's grids go to 1024, tests/test_lstm.py:9-14): R no longer fits the registers
+    of a cluster and is partly streamed from L2 every step; clusters of up to 16 CTAs."""
+    B, T, N, D = shape
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=29 + D, random_init=True)
+    got = run_native(function, Wx, R, b, s0)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=f"{function}{shape}", zero_init=False)
+
+
+@pytest.mark.parametrize("function", CELLS)
 def test_clip_options(cuda_device, function):
     """forward_clipval clamps the new h; gradient_recurrent_clipval clamps the recurrent cotangent
     (reference flashrnn.py:131-136).  The bounds are chosen so that both clamps bite."""

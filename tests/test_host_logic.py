@@ -45,6 +45,14 @@ def test_plan_for_benchmark_configs(function, B, T, N, D, f32):
     assert plan.cache_bytes == rows * T * plan.cache_slots * N * D * 2
 
 
+def test_large_head_dims_take_the_streamed_geometry():
+    for D, cs in ((512, 8), (768, 12), (1024, 16), (320, 5)):
+        plan = _native.query(_native.make_problem("lstm", 8, 16, 1, D, False, True))
+        assert (plan.cluster_size, plan.units_per_cta, plan.threads) == (cs, 64, 512)
+    plan = _native.query(_native.make_problem("elman", 8, 16, 2, 1024, False, True))
+    assert (plan.cluster_size, plan.units_per_cta, plan.threads) == (16, 64, 128)
+
+
 def test_small_batch_spreads_head_large_batch_does_not():
     small = _native.query(_native.make_problem("lstm", 16, 64, 4, 256, False, True))
     large = _native.query(_native.make_problem("elman", 1024, 64, 16, 64, False, True))
@@ -54,7 +62,7 @@ def test_small_batch_spreads_head_large_batch_does_not():
 def test_query_rejects_bad_problems():
     mk = _native.make_problem
     for prob, code in [(mk("lstm", 2, 3, 1, 40, False, True), -3), (mk("lstm", 0, 3, 1, 32, False, True), -3),
-                       (mk("lstm", 2, 3, 1, 512, False, True), -3)]:
+                       (mk("lstm", 2, 3, 1, 1088, False, True), -3), (mk("lstm", 2, 3, 1, 288, False, True), -3)]:
         with pytest.raises(_native.FrnnError) as e:
             _native.query(prob)
         assert e.value.code == code
