@@ -37,6 +37,9 @@ WORKLOADS = {
 }
 DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm": (4, 4, 4, 4)}
 METRIC = "fwd+bwd tokens/sec (B*T/s)"
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the reverse time loop, from an `ncu --set full` capture
+# of this command on a B200 (summary: profiles/ncu_full_C2_kernels.md).  Only workloads that were captured are listed.
+NCU_TRAFFIC_BYTES = {"C2": 237_058_816 + 107_600_128}
 
 
 def measured_peaks():
@@ -76,7 +79,7 @@ class ClockSampler:
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.th = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.th.start()
@@ -317,12 +320,7 @@ def run_ours(args):
     }
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = {k: v for k, v in cpu_sample(function, B, T, N, D).items() if k != "seconds"}
-    prof = ROOT / "profiles" / "traffic.json"
-    if prof.exists():
-        try:
-            line["roofline"]["traffic"] = json.loads(prof.read_text()).get(args.workload, {}).get("bwd_loop_dram_bytes_per_launch")
-        except (ValueError, OSError):
-            pass
+    line["roofline"]["traffic"] = NCU_TRAFFIC_BYTES.get(args.workload)
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
