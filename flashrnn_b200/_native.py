@@ -40,7 +40,8 @@ class FrnnPlan(ctypes.Structure):
     _fields_ = [
         ("abi_version", ctypes.c_int32), ("prob", FrnnProblem), ("cluster_size", ctypes.c_int32),
         ("units_per_cta", ctypes.c_int32), ("batch_tile", ctypes.c_int32), ("threads", ctypes.c_int32),
-        ("wx_stages", ctypes.c_int32), ("cache_slots", ctypes.c_int32), ("reserved", ctypes.c_int32 * 6),
+        ("wx_stages", ctypes.c_int32), ("cache_slots", ctypes.c_int32), ("test_drop_exchange", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 5),
         ("cache_bytes", ctypes.c_uint64), ("workspace_bytes", ctypes.c_uint64), ("grads_offset", ctypes.c_uint64),
         ("grads_count", ctypes.c_uint64),
     ]

@@ -260,6 +260,7 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
+  lp.test_drop = plan->test_drop_exchange;
   const LoopKernel k = get_fwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8);
   e = launch_loop(k, *plan, lp, stream);
   return (int)e;
@@ -311,6 +312,7 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
+  lp.test_drop = plan->test_drop_exchange;
   if (parts & FRNN_PART_LOOP) {
     const LoopKernel k = get_bwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8,
                                         bwd_mpw(pr, cd, plan->cluster_size, plan->batch_tile));

@@ -104,7 +104,7 @@ __host__ __device__ constexpr size_t bwd_smem_bytes(int D, int U, int threads) {
   constexpr int GCA = C::GC > 0 ? C::GC : 1;
   const int CS = D / U;
   const size_t rl = ring_row_len(U, BT, threads);
-  const size_t rings = (size_t)kStages * GCA * IPT * rl * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * rl * 8 + 16;
+  const size_t rings = (size_t)kStages * GCA * IPT * rl * 4 + (size_t)kStages * (C::NNEED + C::NEXT) * IPT * rl * 8 + 32;
   if (MPW > 0)  // delta tile + double-buffered send and receive slices of fp32 partials
     return (size_t)BT * (C::Gr * U + 8) * 2 + (size_t)4 * CS * BT * (U + 4) * 4 + rings;
   return (size_t)2 * CS * BT * (C::Gr * U + 8) * 2 + (size_t)C::Gr * BT * (U + 4) * 4 + rings;
@@ -151,6 +151,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   const int RL = ring_row_len(U, BT, nthr);  // threads that own items: the rings have one slot row per such thread
   uint2* rings = reinterpret_cast<uint2*>(ringc + (size_t)kStages * GCA * IPT * RL);    // [kStages][NSS][IPT][RL]
   uint64_t* full = reinterpret_cast<uint64_t*>(rings + (size_t)kStages * NSS * IPT * RL);  // [2]
+  // gave_up[j & 1] is set by a thread whose bounded wait expired in step index j
+  volatile int* gave_up = reinterpret_cast<volatile int*>(full + 2);
 
   // ---- this warp's fragments of R^T (rows p, columns = gate rows), resident for the whole sequence
   const int g_w = warp / nUT, ug_w = warp - g_w * nUT;  // all-gather: gate / unit tile of this warp
@@ -267,6 +269,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   bool poisoned = false;
   if (CS > 1) {
     if (tid == 0) {
+      gave_up[0] = 0;
+      gave_up[1] = 0;
       mbar_init(&full[0], 1);
       mbar_init(&full[1], 1);
       fence_mbar_init();
@@ -300,13 +304,16 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       }
     }
   };
-  auto wait_exchange = [&](int buf, int j, int t) {  // data of step index j has landed in buffer `buf`
+  // data of step index j has landed in buffer `buf`; `slot` = parity of the step index the wait happens in
+  auto wait_exchange = [&](int buf, int j, int t, int slot) {
     if (CS > 1) {
       if (!poisoned && !mbar_wait_bounded(&full[buf], (uint32_t)((j >> 1) & 1))) {
         poisoned = true;
+        gave_up[slot] = 1;
         report_timeout(p.status, t);
       }
-      if (tid == 0 && j + 2 < T) mbar_arrive_expect_tx(&full[buf], expect_bytes);  // re-arm for step index j + 2
+      // re-arm for step index j + 2; never after an expired wait: that phase is still open, no arrival left to give
+      if (tid == 0 && !poisoned && j + 2 < T) mbar_arrive_expect_tx(&full[buf], expect_bytes);
     }
   };
 
@@ -316,7 +323,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     const int t = T - 1 - j, buf = j & 1;
     FRNN_PROF_MARK(0);
     cp_async_wait<kStages - 1>();
-    if constexpr (RS) { if (j > 0) wait_exchange(buf ^ 1, j - 1, t); }  // partial sums produced in step j-1
+    if constexpr (RS) { if (j > 0) wait_exchange(buf ^ 1, j - 1, t, buf); }  // partial sums produced in step j-1
     FRNN_PROF_MARK(1);
     float dwv[IPT][Gw][2], dg0v[IPT][2];
     __nv_bfloat16* ddst = RS ? dgbuf : dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
@@ -372,6 +379,11 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     if (!RS && CS > 1) fence_proxy_async_smem();
     FRNN_PROF_MARK(2);
     __syncthreads();
+    // Set when a wait expired in some thread of this CTA: in this step before the barrier above (reduce-scatter), or in
+    // the previous step (all-gather, whose wait follows this barrier).  Either way the write precedes the barrier and
+    // no thread writes this slot again before the next one, so every thread reads the same value.  The CTA acts on
+    // it at the end of the step, where the load has long landed.
+    const int quit = (CS > 1) ? gave_up[RS ? buf : buf ^ 1] : 0;
     if constexpr (RS) {
       // ---------------- phase A (reduce-scatter): partial dh_{t-1}[all p] from this CTA's deltas only
       float* sbuf = stage_buf + (size_t)buf * CS * PSL;
@@ -397,7 +409,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       FRNN_PROF_MARK(3);
       __syncthreads();
       // ---------------- push the partial sums of every peer's rows into that peer's receive slice [buf][me]
-      if (CS > 1) {
+      if (CS > 1 && !(p.test_drop && crank == 0 && j == 0)) {  // (test hook: CTA 0 may withhold its first message)
         __syncwarp();
         const uint32_t s0a = smem_u32(sbuf), r0a = smem_u32(rbuf) + crank * slice_bytes;
 #pragma unroll 1
@@ -410,7 +422,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       FRNN_PROF_MARK(4);
     } else {
       // ---------------- push this CTA's delta slice to every other CTA of the cluster
-      if (CS > 1)  // uniform branch; inside, one elected lane per warp issues a copy
+      if (CS > 1 && !(p.test_drop && crank == 0 && j == 0))  // uniform branch; one elected lane per warp copies
         push_slice_to_peers(smem_u32(ddst), slice_bytes, full_u32 + buf * 8, crank, (uint32_t)CS, (uint32_t)warp,
                             (uint32_t)(nthr >> 5));
     }
@@ -431,7 +443,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     stage = (stage + 1 == kStages) ? 0 : stage + 1;
     if constexpr (!RS) {
       FRNN_PROF_MARK(3);
-      wait_exchange(buf, j, t);
+      wait_exchange(buf, j, t, buf);
       FRNN_PROF_MARK(4);
       // ---------------- phase A (all-gather): part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
       float acc[NT][4];
@@ -451,9 +463,13 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       __syncthreads();
     }
     FRNN_PROF_MARK(6);
+    // After an expired wait the whole CTA leaves the time loop.  It sends nothing further, so every other CTA of the
+    // cluster runs into its own bounded wait and leaves the same way; the byte counts of the barriers stay within the
+    // few messages already in flight.
+    if (quit) { poisoned = true; break; }
   }
   cp_async_wait<0>();
-  if constexpr (RS) { if (T > 0) wait_exchange((T - 1) & 1, T - 1, -1); }
+  if constexpr (RS) { if (T > 0) wait_exchange((T - 1) & 1, T - 1, -1, T & 1); }
   FRNN_PROF_DUMP(p.status);
 
   // ---- cotangent of the initial states, bias gradient

@@ -61,6 +61,7 @@ struct LoopParams {
   int state_f32;             // states / dstates / s0 / ds0 are fp32 (else bf16)
   float fclip, gclip;        // <= 0: off
   int grad_cut;              // backward: ignore the matrix part of the recurrent cotangent (truncated BPTT)
+  int test_drop;             // test hook: CTA 0 of each cluster withholds one exchange message (see frnn_plan)
 };
 
 // ------------------------------------------------------------------------------------------------ PTX
@@ -131,7 +132,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Waits for a phase of `bar`, but never longer than ~2 s: on expiry the caller records the failure in
+// Waits for a phase of `bar`, but never longer than ~1 s: on expiry the caller records the failure in
 // the status block and stops waiting for the rest of the kernel (results are then invalid, the kernel ends).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -140,7 +141,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
 #pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
-    if (global_timer_ns() - t0 > 2000000000ull) return false;
+    if (global_timer_ns() - t0 > 1000000000ull) return false;
   }
 }
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -71,7 +71,7 @@ __host__ __device__ constexpr size_t fwd_smem_bytes(int D, int U, int threads) {
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
   const int CS = D / U;
   return (size_t)2 * CS * BT * (U + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
-         (size_t)kStages * C::Gw * IPT * ring_row_len(U, BT, threads) * 4 + 16;
+         (size_t)kStages * C::Gw * IPT * ring_row_len(U, BT, threads) * 4 + 32;
 }
 
 // KT = k-steps (16 columns of R each) a warp keeps in registers.  DYN == false: that is the whole row, D = 16 * KT.
@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   const int RL = ring_row_len(U, BT, nthr);  // threads that own items: the ring has one slot row per such thread
   uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);                // [kStages][Gw][IPT][RL]
   uint64_t* full = reinterpret_cast<uint64_t*>(ring + (size_t)kStages * Gw * IPT * RL);  // [2]
+  volatile int* gave_up = reinterpret_cast<volatile int*>(full + 2);  // set by a thread whose bounded wait expired
 
   // ---- this warp's slice of R: gate g_w of units [unit0 + 16*ug_w, +16), all D inputs, as A fragments
   const int nUT = U >> 4;
@@ -192,6 +193,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   bool poisoned = false;
   if (CS > 1) {
     if (tid == 0) {
+      *gave_up = 0;
       mbar_init(&full[0], 1);
       mbar_init(&full[1], 1);
       fence_mbar_init();
@@ -212,11 +214,13 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     const int cur = t & 1, nxt = cur ^ 1, stage = t % kStages;
     FRNN_PROF_MARK(0);
     if (CS > 1 && t > 0) {
-      if (!poisoned && !mbar_wait_bounded(&full[cur], ((t - 1) >> 1) & 1)) {
+      if (!mbar_wait_bounded(&full[cur], ((t - 1) >> 1) & 1)) {
         poisoned = true;
+        *gave_up = 1;
         report_timeout(p.status, t);
       }
-      if (tid == 0 && t + 2 < T) mbar_arrive_expect_tx(&full[cur], expect_bytes);  // re-arm for h_{t+1}
+      // re-arm for h_{t+1}; never after an expired wait: that phase is still open and has no arrival left to give
+      if (tid == 0 && !poisoned && t + 2 < T) mbar_arrive_expect_tx(&full[cur], expect_bytes);
     }
     FRNN_PROF_MARK(1);
     // ---------------- phase A: pre[b][g*U + u] = sum_k R[g][u][k] * h_{t-1}[b][k]
@@ -237,6 +241,9 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     }
     FRNN_PROF_MARK(2);
     __syncthreads();
+    // Set when a wait of this step expired in some thread of the CTA.  The flag was written before the barrier above,
+    // so every thread reads the same value; the CTA acts on it at the end of the step, where the load has long landed.
+    const int quit = (CS > 1) ? *gave_up : 0;
     // ---------------- phase B: cell update of this thread's items; new h into this CTA's slice of hbuf[nxt]
     cp_async_wait<kStages - 1>();
     FRNN_PROF_MARK(3);
@@ -283,7 +290,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     FRNN_PROF_MARK(4);
     __syncthreads();
     // ---------------- push: this CTA's slice of h_t -> hbuf[nxt] of every other CTA of the cluster
-    if (CS > 1 && t + 1 < T)  // uniform branch; inside, one elected lane per warp issues a copy
+    // (test hook: CTA 0 may withhold its message of step 1 so that the peers' bounded waits can be seen to expire)
+    if (CS > 1 && t + 1 < T && !(p.test_drop && crank == 0 && t == 1))  // uniform branch; one elected lane per warp copies
       push_slice_to_peers(my_slice0 + nxt * buf_bytes, slice_bytes, full_u32 + nxt * 8, crank, (uint32_t)CS,
                           (uint32_t)warp, (uint32_t)(nthr >> 5));
     FRNN_PROF_MARK(5);
@@ -305,6 +313,10 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     }
     issue_wx(t + kStages < T, stage);
     FRNN_PROF_MARK(6);
+    // After an expired wait the whole CTA leaves the time loop.  It sends nothing further, so every other CTA of the
+    // cluster runs into its own bounded wait and leaves the same way; the byte counts of the barriers stay within the
+    // few messages already in flight.
+    if (quit) break;
   }
   cp_async_wait<0>();
   if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight

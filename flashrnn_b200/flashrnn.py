@@ -76,6 +76,10 @@ class FlashRNNConfig:
     # sm_100a tile override for measurements: 0 = take the library's table
     cluster_size: int = 0
     batch_tile: int = 0
+    # synchronise after each launch and raise if a bounded device-side wait expired (a CTA of a cluster never
+    # delivered its part); off by default because it costs a host synchronisation per call
+    check_device_status: bool = False
+    _test_drop_exchange: bool = False  # test hook: make one CTA per cluster withhold a message (see include/frnn.h)
 
     def __post_init__(self):
         if self.num_heads <= 0 and self.head_dim <= 0:
@@ -150,6 +154,16 @@ def _stream_ptr(device) -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+def _raise_on_device_status(ws: torch.Tensor, device, what: str) -> None:
+    """Reads the status block of a workspace (synchronises the stream) and raises if a bounded wait expired."""
+    st = _native.FrnnDevStatus()
+    _native.check("frnn_read_device_status",
+                  _native.lib().frnn_read_device_status(_ptr(ws), _stream_ptr(device), ctypes.byref(st)))
+    if st.code != 0:
+        raise RuntimeError(f"flashrnn_b200: a device-side wait expired in the {what} time loop "
+                           f"(time step {st.where}, CTA {st.cta}); the results of this call are invalid")
+
+
 class _FrnnFunction(torch.autograd.Function):
     """autograd bridge: one frnn_forward, one frnn_backward (+ optional all-reduce) + frnn_finalize_grads.
     Takes the place of FlashRNNFunctionFused (reference flashrnn.py:688-801)."""
@@ -166,6 +180,7 @@ class _FrnnFunction(torch.autograd.Function):
         prob = _native.make_problem(cfg.function, B, T, N, D, state_dtype == torch.float32, training,
                                     cfg.forward_clipval, cfg.gradient_recurrent_clipval, cfg.gradient_recurrent_cut)
         plan = _native.query(prob, cfg.cluster_size, cfg.batch_tile)
+        plan.test_drop_exchange = 1 if cfg._test_drop_exchange else 0
         dev = Wx.device
         states = torch.empty((cfg.num_states, B, T, N, D), dtype=state_dtype, device=dev)
         cache = torch.empty(max(int(plan.cache_bytes), 16), dtype=torch.uint8, device=dev) if training else None
@@ -173,10 +188,13 @@ class _FrnnFunction(torch.autograd.Function):
         args = _native.FrnnFwdArgs(_ptr(Wx_k), _ptr(R_k), _ptr(b_k), _ptr(s0_k), _ptr(states), _ptr(cache), _ptr(ws))
         with torch.cuda.device(dev):
             _native.check("frnn_forward", _native.lib().frnn_forward(ctypes.byref(plan), ctypes.byref(args), _stream_ptr(dev)))
+            if cfg.check_device_status:
+                _raise_on_device_status(ws, dev, "forward")
         if training:
             ctx.save_for_backward(R_k, s0_k, states, cache)
             ctx.plan, ctx.ws, ctx.in_dtypes, ctx.wx_shape, ctx.grad_group = plan, ws, in_dtypes, Wx.shape, grad_group
             ctx.b_shape = b.shape
+            ctx.check_status = cfg.check_device_status
         ctx.training = training
         return states
 
@@ -194,6 +212,8 @@ class _FrnnFunction(torch.autograd.Function):
         L = _native.lib()
         with torch.cuda.device(dev):
             _native.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(args), _stream_ptr(dev)))
+            if ctx.check_status:
+                _raise_on_device_status(ws, dev, "backward")
             off, cnt = int(plan.grads_offset), int(plan.grads_count)
             grads = ws[off:off + 4 * cnt].view(torch.float32)
             if ctx.grad_group is not None:

@@ -73,7 +73,11 @@ typedef struct frnn_plan {
   int32_t threads;         /* threads per CTA of the time-loop kernels                       */
   int32_t wx_stages;       /* time steps of Wx prefetched ahead into shared memory           */
   int32_t cache_slots;     /* activation values cached per (b,t,n,d) in training             */
-  int32_t reserved[6];
+  int32_t test_drop_exchange; /* TEST HOOK, leave 0.  1: CTA 0 of every cluster withholds one exchange message
+                                 (forward: its h of step 1; backward: its first message) so that its peers' bounded
+                                 waits expire; the kernels then finish with invalid results and report it in the
+                                 status block.  Exercises the failure-detection path without faulting the GPU.     */
+  int32_t reserved[5];
   uint64_t cache_bytes;     /* size of the activation cache (opaque layout, tied to this plan) */
   uint64_t workspace_bytes; /* size of the scratch workspace                                  */
   uint64_t grads_offset;    /* byte offset, inside the workspace, of the fp32 gradients dR || db */
