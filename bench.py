@@ -301,6 +301,7 @@ def run_ours(args):
     bwd_bytes = E * (S * ssz + S * ssz + Gw * esz)
     fwd_bytes = E * (Gw * esz + S * ssz)
     achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+    wide = plan.batch_tile == 128  # tcgen05 loops: forward, reverse loop (with dR and db inside), cast = 3 launches per step
     line = {
         "metric": METRIC, "value": world * B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -313,15 +314,17 @@ def run_ours(args):
                    "l2": "working set per step (Wx+states+cache+dWx > 400 MB for C2) exceeds the 126 MB L2; no explicit flush"},
         "kernel_ms": {"forward_loop": fwd_ms, "backward_loop": bwd_ms, "recurrent_grad": dr_ms},
         "us_per_time_step": {"forward": 1e3 * fwd_ms / T, "backward": 1e3 * bwd_ms / T},
-        "roofline": {"bound": "hbm", "kernel": "frnn_bwd_kernel (reverse time loop)", "achieved": achieved, "peak": hbm_peak,
+        "roofline": {"bound": "hbm", "kernel": "wide_bwd_elman_kernel (reverse time loop, dR and db inside)" if wide
+                     else "frnn_bwd_kernel (reverse time loop)", "achieved": achieved, "peak": hbm_peak,
                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": which, "traffic": None,
                      "algorithmic_bytes_per_launch": bwd_bytes,
                      "forward_loop": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "algorithmic_bytes_per_launch": fwd_bytes},
                      "tensor_frac_whole_step": (6.0 * E * Gr * D / (ms * 1e-3) / 1e12) / tc_peak,
-                     "note": "the serial chain of 2T dependent steps, not HBM or the tensor pipe, bounds this workload"},
+                     "note": "streams one 16 KB tile per operand, step and CTA; HBM-bound" if wide else
+                     "the serial chain of 2T dependent steps, not HBM or the tensor pipe, bounds this workload"},
         "e2e": {"value": world * B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
-        "gpu_launches": 6 * args.steps,
+        "gpu_launches": (3 if wide else 6) * args.steps,
         "clocks": clk.summary(),
     }
     if world == 1 and not args.no_cpu:

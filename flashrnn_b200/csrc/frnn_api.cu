@@ -80,8 +80,15 @@ static int bwd_mpw(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
 
 // A tile (cluster size, batch tile) is usable when both loop kernels exist for it, the CTA fits the
 // instantiation's thread bound and the shared-memory budget.
+static bool wide_problem(const frnn_problem& pr) {
+  return wide_supported(pr.cell, pr.D, pr.dtype_state == FRNN_DTYPE_F32, pr.forward_clip, pr.grad_clip, pr.grad_cut);
+}
+static bool is_wide(const frnn_plan& pl) { return pl.batch_tile == kWideBatchTile; }
+static int plan_threads(const CellDims& cd, int units, int bt) { return bt == kWideBatchTile ? kWideThreads : 2 * cd.Gr * units; }
+
 static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) {
   const int D = pr.D;
+  if (bt == kWideBatchTile) return cs == 1 && wide_problem(pr);  // 128-row tensor-core loops: one CTA per head and tile
   if (cs < 1 || D % cs) return false;
   if (streamed(pr) ? (cs > 16 || D / cs != kStreamU) : cs > 8) return false;
   const int U = D / cs;
@@ -99,7 +106,15 @@ static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) 
 // the head is spread over as many SMs as a portable cluster allows; large-batch problems already fill the
 // GPU with (head, batch tile) pairs and take the smallest cluster (no cross-CTA exchange when it is 1).
 static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs, int want_bt, int* cs_out, int* bt_out) {
-  // measured on B200: 8-row batch tiles win for every benchmark configuration (more CTAs, shorter steps)
+  // Large batches of a cell / head dim the 128-row tensor-core loops cover: those stream at the HBM rate once their
+  // (head, 128-row tile) pairs occupy most of the SMs
+  if ((want_bt == kWideBatchTile || (!want_bt && !want_cs && (long long)(pr.B / kWideBatchTile) * pr.N >= 64)) &&
+      tile_ok(pr, cd, 1, kWideBatchTile) && (want_cs == 0 || want_cs == 1)) {
+    *cs_out = 1;
+    *bt_out = kWideBatchTile;
+    return true;
+  }
+  // measured on B200: otherwise 8-row batch tiles win for every benchmark configuration (more CTAs, shorter steps)
   const int bt_pref[3] = {8, 16, 32};
   for (int bi = 0; bi < 3; ++bi) {
     const int bt = want_bt ? want_bt : bt_pref[bi];
@@ -148,7 +163,7 @@ static int fill_plan(const frnn_problem* pr, int cs, int bt, int stages, frnn_pl
   pl.cluster_size = ccs;
   pl.units_per_cta = pr->D / ccs;
   pl.batch_tile = cbt;
-  pl.threads = 2 * cd.Gr * pl.units_per_cta;
+  pl.threads = plan_threads(cd, pl.units_per_cta, cbt);
   pl.wx_stages = kStages;
   // Elman needs its one cache slot (the tanh output) only when h is clamped afterwards; otherwise h itself serves
   pl.cache_slots = (pr->cell == CELL_ELMAN && !(pr->forward_clip > 0.f)) ? 0 : cd.GC;
@@ -170,7 +185,7 @@ static int check_plan(const frnn_plan* pl, CellDims* cd) {
   if (rc) return rc;
   if (!tile_ok(pl->prob, *cd, pl->cluster_size, pl->batch_tile)) return FRNN_ERR_PLAN;
   if (pl->units_per_cta * pl->cluster_size != pl->prob.D) return FRNN_ERR_PLAN;
-  if (pl->threads != 2 * cd->Gr * pl->units_per_cta) return FRNN_ERR_PLAN;
+  if (pl->threads != plan_threads(*cd, pl->units_per_cta, pl->batch_tile)) return FRNN_ERR_PLAN;
   if (pl->workspace_bytes != workspace_layout(pl->prob, *cd).total) return FRNN_ERR_PLAN;
   return FRNN_OK;
 }
@@ -245,6 +260,9 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
 
   cudaError_t e = cudaMemsetAsync(ws, 0, kStatusBytes, stream);
   if (e != cudaSuccess) return (int)e;
+  if (is_wide(*plan))
+    return (int)launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,
+                                    stream);
   e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
   if (e != cudaSuccess) return (int)e;
 
@@ -293,8 +311,14 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
     if (e != cudaSuccess) return (int)e;
     e = cudaMemsetAsync(grads, 0, (nR + nb) * sizeof(float), stream);
     if (e != cudaSuccess) return (int)e;
-    e = launch_pack_recurrent(a->R, ws + w.rpack_bwd, cd.Gr, pr.N, pr.D, 1, stream);
+    if (!is_wide(*plan)) e = launch_pack_recurrent(a->R, ws + w.rpack_bwd, cd.Gr, pr.N, pr.D, 1, stream);
     if (e != cudaSuccess) return (int)e;
+  }
+  if (is_wide(*plan)) {  // one kernel: reverse loop with dR and db accumulated inside; the dR part has nothing left to do
+    if (parts & FRNN_PART_LOOP)
+      e = launch_wide_backward(a->R, a->s0, a->states, a->dstates, a->dWx, a->ds0, grads, grads + nR,
+                               reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, stream);
+    return (int)e;
   }
 
   LoopParams lp = {};

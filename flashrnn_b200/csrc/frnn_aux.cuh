@@ -44,6 +44,15 @@ cudaError_t launch_recurrent_grad(int cell, int B, int T, int N, int D, int Gr, 
 cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,
                                      const void* dg0, const void* states, const void* s0, float* dR, unsigned* status,
                                      int sm_count, cudaStream_t stream);
+// 128-row tensor-core time loops (frnn_wide.cu): one CTA per (head, 128 batch rows); the backward also produces dR and db
+constexpr int kWideBatchTile = 128;
+constexpr int kWideThreads = 160;
+bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, int grad_cut);
+cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
+                                unsigned* status, int B, int T, int N, cudaStream_t stream);
+cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
+                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N,
+                                 cudaStream_t stream);
 cudaError_t launch_cast_grads(const float* src, void* dR, void* db, size_t nR, size_t nb, cudaStream_t stream);
 
 }  // namespace frnn

@@ -1,0 +1,553 @@
+// Time loops for LARGE batches on the 5th-generation tensor cores: one CTA owns a whole head (head dim 64) and a tile
+// of 128 batch rows for all T steps.  Elman cell (h_t = tanh(Wx_t + R h_{t-1} + b)).
+//
+// Forward, per step:  acc[128 x 64] (fp32, tensor memory) = Wx_t * I + 1 * b  (issued ahead, off the critical path)
+//                     acc += h_{t-1} * R^T                                     (tcgen05.mma, operands in shared memory)
+//                     h_t = tanh(acc) -> bf16 tile in shared memory            (tcgen05.ld, one batch row per thread)
+//   The h tile is the A operand of the next step and the source of a tensor-map bulk store into `states`; Wx tiles are
+//   fetched by tensor-map bulk loads a few steps ahead.  Identity and bias products put the additions on the tensor pipe,
+//   so the 128 row threads only do tanh, the bf16 packing and eight 16-byte shared-memory stores per step.
+// Backward, per step: acc = dh_ext_t * I (ahead) + delta_{t+1} * R;  delta_t = acc * (1 - h_t^2) -> bf16 tile;
+//                     dR (tensor memory, kept for all T steps) += delta_t^T * h_{t-1};  delta tile -> dWx (bulk store);
+//                     db in registers.  No separate dR pass over HBM: the delta and h tiles are in shared memory anyway.
+// Warps 0-3: one batch row per thread.  Warp 4, one lane: issues every bulk copy and every MMA.  All tiles are
+// [128 rows][64 bf16] = rows of 128 bytes in the 128-byte-swizzle layout shared by the bulk copies and the MMA descriptors.
+//
+// Replaces, for these shapes, FLASHRNNCellFusedForward / FLASHRNNCellFusedBackward and the dR GEMM + bias reduction that
+// follow the reverse loop (flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:146-659, flashrnn_fused_backward.cu:129-624,
+// 626-665, 1049-1058; cell: fused/elman_fused_pointwise.cuh:34-93).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "frnn_aux.cuh"
+#include "frnn_tc.cuh"
+
+namespace frnn {
+
+namespace {
+
+constexpr int WD = 64;                          // head dim
+constexpr int WM = 128;                         // batch rows per CTA = UMMA M
+constexpr uint32_t WTILE = WM * WD * 2;         // bytes of a [128][64] bf16 tile
+constexpr uint32_t WMAT = WD * WD * 2;          // bytes of a [64][64] bf16 operand
+constexpr int WF_STAGES = 6;                    // forward: Wx tiles in flight
+constexpr int WB_STAGES = 4;                    // backward: h tiles and cotangent tiles in flight (each)
+constexpr int W_THREADS = 160;
+
+// byte offset of 16-byte chunk `chunk` of row `row` inside a 128-byte-swizzled tile
+__device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
+
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+  return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+
+// ================================================================================================ forward
+struct WideFwdParams {
+  const __nv_bfloat16* R;     // [1,N,64,64]
+  const __nv_bfloat16* bias;  // [1,N,64]
+  const __nv_bfloat16* s0;    // [1,B,1,N,64]
+  unsigned* status;
+  int B, T, N;
+};
+
+constexpr uint32_t WF_OFF_WX = 0;
+constexpr uint32_t WF_OFF_H = WF_OFF_WX + WF_STAGES * WTILE;
+constexpr uint32_t WF_OFF_R = WF_OFF_H + 2 * WTILE;
+constexpr uint32_t WF_OFF_I = WF_OFF_R + WMAT;
+constexpr uint32_t WF_OFF_ONES = WF_OFF_I + WMAT;       // A operand [128 rows][16 k], k = 0 holds 1.0 (no swizzle)
+constexpr uint32_t WF_OFF_BIAS = WF_OFF_ONES + 4096;    // B operand [64 rows][16 k], k = 0 holds b[row] (no swizzle)
+constexpr uint32_t WF_OFF_BAR = WF_OFF_BIAS + 2048;
+constexpr uint32_t WF_SMEM = WF_OFF_BAR + 8 * (WF_STAGES + 3) + 16 + 1024;  // + slack for the 1024-byte alignment
+
+__global__ void __launch_bounds__(W_THREADS, 1)
+wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states,
+                      const WideFwdParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_raw + (base - raw);
+  uint64_t* wx_full = reinterpret_cast<uint64_t*>(sm + WF_OFF_BAR);  // [WF_STAGES] bytes of a Wx tile have landed
+  uint64_t* acc_full = wx_full + WF_STAGES;                          // [2] MMAs into accumulator x have completed
+  uint64_t* h_ready = acc_full + 2;                                  // 128 arrivals: h_t is in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(h_ready + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T;
+
+  // ---- operands written once: R (as [d][p], K-major), the identity, the ones column, the bias row, h_{-1}
+  {
+    const __nv_bfloat16* Rn = p.R + (size_t)n * WD * WD;
+    for (int c = tid; c < WD * 8; c += W_THREADS) {
+      const uint32_t d = c >> 3, j = c & 7;
+      *reinterpret_cast<uint4*>(sm + WF_OFF_R + sw128(d, j)) = *reinterpret_cast<const uint4*>(Rn + d * WD + j * 8);
+      const uint32_t w = (d & 7) >> 1, one = ((d >> 3) == j) ? (0x3F80u << (16 * (d & 1))) : 0u;  // bf16 1.0 at k = d
+      *reinterpret_cast<uint4*>(sm + WF_OFF_I + sw128(d, j)) =
+          make_uint4(w == 0 ? one : 0u, w == 1 ? one : 0u, w == 2 ? one : 0u, w == 3 ? one : 0u);
+    }
+    for (int r = tid; r < WM; r += W_THREADS) {
+      unsigned char* q = sm + WF_OFF_ONES + (r >> 3) * 256 + (r & 7) * 16;
+      *reinterpret_cast<uint4*>(q) = make_uint4(0x3F80u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    for (int d = tid; d < WD; d += W_THREADS) {
+      unsigned char* q = sm + WF_OFF_BIAS + (d >> 3) * 256 + (d & 7) * 16;
+      *reinterpret_cast<uint4*>(q) = make_uint4((uint32_t)__bfloat16_as_ushort(p.bias[(size_t)n * WD + d]), 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (tid < WM) {  // h_{-1} -> h buffer 1 (step t reads buffer (t + 1) & 1)
+      const int b = b0 + tid;
+      const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)(b < p.B ? b : 0) * p.N + n) * WD);
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(sm + WF_OFF_H + WTILE + sw128(tid, j)) = (b < p.B) ? src[j] : make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  if (tid == 0) {
+    for (int s = 0; s < WF_STAGES; ++s) mbar_init(&wx_full[s], 1);
+    mbar_init(&acc_full[0], 1);
+    mbar_init(&acc_full[1], 1);
+    mbar_init(h_ready, WM);
+    fence_mbar_init();
+  }
+  if (warp == 4) tmem_alloc(tmem_slot, 128);  // two accumulators of 64 fp32 columns
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer: bulk copies and MMAs
+      const uint32_t idesc = instr_desc_bf16(WM, WD, 0, 0);
+      const void* tmw = &tm_wx;
+      const void* tms = &tm_states;
+      int loads = 0, waited = 0;  // Wx tiles requested / seen to land (both in step order)
+      auto load_wx = [&](int t) {
+        const int s = t % WF_STAGES;
+        mbar_arrive_expect_tx(&wx_full[s], WTILE);
+        tma_load_5d(base + WF_OFF_WX + s * WTILE, tmw, 0, n, 0, t, b0, &wx_full[s]);
+        ++loads;
+      };
+      auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I + ones * bias
+        const uint32_t a0 = base + WF_OFF_WX + (t % WF_STAGES) * WTILE, d = tmem + (t & 1) * WD;
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k)
+          umma_bf16(d, smem_desc_sw128(a0 + k * 32, 0, 1024), smem_desc_sw128(base + WF_OFF_I + k * 32, 0, 1024), idesc, k);
+        umma_bf16(d, smem_desc(base + WF_OFF_ONES, 128, 256), smem_desc(base + WF_OFF_BIAS, 128, 256), idesc, 1u);
+      };
+      for (int t = 0; t < T && t < WF_STAGES; ++t) load_wx(t);
+      bool ok = mbar_wait_bounded(&wx_full[0], 0);
+      if (ok) {
+        waited = 1;
+        issue_pre(0);
+      } else {
+        report_timeout(p.status, 0);
+      }
+      for (int t = 0; ok && t < T; ++t) {
+        if (t > 0) {
+          if (!mbar_wait_bounded(h_ready, (uint32_t)((t - 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
+          tc_fence_after();
+        }
+        bulk_wait_group_read<0>();  // the store of h_{t-2} has left the buffer that step t's threads overwrite
+        const uint32_t a0 = base + WF_OFF_H + ((t + 1) & 1) * WTILE, d = tmem + (t & 1) * WD;
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k)
+          umma_bf16(d, smem_desc_sw128(a0 + k * 32, 0, 1024), smem_desc_sw128(base + WF_OFF_R + k * 32, 0, 1024), idesc, 1u);
+        umma_commit(&acc_full[t & 1]);
+        if (t > 0) {  // h_{t-1} -> states[0][b0.., t-1, n, :]
+          tma_store_5d(tms, a0, 0, n, t - 1, b0, 0);
+          bulk_commit_group();
+          // the Wx tile of step t-1 was consumed by MMAs that completed before h_{t-1} could be computed
+          if (t - 1 + WF_STAGES < T) load_wx(t - 1 + WF_STAGES);
+        }
+        if (t + 1 < T) {
+          if (!mbar_wait_bounded(&wx_full[(t + 1) % WF_STAGES], (uint32_t)(((t + 1) / WF_STAGES) & 1))) {
+            report_timeout(p.status, t);
+            ok = false;
+            break;
+          }
+          ++waited;
+          issue_pre(t + 1);
+        }
+      }
+      if (ok) {
+        if (mbar_wait_bounded(h_ready, (uint32_t)((T - 1) & 1))) {
+          tma_store_5d(tms, base + WF_OFF_H + ((T - 1) & 1) * WTILE, 0, n, T - 1, b0, 0);
+          bulk_commit_group();
+        } else {
+          report_timeout(p.status, T);
+        }
+      }
+      // never leave with copies in flight (only an expired wait leaves any load unobserved)
+      for (int i = (waited > loads - WF_STAGES ? waited : loads - WF_STAGES); i < loads; ++i)
+        mbar_wait_bounded(&wx_full[i % WF_STAGES], (uint32_t)((i / WF_STAGES) & 1));
+      bulk_wait_group<0>();
+    }
+  } else {
+    // ------------------------------------------------------------ row threads: h_t = tanh(acc)
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    for (int t = 0; t < T; ++t) {
+      if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); break; }
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32_nowait(trow + (t & 1) * WD, r0);
+      tmem_ld32_nowait(trow + (t & 1) * WD + 32, r1);
+      tmem_ld_wait();
+      unsigned char* dst = sm + WF_OFF_H + (t & 1) * WTILE;
+#pragma unroll
+      for (uint32_t j = 0; j < 8; ++j) {
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = fast_tanh(__uint_as_float(j < 4 ? r0[j * 8 + i] : r1[(j - 4) * 8 + i]));
+        *reinterpret_cast<uint4*>(dst + sw128(tid, j)) = pack8(v);
+      }
+      fence_proxy_async_smem();  // the tile is read by the tensor core and by the bulk store
+      tc_fence_before();
+      mbar_arrive(h_ready);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    __syncwarp();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
+// ================================================================================================ backward
+struct WideBwdParams {
+  const __nv_bfloat16* R;  // [1,N,64,64]
+  __nv_bfloat16* ds0;      // [1,B,1,N,64]
+  float* dR;               // fp32 [1,N,64,64], accumulated with atomics
+  float* dbias;            // fp32 [1,N,64]
+  unsigned* status;
+  int B, T, N;
+};
+
+constexpr uint32_t WB_OFF_H = 0;                                  // h tiles: sequence index q <-> time T-1-q (q = T: h_{-1})
+constexpr uint32_t WB_OFF_E = WB_OFF_H + WB_STAGES * WTILE;       // cotangent tiles: sequence index j <-> time T-1-j
+constexpr uint32_t WB_OFF_D = WB_OFF_E + WB_STAGES * WTILE;       // delta tiles [2]
+constexpr uint32_t WB_OFF_R = WB_OFF_D + 2 * WTILE;               // R as [p][d] (K-major B operand of delta * R)
+constexpr uint32_t WB_OFF_I = WB_OFF_R + WMAT;
+constexpr uint32_t WB_OFF_DB = WB_OFF_I + WMAT;                   // float[64]
+constexpr uint32_t WB_OFF_BAR = WB_OFF_DB + 256;
+constexpr uint32_t WB_SMEM = WB_OFF_BAR + 8 * (2 * WB_STAGES + 4) + 16 + 1024;
+
+__global__ void __launch_bounds__(W_THREADS, 1)
+wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __grid_constant__ CUtensorMap tm_s0,
+                      const __grid_constant__ CUtensorMap tm_dstates, const __grid_constant__ CUtensorMap tm_dwx,
+                      const WideBwdParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_raw + (base - raw);
+  float* sdb = reinterpret_cast<float*>(sm + WB_OFF_DB);
+  uint64_t* h_full = reinterpret_cast<uint64_t*>(sm + WB_OFF_BAR);  // [WB_STAGES]
+  uint64_t* e_full = h_full + WB_STAGES;                            // [WB_STAGES]
+  uint64_t* acc_full = e_full + WB_STAGES;                          // [2]
+  uint64_t* d_ready = acc_full + 2;                                 // 128 arrivals: delta tile written
+  uint64_t* dr_done = d_ready + 1;                                  // all dR MMAs have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dr_done + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T;
+
+  {
+    const __nv_bfloat16* Rn = p.R + (size_t)n * WD * WD;
+    for (int c = tid; c < WD * 8; c += W_THREADS) {
+      const uint32_t pp = c >> 3, j = c & 7;  // row p, chunk of d = 8j .. 8j+7:  Rk[p][d] = R[d][p]
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t lo = __bfloat16_as_ushort(Rn[(j * 8 + 2 * i) * WD + pp]);
+        const uint32_t hi = __bfloat16_as_ushort(Rn[(j * 8 + 2 * i + 1) * WD + pp]);
+        w[i] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4*>(sm + WB_OFF_R + sw128(pp, j)) = make_uint4(w[0], w[1], w[2], w[3]);
+      const uint32_t wi = (pp & 7) >> 1, one = ((pp >> 3) == j) ? (0x3F80u << (16 * (pp & 1))) : 0u;
+      *reinterpret_cast<uint4*>(sm + WB_OFF_I + sw128(pp, j)) =
+          make_uint4(wi == 0 ? one : 0u, wi == 1 ? one : 0u, wi == 2 ? one : 0u, wi == 3 ? one : 0u);
+    }
+    if (tid < WD) sdb[tid] = 0.f;
+  }
+  if (tid == 0) {
+    for (int s = 0; s < WB_STAGES; ++s) { mbar_init(&h_full[s], 1); mbar_init(&e_full[s], 1); }
+    mbar_init(&acc_full[0], 1);
+    mbar_init(&acc_full[1], 1);
+    mbar_init(d_ready, WM);
+    mbar_init(dr_done, 1);
+    fence_mbar_init();
+  }
+  if (warp == 4) tmem_alloc(tmem_slot, 256);  // columns [0,128): two dh accumulators; [128,192): dR
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer
+      const uint32_t idesc_kk = instr_desc_bf16(WM, WD, 0, 0);  // dh: [128 b] x [64 p], K = d
+      const uint32_t idesc_mm = instr_desc_bf16(WD, WD, 1, 1);  // dR: [64 d] x [64 p], K = b; both operands MN-major
+      const void* tmh = &tm_states;
+      const void* tm0 = &tm_s0;
+      const void* tme = &tm_dstates;
+      const void* tmd = &tm_dwx;
+      int h_loads = 0, h_seen = 0, e_loads = 0, e_seen = 0;  // tiles requested / known to have landed, in sequence order
+      auto load_h = [&](int q) {
+        const int s = q % WB_STAGES;
+        mbar_arrive_expect_tx(&h_full[s], WTILE);
+        if (q < T) tma_load_5d(base + WB_OFF_H + s * WTILE, tmh, 0, n, T - 1 - q, b0, 0, &h_full[s]);
+        else tma_load_5d(base + WB_OFF_H + s * WTILE, tm0, 0, n, 0, b0, 0, &h_full[s]);
+        ++h_loads;
+      };
+      auto load_e = [&](int j) {
+        const int s = j % WB_STAGES;
+        mbar_arrive_expect_tx(&e_full[s], WTILE);
+        tma_load_5d(base + WB_OFF_E + s * WTILE, tme, 0, n, T - 1 - j, b0, 0, &e_full[s]);
+        ++e_loads;
+      };
+      auto issue_pre = [&](int j) {  // acc[j & 1] = dh_ext_j * I
+        const uint32_t a0 = base + WB_OFF_E + (j % WB_STAGES) * WTILE, d = tmem + (j & 1) * WD;
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k)
+          umma_bf16(d, smem_desc_sw128(a0 + k * 32, 0, 1024), smem_desc_sw128(base + WB_OFF_I + k * 32, 0, 1024), idesc_kk, k);
+      };
+      for (int q = 0; q <= T && q < WB_STAGES; ++q) load_h(q);
+      for (int j = 0; j < T && j < WB_STAGES; ++j) load_e(j);
+      bool ok = true;
+      int where = 0;
+      do {
+        if (!mbar_wait_bounded(&e_full[0], 0)) { ok = false; break; }
+        e_seen = 1;
+        issue_pre(0);
+        umma_commit(&acc_full[0]);  // step 0 (t = T-1) has no recurrent part
+        if (T > 1) {
+          if (!mbar_wait_bounded(&e_full[1], 0)) { ok = false; break; }
+          e_seen = 2;
+          issue_pre(1);
+        }
+        for (int j = 0; j < T; ++j) {
+          where = j;
+          if (!mbar_wait_bounded(d_ready, (uint32_t)(j & 1))) { ok = false; break; }
+          tc_fence_after();
+          if (h_seen < j + 1) h_seen = j + 1;  // the row threads of step j have read h tile j
+          bulk_wait_group_read<0>();           // the store of delta_{j-1} has left the buffer step j+1 overwrites
+          const uint32_t dt = base + WB_OFF_D + (j & 1) * WTILE;
+          // dh accumulator of step j+1 (+)= delta_j * R; step T (the cotangent of h_{-1}) has no external part
+          const uint32_t acc = tmem + ((j + 1) & 1) * WD;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k)
+            umma_bf16(acc, smem_desc_sw128(dt + k * 32, 0, 1024), smem_desc_sw128(base + WB_OFF_R + k * 32, 0, 1024), idesc_kk,
+                      (j + 1 < T || k > 0) ? 1u : 0u);
+          umma_commit(&acc_full[(j + 1) & 1]);
+          tma_store_5d(tmd, dt, 0, n, 0, T - 1 - j, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
+          bulk_commit_group();
+          // dR += delta_j^T * h_{t-1}  (h tile of sequence index j + 1)
+          if (!mbar_wait_bounded(&h_full[(j + 1) % WB_STAGES], (uint32_t)(((j + 1) / WB_STAGES) & 1))) { ok = false; break; }
+          h_seen = j + 2;
+          const uint32_t ht = base + WB_OFF_H + ((j + 1) % WB_STAGES) * WTILE;
+#pragma unroll
+          for (uint32_t ks = 0; ks < 8; ++ks)
+            umma_bf16(tmem + 2 * WD, smem_desc_sw128(dt + ks * 2048, 0, 1024), smem_desc_sw128(ht + ks * 2048, 0, 1024), idesc_mm,
+                      (j > 0 || ks > 0) ? 1u : 0u);
+          // h tile j-1: its row threads (step j-1) and its dR MMAs (step j-2, completed before the accumulator of
+          // step j was signalled) are done; cotangent tile j: consumed by MMAs that completed before step j started
+          if (j >= 1 && j - 1 + WB_STAGES <= T) load_h(j - 1 + WB_STAGES);
+          if (j + WB_STAGES < T) load_e(j + WB_STAGES);
+          if (j + 2 < T) {
+            if (!mbar_wait_bounded(&e_full[(j + 2) % WB_STAGES], (uint32_t)(((j + 2) / WB_STAGES) & 1))) { ok = false; break; }
+            e_seen = j + 3;
+            issue_pre(j + 2);
+          }
+        }
+      } while (false);
+      if (!ok) report_timeout(p.status, where);
+      umma_commit(dr_done);
+      for (int i = (h_seen > h_loads - WB_STAGES ? h_seen : h_loads - WB_STAGES); i < h_loads; ++i)
+        mbar_wait_bounded(&h_full[i % WB_STAGES], (uint32_t)((i / WB_STAGES) & 1));
+      for (int i = (e_seen > e_loads - WB_STAGES ? e_seen : e_loads - WB_STAGES); i < e_loads; ++i)
+        mbar_wait_bounded(&e_full[i % WB_STAGES], (uint32_t)((i / WB_STAGES) & 1));
+      bulk_wait_group<0>();
+    }
+  } else {
+    // ------------------------------------------------------------ row threads: delta_t = dh_t * (1 - h_t^2)
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    float db[WD];
+#pragma unroll
+    for (int i = 0; i < WD; ++i) db[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < T; ++j) {
+      if (!mbar_wait_bounded(&acc_full[j & 1], (uint32_t)((j >> 1) & 1)) ||
+          !mbar_wait_bounded(&h_full[j % WB_STAGES], (uint32_t)((j / WB_STAGES) & 1))) {
+        report_timeout(p.status, j);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32_nowait(trow + (j & 1) * WD, r0);
+      tmem_ld32_nowait(trow + (j & 1) * WD + 32, r1);
+      tmem_ld_wait();
+      const unsigned char* hsrc = sm + WB_OFF_H + (j % WB_STAGES) * WTILE;
+      unsigned char* dst = sm + WB_OFF_D + (j & 1) * WTILE;
+#pragma unroll
+      for (uint32_t c = 0; c < 8; ++c) {
+        const uint32_t off = sw128(tid, c);
+        const uint4 hv = *reinterpret_cast<const uint4*>(hsrc + off);
+        const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 h2 = unpack_bf16x2(hw[i]);
+          const float g0 = __uint_as_float(c < 4 ? r0[c * 8 + 2 * i] : r1[(c - 4) * 8 + 2 * i]);
+          const float g1 = __uint_as_float(c < 4 ? r0[c * 8 + 2 * i + 1] : r1[(c - 4) * 8 + 2 * i + 1]);
+          v[2 * i] = g0 * (1.f - h2.x * h2.x);
+          v[2 * i + 1] = g1 * (1.f - h2.y * h2.y);
+          db[c * 8 + 2 * i] += v[2 * i];
+          db[c * 8 + 2 * i + 1] += v[2 * i + 1];
+        }
+        *reinterpret_cast<uint4*>(dst + off) = pack8(v);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(d_ready);
+    }
+    // cotangent of the initial state: the accumulator of "step T"
+    if (ok && mbar_wait_bounded(&acc_full[T & 1], (uint32_t)((T >> 1) & 1))) {
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32_nowait(trow + (T & 1) * WD, r0);
+      tmem_ld32_nowait(trow + (T & 1) * WD + 32, r1);
+      tmem_ld_wait();
+      const int b = b0 + tid;
+      if (b < p.B) {
+        uint4* out = reinterpret_cast<uint4*>(p.ds0 + ((size_t)b * p.N + n) * WD);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(c < 4 ? r0[c * 8 + i] : r1[(c - 4) * 8 + i]);
+          out[c] = pack8(v);
+        }
+      }
+    } else if (ok) {
+      report_timeout(p.status, T);
+      ok = false;
+    }
+    // dR: row d of the 64 x 64 accumulator sits in lane (d / 16) * 32 + d % 16 of tensor memory
+    if (ok && mbar_wait_bounded(dr_done, 0)) {
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32_nowait(trow + 2 * WD, r0);
+      tmem_ld32_nowait(trow + 2 * WD + 32, r1);
+      tmem_ld_wait();
+      if (lane < 16) {
+        float* out = p.dR + ((size_t)n * WD + (warp * 16 + lane)) * WD;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          atomicAdd(out + i, __uint_as_float(r0[i]));
+          atomicAdd(out + 32 + i, __uint_as_float(r1[i]));
+        }
+      }
+    } else if (ok) {
+      report_timeout(p.status, T + 1);
+    }
+#pragma unroll
+    for (int i = 0; i < WD; ++i) atomicAdd(&sdb[i], db[i]);  // once per kernel; static indices keep db in registers
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid < WD) atomicAdd(p.dbias + (size_t)n * WD + tid, sdb[tid]);
+  if (warp == 4) {
+    __syncwarp();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ================================================================================================ host
+// Tensor map over a bf16 tensor seen as 5-d (extents / byte strides innermost first; dims[0] = 64 contiguous elements):
+// tiles of 64 elements x 128 entries of dimension `batch_dim`, 128-byte swizzle, out-of-range rows read as zero and
+// are dropped on stores.
+bool encode_tiles(CUtensorMap* tm, const void* base, const uint64_t (&dims)[5], const uint64_t (&strides)[4], int batch_dim) {
+  static const PFN_cuTensorMapEncodeTiled_v12000 encode = [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  }();
+  if (!encode) return false;
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t box[5], estr[5];
+  for (int i = 0; i < 5; ++i) { gdim[i] = dims[i]; box[i] = 1; estr[i] = 1; }
+  for (int i = 0; i < 4; ++i) gstr[i] = strides[i];
+  box[0] = WD;
+  box[batch_dim] = WM;
+  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), gdim, gstr, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// [B,T,1,N,64] (Wx, dWx): coordinates (0, n, 0, t, b)
+bool map_btgnd(CUtensorMap* tm, const void* base, int B, int T, int N) {
+  const uint64_t row = WD * 2;
+  const uint64_t dims[5] = {WD, (uint64_t)N, 1, (uint64_t)T, (uint64_t)B};
+  const uint64_t strides[4] = {row, row * N, row * N, row * N * T};
+  return encode_tiles(tm, base, dims, strides, 4);
+}
+// [1,B,T,N,64] (states, dstates): coordinates (0, n, t, b, 0);  T = 1 gives the initial-state layout [1,B,1,N,64]
+bool map_sbtnd(CUtensorMap* tm, const void* base, int B, int T, int N) {
+  const uint64_t row = WD * 2;
+  const uint64_t dims[5] = {WD, (uint64_t)N, (uint64_t)T, (uint64_t)B, 1};
+  const uint64_t strides[4] = {row, row * N, row * N * T, row * N * T * B};
+  return encode_tiles(tm, base, dims, strides, 3);
+}
+
+}  // namespace
+
+bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, int grad_cut) {
+  return cell == CELL_ELMAN && D == WD && !state_f32 && !(fclip > 0.f) && !(gclip > 0.f) && !grad_cut;
+}
+
+cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
+                                unsigned* status, int B, int T, int N, cudaStream_t stream) {
+  CUtensorMap tm_wx, tm_st;
+  if (!map_btgnd(&tm_wx, Wx, B, T, N) || !map_sbtnd(&tm_st, states, B, T, N)) return cudaErrorNotSupported;
+  WideFwdParams p;
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.s0 = static_cast<const __nv_bfloat16*>(s0);
+  p.status = status;
+  p.B = B; p.T = T; p.N = N;
+  cudaError_t e = cudaFuncSetAttribute(wide_fwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
+  if (e != cudaSuccess) return e;
+  wide_fwd_elman_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WF_SMEM, stream>>>(tm_wx, tm_st, p);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
+                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N,
+                                 cudaStream_t stream) {
+  CUtensorMap tm_st, tm_s0, tm_dst, tm_dwx;
+  if (!map_sbtnd(&tm_st, states, B, T, N) || !map_sbtnd(&tm_s0, s0, B, 1, N) || !map_sbtnd(&tm_dst, dstates, B, T, N) ||
+      !map_btgnd(&tm_dwx, dWx, B, T, N))
+    return cudaErrorNotSupported;
+  WideBwdParams p;
+  p.R = static_cast<const __nv_bfloat16*>(R);
+  p.ds0 = static_cast<__nv_bfloat16*>(ds0);
+  p.dR = dR;
+  p.dbias = dbias;
+  p.status = status;
+  p.B = B; p.T = T; p.N = N;
+  cudaError_t e = cudaFuncSetAttribute(wide_bwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WB_SMEM);
+  if (e != cudaSuccess) return e;
+  wide_bwd_elman_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WB_SMEM, stream>>>(tm_st, tm_s0, tm_dst,
+                                                                                                          tm_dwx, p);
+  return cudaGetLastError();
+}
+
+}  // namespace frnn

@@ -1,0 +1,45 @@
+"""GPU parity of the 128-row tensor-core time loops (Elman, head dim 64; tcgen05 + tensor memory, tensor-map bulk
+copies, dR/db accumulated inside the reverse loop) against the fp64 oracle, through the public API.
+
+The tile is forced with ``batch_tile=128`` so that small batches exercise it; ragged batches cover the rows a
+tensor-map copy clips (zero-filled loads, dropped stores)."""
+import numpy as np
+import pytest
+import torch
+
+from flashrnn_b200 import _native as nv
+from tests.util import assert_parity, make_inputs, run_native, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("B,T,N", [(128, 5, 1), (128, 1, 2), (128, 2, 1), (130, 9, 2), (37, 12, 3), (300, 33, 2)])
+def test_wide_elman_matches_oracle(cuda_device, B, T, N):
+    Wx, R, b, s0 = make_inputs("elman", B, T, N, 64, seed=B + T, random_init=True)
+    g = torch.Generator().manual_seed(7)
+    cot = torch.randn(1, B, T, N, 64, generator=g, dtype=torch.float64).to(torch.bfloat16).to(torch.float64)
+    got = run_native("elman", Wx, R, b, s0, cot=cot, batch_tile=128)
+    ref = run_oracle("elman", Wx, R, b, s0, cot=cot)
+    errs = assert_parity("elman", got, ref, tag=f"wide B{B} T{T} N{N}")
+    assert errs["h"] < 1.5e-2
+
+
+def test_wide_matches_small_tile_kernels(cuda_device):
+    """Same problem through the 8-row warp-MMA loops and through the 128-row tcgen05 loops."""
+    Wx, R, b, s0 = make_inputs("elman", 256, 64, 4, 64, seed=3)
+    a = run_native("elman", Wx, R, b, s0, batch_tile=128)
+    c = run_native("elman", Wx, R, b, s0, batch_tile=8)
+    assert np.abs(a["states"] - c["states"]).max() < 2e-2
+    for k in ("dWx", "dR", "db"):
+        den = np.linalg.norm(c[k].ravel())
+        assert np.linalg.norm((a[k] - c[k]).ravel()) / den < 1e-2, k
+
+
+def test_wide_is_the_default_for_large_batches():
+    big = nv.query(nv.make_problem("elman", 1024, 16, 16, 64, False, True))
+    assert (big.batch_tile, big.cluster_size, big.threads) == (128, 1, 160)
+    small = nv.query(nv.make_problem("elman", 64, 16, 16, 64, False, True))
+    assert small.batch_tile == 8
+    # cells / options the 128-row loops do not cover keep the small tiles
+    assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True)).batch_tile == 8
+    assert nv.query(nv.make_problem("elman", 1024, 16, 16, 64, True, True)).batch_tile == 8
