@@ -191,9 +191,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); break; }
       tc_fence_after();
       uint32_t r0[32], r1[32];
-      tmem_ld32_nowait(trow + (t & 1) * WD, r0);
-      tmem_ld32_nowait(trow + (t & 1) * WD + 32, r1);
-      tmem_ld_wait();
+      tmem_ld64(trow + (t & 1) * WD, r0, r1);
       unsigned char* dst = sm + WF_OFF_H + (t & 1) * WTILE;
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j) {
@@ -388,9 +386,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       }
       tc_fence_after();
       uint32_t r0[32], r1[32];
-      tmem_ld32_nowait(trow + (j & 1) * WD, r0);
-      tmem_ld32_nowait(trow + (j & 1) * WD + 32, r1);
-      tmem_ld_wait();
+      tmem_ld64(trow + (j & 1) * WD, r0, r1);
       const unsigned char* hsrc = sm + WB_OFF_H + (j % WB_STAGES) * WTILE;
       unsigned char* dst = sm + WB_OFF_D + (j & 1) * WTILE;
 #pragma unroll
@@ -419,9 +415,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
     if (ok && mbar_wait_bounded(&acc_full[T & 1], (uint32_t)((T >> 1) & 1))) {
       tc_fence_after();
       uint32_t r0[32], r1[32];
-      tmem_ld32_nowait(trow + (T & 1) * WD, r0);
-      tmem_ld32_nowait(trow + (T & 1) * WD + 32, r1);
-      tmem_ld_wait();
+      tmem_ld64(trow + (T & 1) * WD, r0, r1);
       const int b = b0 + tid;
       if (b < p.B) {
         uint4* out = reinterpret_cast<uint4*>(p.ds0 + ((size_t)b * p.N + n) * WD);
@@ -441,9 +435,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
     if (ok && mbar_wait_bounded(dr_done, 0)) {
       tc_fence_after();
       uint32_t r0[32], r1[32];
-      tmem_ld32_nowait(trow + 2 * WD, r0);
-      tmem_ld32_nowait(trow + 2 * WD + 32, r1);
-      tmem_ld_wait();
+      tmem_ld64(trow + 2 * WD, r0, r1);
       if (lane < 16) {
         float* out = p.dR + ((size_t)n * WD + (warp * 16 + lane)) * WD;
 #pragma unroll
