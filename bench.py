@@ -34,6 +34,7 @@ WORKLOADS = {
     "C3": ("gru", 32, 2048, 8, 128, False),
     "C4": ("slstm", 8, 4096, 4, 192, True),
     "C5": ("elman", 1024, 2048, 16, 64, False),
+    "C5s": ("elman", 1024, 256, 16, 64, False),  # C5 with T cut to 256 (2.1 GB resident): the size ncu captures use
 }
 DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm": (4, 4, 4, 4)}
 METRIC = "fwd+bwd tokens/sec (B*T/s)"

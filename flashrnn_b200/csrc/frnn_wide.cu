@@ -30,9 +30,26 @@ constexpr int WD = 64;                          // head dim
 constexpr int WM = 128;                         // batch rows per CTA = UMMA M
 constexpr uint32_t WTILE = WM * WD * 2;         // bytes of a [128][64] bf16 tile
 constexpr uint32_t WMAT = WD * WD * 2;          // bytes of a [64][64] bf16 operand
-constexpr int WF_STAGES = 6;                    // forward: Wx tiles in flight
+constexpr int WF_STAGES = 8;                    // forward: Wx tiles in flight
 constexpr int WB_STAGES = 4;                    // backward: h tiles and cotangent tiles in flight (each)
 constexpr int W_THREADS = 160;
+
+// Development aid (off in the shipped library): with -DFRNN_PROFILE one row thread (slot 0) and the issuing thread
+// (slot 1) of CTA (0,0) sum the SM clock between marks of the step loop; the sums land at bytes 64 / 128 of the status block.
+#ifdef FRNN_PROFILE
+#define WPROF_DECL(on)                                                      \
+  const bool wprof_on = (on) && blockIdx.x == 0 && blockIdx.y == 0;         \
+  long long wprof_sum[7] = {0, 0, 0, 0, 0, 0, 0};                           \
+  long long wprof_last = clock64()
+#define WPROF_MARK(i) \
+  do { if (wprof_on) { const long long c_ = clock64(); wprof_sum[i] += c_ - wprof_last; wprof_last = c_; } } while (0)
+#define WPROF_DUMP(status, slot) \
+  do { if (wprof_on) for (int i_ = 0; i_ < 7; ++i_) reinterpret_cast<long long*>(status)[8 + 8 * (slot) + i_] = wprof_sum[i_]; } while (0)
+#else
+#define WPROF_DECL(on) do { } while (0)
+#define WPROF_MARK(i) do { } while (0)
+#define WPROF_DUMP(status, slot) do { } while (0)
+#endif
 
 // byte offset of 16-byte chunk `chunk` of row `row` inside a 128-byte-swizzled tile
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
@@ -52,7 +69,7 @@ struct WideFwdParams {
 
 constexpr uint32_t WF_OFF_WX = 0;
 constexpr uint32_t WF_OFF_H = WF_OFF_WX + WF_STAGES * WTILE;
-constexpr uint32_t WF_OFF_R = WF_OFF_H + 2 * WTILE;
+constexpr uint32_t WF_OFF_R = WF_OFF_H + 3 * WTILE;  // three h tiles: h_t lives in tile t % 3
 constexpr uint32_t WF_OFF_I = WF_OFF_R + WMAT;
 constexpr uint32_t WF_OFF_ONES = WF_OFF_I + WMAT;       // A operand [128 rows][16 k], k = 0 holds 1.0 (no swizzle)
 constexpr uint32_t WF_OFF_BIAS = WF_OFF_ONES + 4096;    // B operand [64 rows][16 k], k = 0 holds b[row] (no swizzle)
@@ -94,12 +111,12 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       *reinterpret_cast<uint4*>(q) = make_uint4((uint32_t)__bfloat16_as_ushort(p.bias[(size_t)n * WD + d]), 0u, 0u, 0u);
       *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
     }
-    if (tid < WM) {  // h_{-1} -> h buffer 1 (step t reads buffer (t + 1) & 1)
+    if (tid < WM) {  // h_{-1} -> h tile 2 (step t reads tile (t + 2) % 3 and writes tile t % 3)
       const int b = b0 + tid;
       const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)(b < p.B ? b : 0) * p.N + n) * WD);
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(sm + WF_OFF_H + WTILE + sw128(tid, j)) = (b < p.B) ? src[j] : make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(sm + WF_OFF_H + 2 * WTILE + sw128(tid, j)) = (b < p.B) ? src[j] : make_uint4(0u, 0u, 0u, 0u);
     }
   }
   if (tid == 0) {
@@ -122,58 +139,74 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       const uint32_t idesc = instr_desc_bf16(WM, WD, 0, 0);
       const void* tmw = &tm_wx;
       const void* tms = &tm_states;
+      // descriptor halves: the low word carries the address (16-byte units), the high word is a constant of the layout
+      constexpr uint32_t HI = desc_hi(1024, true), HIP = desc_hi(256, false), TILE16 = WTILE >> 4;
+      const uint32_t wx_lo = (base + WF_OFF_WX) >> 4, h_lo = (base + WF_OFF_H) >> 4, r_lo = (base + WF_OFF_R) >> 4,
+                     i_lo = (base + WF_OFF_I) >> 4, ones_lo = ((base + WF_OFF_ONES) >> 4) | ((128u >> 4) << 16),
+                     bias_lo = ((base + WF_OFF_BIAS) >> 4) | ((128u >> 4) << 16);
       int loads = 0, waited = 0;  // Wx tiles requested / seen to land (both in step order)
+      int ls = 0;                 // ring slot of the next request
+      int cs = 0;                 // ring slot and barrier parity of the next tile to consume
+      uint32_t cpar = 0;
       auto load_wx = [&](int t) {
-        const int s = t % WF_STAGES;
-        mbar_arrive_expect_tx(&wx_full[s], WTILE);
-        tma_load_5d(base + WF_OFF_WX + s * WTILE, tmw, 0, n, 0, t, b0, &wx_full[s]);
+        mbar_arrive_expect_tx(&wx_full[ls], WTILE);
+        tma_load_5d(base + WF_OFF_WX + ls * WTILE, tmw, 0, n, 0, t, b0, &wx_full[ls]);
+        ls = (ls + 1 == WF_STAGES) ? 0 : ls + 1;
         ++loads;
       };
-      auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I + ones * bias
-        const uint32_t a0 = base + WF_OFF_WX + (t % WF_STAGES) * WTILE, d = tmem + (t & 1) * WD;
+      auto wait_wx = [&]() { return mbar_wait_bounded(&wx_full[cs], cpar); };
+      auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I + ones * bias, from ring slot cs
+        const uint32_t a = wx_lo + cs * TILE16, d = tmem + (t & 1) * WD;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k)
-          umma_bf16(d, smem_desc_sw128(a0 + k * 32, 0, 1024), smem_desc_sw128(base + WF_OFF_I + k * 32, 0, 1024), idesc, k);
-        umma_bf16(d, smem_desc(base + WF_OFF_ONES, 128, 256), smem_desc(base + WF_OFF_BIAS, 128, 256), idesc, 1u);
+        for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI, i_lo + 2 * k, HI, idesc, k);
+        umma_bf16_parts(d, ones_lo, HIP, bias_lo, HIP, idesc, 1u);
+        ++waited;
+        if (++cs == WF_STAGES) { cs = 0; cpar ^= 1u; }
       };
       for (int t = 0; t < T && t < WF_STAGES; ++t) load_wx(t);
-      bool ok = mbar_wait_bounded(&wx_full[0], 0);
-      if (ok) {
-        waited = 1;
-        issue_pre(0);
-      } else {
-        report_timeout(p.status, 0);
-      }
+      bool ok = wait_wx();
+      if (ok) issue_pre(0);
+      else report_timeout(p.status, 0);
+      int hr = 2;  // tile holding h_{t-1}
+      WPROF_DECL(true);
       for (int t = 0; ok && t < T; ++t) {
         if (t > 0) {
           if (!mbar_wait_bounded(h_ready, (uint32_t)((t - 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
           tc_fence_after();
         }
-        bulk_wait_group_read<0>();  // the store of h_{t-2} has left the buffer that step t's threads overwrite
-        const uint32_t a0 = base + WF_OFF_H + ((t + 1) & 1) * WTILE, d = tmem + (t & 1) * WD;
+        WPROF_MARK(0);
+        // step t's threads overwrite the tile of h_{t-3}: its store (two groups back) must have left shared memory; with
+        // three tiles the store gets two whole steps for that, and this wait is off the critical path
+        bulk_wait_group_read<1>();
+        WPROF_MARK(1);
+        const uint32_t a = h_lo + hr * TILE16, d = tmem + (t & 1) * WD;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k)
-          umma_bf16(d, smem_desc_sw128(a0 + k * 32, 0, 1024), smem_desc_sw128(base + WF_OFF_R + k * 32, 0, 1024), idesc, 1u);
+        for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc, 1u);
         umma_commit(&acc_full[t & 1]);
+        WPROF_MARK(2);
         if (t > 0) {  // h_{t-1} -> states[0][b0.., t-1, n, :]
-          tma_store_5d(tms, a0, 0, n, t - 1, b0, 0);
+          tma_store_5d(tms, base + WF_OFF_H + hr * WTILE, 0, n, t - 1, b0, 0);
           bulk_commit_group();
           // the Wx tile of step t-1 was consumed by MMAs that completed before h_{t-1} could be computed
           if (t - 1 + WF_STAGES < T) load_wx(t - 1 + WF_STAGES);
         }
+        WPROF_MARK(3);
         if (t + 1 < T) {
-          if (!mbar_wait_bounded(&wx_full[(t + 1) % WF_STAGES], (uint32_t)(((t + 1) / WF_STAGES) & 1))) {
+          if (!wait_wx()) {
             report_timeout(p.status, t);
             ok = false;
             break;
           }
-          ++waited;
+          WPROF_MARK(4);
           issue_pre(t + 1);
+          WPROF_MARK(5);
         }
+        hr = (hr == 2) ? 0 : hr + 1;
       }
+      WPROF_DUMP(p.status, 1);
       if (ok) {
         if (mbar_wait_bounded(h_ready, (uint32_t)((T - 1) & 1))) {
-          tma_store_5d(tms, base + WF_OFF_H + ((T - 1) & 1) * WTILE, 0, n, T - 1, b0, 0);
+          tma_store_5d(tms, base + WF_OFF_H + hr * WTILE, 0, n, T - 1, b0, 0);
           bulk_commit_group();
         } else {
           report_timeout(p.status, T);
@@ -187,12 +220,17 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
   } else {
     // ------------------------------------------------------------ row threads: h_t = tanh(acc)
     const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    int hw = 0;  // tile that receives h_t
+    WPROF_DECL(tid == 0);
     for (int t = 0; t < T; ++t) {
       if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); break; }
       tc_fence_after();
+      WPROF_MARK(0);
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (t & 1) * WD, r0, r1);
-      unsigned char* dst = sm + WF_OFF_H + (t & 1) * WTILE;
+      WPROF_MARK(1);
+      unsigned char* dst = sm + WF_OFF_H + hw * WTILE;
+      hw = (hw == 2) ? 0 : hw + 1;
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j) {
         float v[8];
@@ -200,10 +238,13 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         for (int i = 0; i < 8; ++i) v[i] = fast_tanh(__uint_as_float(j < 4 ? r0[j * 8 + i] : r1[(j - 4) * 8 + i]));
         *reinterpret_cast<uint4*>(dst + sw128(tid, j)) = pack8(v);
       }
+      WPROF_MARK(2);
       fence_proxy_async_smem();  // the tile is read by the tensor core and by the bulk store
       tc_fence_before();
       mbar_arrive(h_ready);
+      WPROF_MARK(3);
     }
+    WPROF_DUMP(p.status, 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -212,6 +253,43 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     tmem_dealloc(tmem, 128);
   }
 }
+
+#ifdef FRNN_WIDE_COPYONLY
+// Development aid: the streaming ceiling of the forward loop's access pattern -- every step one tile of Wx in, the same
+// tile out to `states`, no arithmetic.  Built only with -DFRNN_WIDE_COPYONLY, where it replaces the forward kernel.
+__global__ void __launch_bounds__(W_THREADS, 1)
+wide_copy_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states, const WideFwdParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_raw + (base - raw);
+  constexpr int S = 10;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sm + S * WTILE);
+  const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 128) {
+    const void* tmw = &tm_wx;
+    const void* tms = &tm_states;
+    auto load = [&](int t) {
+      mbar_arrive_expect_tx(&full[t % S], WTILE);
+      tma_load_5d(base + (t % S) * WTILE, tmw, 0, n, 0, t, b0, &full[t % S]);
+    };
+    for (int t = 0; t < T && t < S; ++t) load(t);
+    for (int t = 0; t < T; ++t) {
+      if (!mbar_wait_bounded(&full[t % S], (uint32_t)((t / S) & 1))) { report_timeout(p.status, t); break; }
+      tma_store_5d(tms, base + (t % S) * WTILE, 0, n, t, b0, 0);
+      bulk_commit_group();
+      bulk_wait_group_read<3>();  // the store issued four steps ago has left its slot
+      if (t >= 3 && t - 3 + S < T) load(t - 3 + S);
+    }
+    bulk_wait_group<0>();
+  }
+}
+#endif
 
 // ================================================================================================ backward
 struct WideBwdParams {
@@ -225,8 +303,8 @@ struct WideBwdParams {
 
 constexpr uint32_t WB_OFF_H = 0;                                  // h tiles: sequence index q <-> time T-1-q (q = T: h_{-1})
 constexpr uint32_t WB_OFF_E = WB_OFF_H + WB_STAGES * WTILE;       // cotangent tiles: sequence index j <-> time T-1-j
-constexpr uint32_t WB_OFF_D = WB_OFF_E + WB_STAGES * WTILE;       // delta tiles [2]
-constexpr uint32_t WB_OFF_R = WB_OFF_D + 2 * WTILE;               // R as [p][d] (K-major B operand of delta * R)
+constexpr uint32_t WB_OFF_D = WB_OFF_E + WB_STAGES * WTILE;       // delta tiles [3]: delta of step index j in tile j % 3
+constexpr uint32_t WB_OFF_R = WB_OFF_D + 3 * WTILE;               // R as [p][d] (K-major B operand of delta * R)
 constexpr uint32_t WB_OFF_I = WB_OFF_R + WMAT;
 constexpr uint32_t WB_OFF_DB = WB_OFF_I + WMAT;                   // float[64]
 constexpr uint32_t WB_OFF_BAR = WB_OFF_DB + 256;
@@ -307,16 +385,20 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         tma_load_5d(base + WB_OFF_E + s * WTILE, tme, 0, n, T - 1 - j, b0, 0, &e_full[s]);
         ++e_loads;
       };
+      constexpr uint32_t HI = desc_hi(1024, true), TILE16 = WTILE >> 4;  // descriptor halves as in the forward kernel
+      const uint32_t hr_lo = (base + WB_OFF_H) >> 4, er_lo = (base + WB_OFF_E) >> 4, d_lo = (base + WB_OFF_D) >> 4,
+                     r_lo = (base + WB_OFF_R) >> 4, i_lo = (base + WB_OFF_I) >> 4;
       auto issue_pre = [&](int j) {  // acc[j & 1] = dh_ext_j * I
-        const uint32_t a0 = base + WB_OFF_E + (j % WB_STAGES) * WTILE, d = tmem + (j & 1) * WD;
+        const uint32_t a = er_lo + (j % WB_STAGES) * TILE16, d = tmem + (j & 1) * WD;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k)
-          umma_bf16(d, smem_desc_sw128(a0 + k * 32, 0, 1024), smem_desc_sw128(base + WB_OFF_I + k * 32, 0, 1024), idesc_kk, k);
+        for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI, i_lo + 2 * k, HI, idesc_kk, k);
       };
       for (int q = 0; q <= T && q < WB_STAGES; ++q) load_h(q);
       for (int j = 0; j < T && j < WB_STAGES; ++j) load_e(j);
       bool ok = true;
       int where = 0;
+      int dj = 0;  // delta tile of step index j
+      WPROF_DECL(true);
       do {
         if (!mbar_wait_bounded(&e_full[0], 0)) { ok = false; break; }
         e_seen = 1;
@@ -331,26 +413,31 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           where = j;
           if (!mbar_wait_bounded(d_ready, (uint32_t)(j & 1))) { ok = false; break; }
           tc_fence_after();
+          WPROF_MARK(0);
           if (h_seen < j + 1) h_seen = j + 1;  // the row threads of step j have read h tile j
-          bulk_wait_group_read<0>();           // the store of delta_{j-1} has left the buffer step j+1 overwrites
-          const uint32_t dt = base + WB_OFF_D + (j & 1) * WTILE;
+          // step j+1 overwrites the tile of delta_{j-2}: that store (two groups back) must have left shared memory
+          bulk_wait_group_read<1>();
+          WPROF_MARK(1);
+          const uint32_t dt = base + WB_OFF_D + dj * WTILE, dl = d_lo + dj * TILE16;
           // dh accumulator of step j+1 (+)= delta_j * R; step T (the cotangent of h_{-1}) has no external part
           const uint32_t acc = tmem + ((j + 1) & 1) * WD;
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            umma_bf16(acc, smem_desc_sw128(dt + k * 32, 0, 1024), smem_desc_sw128(base + WB_OFF_R + k * 32, 0, 1024), idesc_kk,
-                      (j + 1 < T || k > 0) ? 1u : 0u);
+            umma_bf16_parts(acc, dl + 2 * k, HI, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
           umma_commit(&acc_full[(j + 1) & 1]);
+          WPROF_MARK(2);
           tma_store_5d(tmd, dt, 0, n, 0, T - 1 - j, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
           bulk_commit_group();
+          WPROF_MARK(3);
           // dR += delta_j^T * h_{t-1}  (h tile of sequence index j + 1)
           if (!mbar_wait_bounded(&h_full[(j + 1) % WB_STAGES], (uint32_t)(((j + 1) / WB_STAGES) & 1))) { ok = false; break; }
           h_seen = j + 2;
-          const uint32_t ht = base + WB_OFF_H + ((j + 1) % WB_STAGES) * WTILE;
+          WPROF_MARK(4);
+          const uint32_t hl = hr_lo + ((j + 1) % WB_STAGES) * TILE16;
 #pragma unroll
-          for (uint32_t ks = 0; ks < 8; ++ks)
-            umma_bf16(tmem + 2 * WD, smem_desc_sw128(dt + ks * 2048, 0, 1024), smem_desc_sw128(ht + ks * 2048, 0, 1024), idesc_mm,
-                      (j > 0 || ks > 0) ? 1u : 0u);
+          for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = 2048 bytes per k-step
+            umma_bf16_parts(tmem + 2 * WD, dl + 128 * ks, HI, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+          WPROF_MARK(5);
           // h tile j-1: its row threads (step j-1) and its dR MMAs (step j-2, completed before the accumulator of
           // step j was signalled) are done; cotangent tile j: consumed by MMAs that completed before step j started
           if (j >= 1 && j - 1 + WB_STAGES <= T) load_h(j - 1 + WB_STAGES);
@@ -360,8 +447,11 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
             e_seen = j + 3;
             issue_pre(j + 2);
           }
+          WPROF_MARK(6);
+          dj = (dj == 2) ? 0 : dj + 1;
         }
       } while (false);
+      WPROF_DUMP(p.status, 1);
       if (!ok) report_timeout(p.status, where);
       umma_commit(dr_done);
       for (int i = (h_seen > h_loads - WB_STAGES ? h_seen : h_loads - WB_STAGES); i < h_loads; ++i)
@@ -377,6 +467,8 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
 #pragma unroll
     for (int i = 0; i < WD; ++i) db[i] = 0.f;
     bool ok = true;
+    int dw = 0;  // tile that receives delta of step index j
+    WPROF_DECL(tid == 0);
     for (int j = 0; j < T; ++j) {
       if (!mbar_wait_bounded(&acc_full[j & 1], (uint32_t)((j >> 1) & 1)) ||
           !mbar_wait_bounded(&h_full[j % WB_STAGES], (uint32_t)((j / WB_STAGES) & 1))) {
@@ -385,10 +477,13 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         break;
       }
       tc_fence_after();
+      WPROF_MARK(0);
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (j & 1) * WD, r0, r1);
+      WPROF_MARK(1);
       const unsigned char* hsrc = sm + WB_OFF_H + (j % WB_STAGES) * WTILE;
-      unsigned char* dst = sm + WB_OFF_D + (j & 1) * WTILE;
+      unsigned char* dst = sm + WB_OFF_D + dw * WTILE;
+      dw = (dw == 2) ? 0 : dw + 1;
 #pragma unroll
       for (uint32_t c = 0; c < 8; ++c) {
         const uint32_t off = sw128(tid, c);
@@ -407,10 +502,13 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         }
         *reinterpret_cast<uint4*>(dst + off) = pack8(v);
       }
+      WPROF_MARK(2);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(d_ready);
+      WPROF_MARK(3);
     }
+    WPROF_DUMP(p.status, 0);
     // cotangent of the initial state: the accumulator of "step T"
     if (ok && mbar_wait_bounded(&acc_full[T & 1], (uint32_t)((T >> 1) & 1))) {
       tc_fence_after();
@@ -517,6 +615,12 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
   p.B = B; p.T = T; p.N = N;
   cudaError_t e = cudaFuncSetAttribute(wide_fwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
   if (e != cudaSuccess) return e;
+#ifdef FRNN_WIDE_COPYONLY
+  e = cudaFuncSetAttribute(wide_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 10 * (int)WTILE + 2048);
+  if (e != cudaSuccess) return e;
+  wide_copy_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, 10 * WTILE + 2048, stream>>>(tm_wx, tm_st, p);
+  return cudaGetLastError();
+#endif
   wide_fwd_elman_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WF_SMEM, stream>>>(tm_wx, tm_st, p);
   return cudaGetLastError();
 }
