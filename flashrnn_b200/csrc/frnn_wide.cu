@@ -306,8 +306,8 @@ constexpr uint32_t WB_OFF_E = WB_OFF_H + WB_STAGES * WTILE;       // cotangent t
 constexpr uint32_t WB_OFF_D = WB_OFF_E + WB_STAGES * WTILE;       // delta tiles [3]: delta of step index j in tile j % 3
 constexpr uint32_t WB_OFF_R = WB_OFF_D + 3 * WTILE;               // R as [p][d] (K-major B operand of delta * R)
 constexpr uint32_t WB_OFF_I = WB_OFF_R + WMAT;
-constexpr uint32_t WB_OFF_DB = WB_OFF_I + WMAT;                   // float[64]
-constexpr uint32_t WB_OFF_BAR = WB_OFF_DB + 256;
+constexpr uint32_t WB_OFF_DB = WB_OFF_I + WMAT;                   // float[4][64]: per-warp sums of db
+constexpr uint32_t WB_OFF_BAR = WB_OFF_DB + 1024;
 constexpr uint32_t WB_SMEM = WB_OFF_BAR + 8 * (2 * WB_STAGES + 4) + 16 + 1024;
 
 __global__ void __launch_bounds__(W_THREADS, 1)
@@ -318,6 +318,11 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = smem_raw + (base - raw);
+#ifdef FRNN_PROFILE
+  const bool wt_on = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0;  // wall-clock stamps at byte 192 of the status block
+  unsigned long long* wt = reinterpret_cast<unsigned long long*>(p.status) + 24;
+  if (wt_on) wt[0] = global_timer_ns();
+#endif
   float* sdb = reinterpret_cast<float*>(sm + WB_OFF_DB);
   uint64_t* h_full = reinterpret_cast<uint64_t*>(sm + WB_OFF_BAR);  // [WB_STAGES]
   uint64_t* e_full = h_full + WB_STAGES;                            // [WB_STAGES]
@@ -345,7 +350,6 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       *reinterpret_cast<uint4*>(sm + WB_OFF_I + sw128(pp, j)) =
           make_uint4(wi == 0 ? one : 0u, wi == 1 ? one : 0u, wi == 2 ? one : 0u, wi == 3 ? one : 0u);
     }
-    if (tid < WD) sdb[tid] = 0.f;
   }
   if (tid == 0) {
     for (int s = 0; s < WB_STAGES; ++s) { mbar_init(&h_full[s], 1); mbar_init(&e_full[s], 1); }
@@ -468,6 +472,9 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
     for (int i = 0; i < WD; ++i) db[i] = 0.f;
     bool ok = true;
     int dw = 0;  // tile that receives delta of step index j
+#ifdef FRNN_PROFILE
+    if (wt_on) wt[1] = global_timer_ns();
+#endif
     WPROF_DECL(tid == 0);
     for (int j = 0; j < T; ++j) {
       if (!mbar_wait_bounded(&acc_full[j & 1], (uint32_t)((j >> 1) & 1)) ||
@@ -509,6 +516,9 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       WPROF_MARK(3);
     }
     WPROF_DUMP(p.status, 0);
+#ifdef FRNN_PROFILE
+    if (wt_on) wt[2] = global_timer_ns();
+#endif
     // cotangent of the initial state: the accumulator of "step T"
     if (ok && mbar_wait_bounded(&acc_full[T & 1], (uint32_t)((T >> 1) & 1))) {
       tc_fence_after();
@@ -546,11 +556,25 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       report_timeout(p.status, T + 1);
     }
 #pragma unroll
-    for (int i = 0; i < WD; ++i) atomicAdd(&sdb[i], db[i]);  // once per kernel; static indices keep db in registers
+#ifdef FRNN_PROFILE
+    if (wt_on) wt[3] = global_timer_ns();
+#endif
+    for (int i = 0; i < WD; ++i) {  // db: sum over the 32 rows of the warp by shuffles, then one partial per warp
+      float v = db[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) sdb[warp * WD + i] = v;
+    }
+#ifdef FRNN_PROFILE
+    if (wt_on) wt[4] = global_timer_ns();
+#endif
   }
   tc_fence_before();
   __syncthreads();
-  if (tid < WD) atomicAdd(p.dbias + (size_t)n * WD + tid, sdb[tid]);
+  if (tid < WD) atomicAdd(p.dbias + (size_t)n * WD + tid, sdb[tid] + sdb[WD + tid] + sdb[2 * WD + tid] + sdb[3 * WD + tid]);
+#ifdef FRNN_PROFILE
+  if (wt_on) wt[5] = global_timer_ns();
+#endif
   if (warp == 4) {
     __syncwarp();
     tmem_dealloc(tmem, 256);
