@@ -192,6 +192,14 @@ def run_ours(args):
 
     function, B, T, N, D, f32 = WORKLOADS[args.workload]
     Gr, Gw, Gt, S = DIMS[function]
+    # --shard batch (default): every rank runs the whole workload on its own batch shard (weak scaling; one all-reduce of
+    # dR||db per step).  --shard heads: the ranks split the N independent heads of ONE workload (strong scaling, no
+    # collective: dR/db stay sharded like R/b); the tokens of the job are B*T whatever the number of ranks.
+    by_heads = args.shard == "heads" and world > 1
+    if by_heads:
+        if N % world:
+            raise SystemExit(f"--shard heads needs the {N} heads of {args.workload} to divide by {world} ranks")
+        N = N // world
     Wx, R, b, s0 = make_inputs(function, B, T, N, D, f32, dev, seed=rank)
     sdt = torch.float32 if f32 else torch.bfloat16
     esz, ssz = 2, (4 if f32 else 2)
@@ -225,7 +233,7 @@ def run_ours(args):
         if rec: rec[2].record(stream)
         nv.check("frnn_backward_parts", L.frnn_backward_parts(ctypes.byref(plan), ctypes.byref(ba), sp, 2))
         if rec: rec[3].record(stream)
-        if dist is not None:
+        if dist is not None and not by_heads:
             dist.all_reduce(grads)
         nv.check("frnn_finalize_grads", L.frnn_finalize_grads(ctypes.byref(plan), P(grads), P(dR), P(db), sp))
 
@@ -267,7 +275,8 @@ def run_ours(args):
     def e2e_step():
         w, r, bb, s = (t.to(dev, non_blocking=True) for t in hostW)
         w.requires_grad_(True); r.requires_grad_(True); bb.requires_grad_(True)
-        out, _ = flashrnn(w, r, bb, s, function=function, grad_allreduce_group=(True if dist is not None else None))
+        out, _ = flashrnn(w, r, bb, s, function=function,
+                          grad_allreduce_group=(True if dist is not None and not by_heads else None))
         loss = out[0].float().sum()
         loss.backward()
         host_out[: r.numel()].copy_(r.grad.reshape(-1), non_blocking=True)
@@ -298,18 +307,21 @@ def run_ours(args):
         return 0
 
     hbm_peak, tc_peak, which = measured_peaks()
+    tok_ranks = 1 if by_heads else world  # ranks whose tokens add up (head shards work on the same tokens)
     # algorithmic traffic of the dominant kernel (the reverse time loop): reads dstates and states, writes dWx
     bwd_bytes = E * (S * ssz + S * ssz + Gw * esz)
     fwd_bytes = E * (Gw * esz + S * ssz)
     achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
     wide = plan.batch_tile == 128  # tcgen05 loops: forward, reverse loop (with dR and db inside), cast = 3 launches per step
     line = {
-        "metric": METRIC, "value": world * B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": tok_ranks * B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if by_heads else "weak",
+        "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {function} fwd+bwd B={B} T={T} N={N} D={D} per GPU, loss=sum(h), "
-                               f"states {'f32' if f32 else 'bf16'}", "global_batch": world * B,
-                   "parallelism": f"batch-sharded x{world}, NCCL all-reduce of fp32 dR||db" if world > 1 else "single GPU",
+                               f"states {'f32' if f32 else 'bf16'}", "global_batch": tok_ranks * B,
+                   "parallelism": (f"head-sharded x{world} ({N} of {N * world} heads per GPU), no collective" if by_heads else
+                                   f"batch-sharded x{world}, NCCL all-reduce of fp32 dR||db") if world > 1 else "single GPU",
                    "tile": {"cluster_size": plan.cluster_size, "units_per_cta": plan.units_per_cta, "batch_tile": plan.batch_tile,
                             "threads": plan.threads},
                    "l2": "working set per step (Wx+states+cache+dWx > 400 MB for C2) exceeds the 126 MB L2; no explicit flush"},
@@ -323,7 +335,7 @@ def run_ours(args):
                      "tensor_frac_whole_step": (6.0 * E * Gr * D / (ms * 1e-3) / 1e12) / tc_peak,
                      "note": "streams one 16 KB tile per operand, step and CTA; HBM-bound" if wide else
                      "the serial chain of 2T dependent steps, not HBM or the tensor pipe, bounds this workload"},
-        "e2e": {"value": world * B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+        "e2e": {"value": tok_ranks * B * T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms},
         "gpu_launches": (3 if wide else 6) * args.steps,
         "clocks": clk.summary(),
@@ -346,6 +358,8 @@ def main():
     ap.add_argument("--workload", default="C2", choices=sorted(WORKLOADS))
     ap.add_argument("--cluster-size", dest="cluster_size", type=int, default=0)
     ap.add_argument("--batch-tile", dest="batch_tile", type=int, default=0)
+    ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
+                    help="N > 1 GPUs: batch shards (weak scaling, default) or head shards of one workload (strong scaling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
