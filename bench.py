@@ -272,8 +272,24 @@ def run_ours(args):
     host_out = torch.empty(gcnt, dtype=torch.bfloat16).pin_memory()
     loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
 
-    def e2e_step():
-        w, r, bb, s = (t.to(dev, non_blocking=True) for t in hostW)
+    # Inputs are double-buffered on the device: the H2D copy of step i+1 (own stream) overlaps the kernels of step i,
+    # as an input pipeline with pinned memory does; every step's inputs still cross PCIe inside the timed region.
+    copy_stream = torch.cuda.Stream(device=dev)
+    bufs = [[torch.empty_like(t) for t in (Wx, R, b, s0)] for _ in range(2)]
+    ready = [ev(), ev()]   # inputs of the slot have landed
+    free = [ev(), ev()]    # the step that used the slot has been queued behind (its kernels no longer read the inputs)
+
+    def e2e_copy(slot, after=None):
+        with torch.cuda.stream(copy_stream):
+            if after is not None:
+                copy_stream.wait_event(after)
+            for dst, src in zip(bufs[slot], hostW):
+                dst.copy_(src, non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    def e2e_compute(slot):
+        stream.wait_event(ready[slot])
+        w, r, bb, s = (t.detach() for t in bufs[slot])
         w.requires_grad_(True); r.requires_grad_(True); bb.requires_grad_(True)
         out, _ = flashrnn(w, r, bb, s, function=function,
                           grad_allreduce_group=(True if dist is not None and not by_heads else None))
@@ -282,15 +298,23 @@ def run_ours(args):
         host_out[: r.numel()].copy_(r.grad.reshape(-1), non_blocking=True)
         host_out[r.numel():].copy_(bb.grad.reshape(-1), non_blocking=True)
         loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+        free[slot].record(stream)
 
-    for _ in range(2):
-        e2e_step()
+    def e2e_run(k, start):
+        e2e_copy(0, after=start)
+        for i in range(k):
+            if i + 1 < k:
+                e2e_copy((i + 1) & 1, after=free[(i + 1) & 1] if i >= 1 else None)
+            e2e_compute(i & 1)
+
+    warm = ev()
+    warm.record(stream)
+    e2e_run(2, warm)
     barrier()
     k2 = max(1, min(args.steps, 10))
     e2, e3 = ev(), ev()
     e2.record(stream)
-    for _ in range(k2):
-        e2e_step()
+    e2e_run(k2, e2)
     e3.record(stream)
     barrier()
     e2e_ms = e2.elapsed_time(e3) / k2
