@@ -346,7 +346,11 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   // measured on B200: the tcgen05 kernel wins from head_dim 128 up (C2 0.167 vs 0.212 ms, C3 0.263 vs 0.304 ms); below,
   // the problem is HBM-bound and the warp-MMA kernel with its many small CTAs streams faster (C5 1.55 vs 3.1 ms)
   // (the tcgen05 kernel keeps a whole row tile of dR, N = D <= 256 columns, in one TMEM allocation)
-  if ((parts & FRNN_PART_DR) && pr.D >= 128 && pr.D <= 256)
+  if ((parts & FRNN_PART_DR) && pr.D >= 128 && recurrent_grad_tma_supported(pr.D, lp.state_f32))
+    // bf16 states: both operands are [64 steps][64] tiles a tensor-map copy delivers ready for the MMA (C2 0.167 -> see DESIGN)
+    e = launch_recurrent_grad_tma(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, a->dWx, ws + w.dg0, a->states, a->s0, grads,
+                                  reinterpret_cast<unsigned*>(ws), sm_count_cached(), stream);
+  else if ((parts & FRNN_PART_DR) && pr.D >= 128 && pr.D <= 256)
     e = launch_recurrent_grad_tc(pr.cell, pr.B, pr.T, pr.N, pr.D, cd.Gr, cd.Gw, lp.state_f32, a->dWx, ws + w.dg0, a->states,
                                  a->s0, grads, reinterpret_cast<unsigned*>(ws), sm_count_cached(), stream);
   else if (parts & FRNN_PART_DR)

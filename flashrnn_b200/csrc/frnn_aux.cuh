@@ -53,6 +53,11 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
 cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
                                  void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N,
                                  cudaStream_t stream);
+// dR fed by tensor-map bulk copies (frnn_dr_tma.cu): bf16 states, head dims 64 .. 256 in steps of 64
+bool recurrent_grad_tma_supported(int D, int state_f32);
+cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int Gr, int Gw, const void* dWx, const void* dg0,
+                                      const void* states, const void* s0, float* dR, unsigned* status, int sm_count,
+                                      cudaStream_t stream);
 cudaError_t launch_cast_grads(const float* src, void* dR, void* db, size_t nR, size_t nb, cudaStream_t stream);
 
 }  // namespace frnn

@@ -16,11 +16,9 @@
 // Replaces, for these shapes, FLASHRNNCellFusedForward / FLASHRNNCellFusedBackward and the dR GEMM + bias reduction that
 // follow the reverse loop (flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:146-659, flashrnn_fused_backward.cu:129-624,
 // 626-665, 1049-1058; cell: fused/elman_fused_pointwise.cuh:34-93).
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
 #include "frnn_aux.cuh"
 #include "frnn_tc.cuh"
+#include "frnn_tmap.cuh"
 
 namespace frnn {
 
@@ -582,28 +580,11 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
 }
 
 // ================================================================================================ host
-// Tensor map over a bf16 tensor seen as 5-d (extents / byte strides innermost first; dims[0] = 64 contiguous elements):
-// tiles of 64 elements x 128 entries of dimension `batch_dim`, 128-byte swizzle, out-of-range rows read as zero and
-// are dropped on stores.
+// tiles of 64 elements x 128 entries of dimension `batch_dim` of a bf16 tensor seen as 5-d
 bool encode_tiles(CUtensorMap* tm, const void* base, const uint64_t (&dims)[5], const uint64_t (&strides)[4], int batch_dim) {
-  static const PFN_cuTensorMapEncodeTiled_v12000 encode = [] {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      fn = nullptr;
-    return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
-  }();
-  if (!encode) return false;
-  cuuint64_t gdim[5], gstr[4];
-  cuuint32_t box[5], estr[5];
-  for (int i = 0; i < 5; ++i) { gdim[i] = dims[i]; box[i] = 1; estr[i] = 1; }
-  for (int i = 0; i < 4; ++i) gstr[i] = strides[i];
-  box[0] = WD;
+  uint32_t box[5] = {WD, 1, 1, 1, 1};
   box[batch_dim] = WM;
-  return encode(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(base), gdim, gstr, box, estr,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_bf16_tiles(tm, base, dims, strides, box);
 }
 
 // [B,T,1,N,64] (Wx, dWx): coordinates (0, n, 0, t, b)
