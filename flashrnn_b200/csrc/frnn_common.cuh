@@ -181,6 +181,11 @@ __device__ __forceinline__ void report_timeout(unsigned* status, int where) {
   }
 }
 
+// four consecutive fp32 values added to global memory in one reduction (16-byte aligned address)
+__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 // ------------------------------------------------------------------------------------------------ math
 // Gate nonlinearities.  Default: the hardware tanh (one MUFU op, max error ~5e-4, an order of magnitude
 // below the bf16 rounding of the stored results); sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5.

@@ -202,8 +202,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
     if (warp < 4) tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, r);
     if (row_ok && !poisoned) {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < D) atomicAdd(out + col0 + j, __uint_as_float(r[j]));
+      for (int j = 0; j < 32; j += 4)  // D is a multiple of 32 here (128, 192, 256)
+        red_add_f32x4(out + col0 + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                      __uint_as_float(r[j + 3]));
     }
   }
   tc_fence_before();

@@ -165,7 +165,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
         }
       }
 #pragma unroll
-      for (int j = 0; j < 32; ++j) atomicAdd(out + col0 + j, v[j]);
+      for (int j = 0; j < 32; j += 4) red_add_f32x4(out + col0 + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
     }
   }
   tc_fence_before();

@@ -545,9 +545,11 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       if (lane < 16) {
         float* out = p.dR + ((size_t)n * WD + (warp * 16 + lane)) * WD;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          atomicAdd(out + i, __uint_as_float(r0[i]));
-          atomicAdd(out + 32 + i, __uint_as_float(r1[i]));
+        for (int i = 0; i < 32; i += 4) {
+          red_add_f32x4(out + i, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]), __uint_as_float(r0[i + 2]),
+                        __uint_as_float(r0[i + 3]));
+          red_add_f32x4(out + 32 + i, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]), __uint_as_float(r1[i + 2]),
+                        __uint_as_float(r1[i + 3]));
         }
       }
     } else if (ok) {
