@@ -262,7 +262,7 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   if (e != cudaSuccess) return (int)e;
   if (is_wide(*plan))
     return (int)launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,
-                                    stream);
+                                    plan->test_drop_exchange, stream);
   e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
   if (e != cudaSuccess) return (int)e;
 
@@ -317,7 +317,7 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   if (is_wide(*plan)) {  // one kernel: reverse loop with dR and db accumulated inside; the dR part has nothing left to do
     if (parts & FRNN_PART_LOOP)
       e = launch_wide_backward(a->R, a->s0, a->states, a->dstates, a->dWx, a->ds0, grads, grads + nR,
-                               reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, stream);
+                               reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, plan->test_drop_exchange, stream);
     return (int)e;
   }
 

@@ -49,9 +49,9 @@ constexpr int kWideBatchTile = 128;
 constexpr int kWideThreads = 160;
 bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, int grad_cut);
 cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
-                                unsigned* status, int B, int T, int N, cudaStream_t stream);
+                                unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream);
 cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
-                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N,
+                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N, int test_drop,
                                  cudaStream_t stream);
 // dR fed by tensor-map bulk copies (frnn_dr_tma.cu): bf16 states, head dims 64 .. 256 in steps of 64
 bool recurrent_grad_tma_supported(int D, int state_f32);

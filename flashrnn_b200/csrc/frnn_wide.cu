@@ -63,6 +63,7 @@ struct WideFwdParams {
   const __nv_bfloat16* s0;    // [1,B,1,N,64]
   unsigned* status;
   int B, T, N;
+  int test_drop;  // test hook: the copy of one tile (step index 2) is announced to its barrier but never issued
 };
 
 constexpr uint32_t WF_OFF_WX = 0;
@@ -148,7 +149,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       uint32_t cpar = 0;
       auto load_wx = [&](int t) {
         mbar_arrive_expect_tx(&wx_full[ls], WTILE);
-        tma_load_5d(base + WF_OFF_WX + ls * WTILE, tmw, 0, n, 0, t, b0, &wx_full[ls]);
+        if (!(p.test_drop && t == 2)) tma_load_5d(base + WF_OFF_WX + ls * WTILE, tmw, 0, n, 0, t, b0, &wx_full[ls]);
         ls = (ls + 1 == WF_STAGES) ? 0 : ls + 1;
         ++loads;
       };
@@ -297,6 +298,7 @@ struct WideBwdParams {
   float* dbias;            // fp32 [1,N,64]
   unsigned* status;
   int B, T, N;
+  int test_drop;  // test hook: the copy of one tile (step index 2) is announced to its barrier but never issued
 };
 
 constexpr uint32_t WB_OFF_H = 0;                                  // h tiles: sequence index q <-> time T-1-q (q = T: h_{-1})
@@ -384,7 +386,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       auto load_e = [&](int j) {
         const int s = j % WB_STAGES;
         mbar_arrive_expect_tx(&e_full[s], WTILE);
-        tma_load_5d(base + WB_OFF_E + s * WTILE, tme, 0, n, T - 1 - j, b0, 0, &e_full[s]);
+        if (!(p.test_drop && j == 2)) tma_load_5d(base + WB_OFF_E + s * WTILE, tme, 0, n, T - 1 - j, b0, 0, &e_full[s]);
         ++e_loads;
       };
       constexpr uint32_t HI = desc_hi(1024, true), TILE16 = WTILE >> 4;  // descriptor halves as in the forward kernel
@@ -611,7 +613,7 @@ bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, in
 }
 
 cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
-                                unsigned* status, int B, int T, int N, cudaStream_t stream) {
+                                unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream) {
   CUtensorMap tm_wx, tm_st;
   if (!map_btgnd(&tm_wx, Wx, B, T, N) || !map_sbtnd(&tm_st, states, B, T, N)) return cudaErrorNotSupported;
   WideFwdParams p;
@@ -620,6 +622,7 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
   p.s0 = static_cast<const __nv_bfloat16*>(s0);
   p.status = status;
   p.B = B; p.T = T; p.N = N;
+  p.test_drop = test_drop;
   cudaError_t e = cudaFuncSetAttribute(wide_fwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
   if (e != cudaSuccess) return e;
 #ifdef FRNN_WIDE_COPYONLY
@@ -633,7 +636,7 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
 }
 
 cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
-                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N,
+                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N, int test_drop,
                                  cudaStream_t stream) {
   CUtensorMap tm_st, tm_s0, tm_dst, tm_dwx;
   if (!map_sbtnd(&tm_st, states, B, T, N) || !map_sbtnd(&tm_s0, s0, B, 1, N) || !map_sbtnd(&tm_dst, dstates, B, T, N) ||
@@ -646,6 +649,7 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
   p.dbias = dbias;
   p.status = status;
   p.B = B; p.T = T; p.N = N;
+  p.test_drop = test_drop;
   cudaError_t e = cudaFuncSetAttribute(wide_bwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WB_SMEM);
   if (e != cudaSuccess) return e;
   wide_bwd_elman_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WB_SMEM, stream>>>(tm_st, tm_s0, tm_dst,

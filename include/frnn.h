@@ -76,7 +76,9 @@ typedef struct frnn_plan {
   int32_t test_drop_exchange; /* TEST HOOK, leave 0.  1: CTA 0 of every cluster withholds one exchange message
                                  (forward: its h of step 1; backward: its first message) so that its peers' bounded
                                  waits expire; the kernels then finish with invalid results and report it in the
-                                 status block.  Exercises the failure-detection path without faulting the GPU.     */
+                                 status block.  With the 128-row loops (batch_tile 128): one tile copy (step index 2)
+                                 is announced to its barrier and never issued.  Exercises the failure-detection path
+                                 without faulting the GPU.                                                          */
   int32_t reserved[5];
   uint64_t cache_bytes;     /* size of the activation cache (opaque layout, tied to this plan) */
   uint64_t workspace_bytes; /* size of the scratch workspace                                  */

@@ -61,3 +61,42 @@ def test_backward_wait_expiry_sets_the_status_word(cuda_device):
     nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
     nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
     assert st.code == 0 and torch.isfinite(dWx.float()).all()
+
+
+def test_wide_loops_report_a_copy_that_never_lands(cuda_device):
+    """128-row tensor-core loops: one tile copy is announced to its barrier and never issued; the issuing thread and
+    the row threads give up after their bounded waits, drain what is in flight and report it."""
+    Wx, R, b, s0 = [t.to(cuda_device, torch.bfloat16) for t in make_inputs("elman", 128, 8, 2, 64, seed=5)]
+    bad = FlashRNNConfig(function="elman", head_dim=64, num_heads=2, batch_size=128, batch_tile=128,
+                         check_device_status=True, _test_drop_exchange=True)
+    t0 = time.time()
+    with pytest.raises(RuntimeError, match="device-side wait expired in the forward"):
+        with torch.no_grad():
+            flashrnn(Wx, R, b, s0, function="elman", config=bad)
+    assert time.time() - t0 < 20.0
+    # backward through the C ABI: clean forward first, then the reverse loop with the hook
+    B, T, _, N, D = Wx.shape
+    plan = nv.query(nv.make_problem("elman", B, T, N, D, False, True), 0, 128)
+    assert plan.batch_tile == 128
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
+    states = torch.zeros(1, B, T, N, D, device=cuda_device, dtype=torch.bfloat16)
+    cache = torch.zeros(256, device=cuda_device, dtype=torch.uint8)
+    ws = torch.zeros(int(plan.workspace_bytes), device=cuda_device, dtype=torch.uint8)
+    L = nv.lib()
+    fa = nv.FrnnFwdArgs(P(Wx), P(R), P(b), P(s0), P(states), P(cache), P(ws))
+    nv.check("frnn_forward", L.frnn_forward(ctypes.byref(plan), ctypes.byref(fa), stream))
+    st = nv.FrnnDevStatus()
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 0 and torch.isfinite(states.float()).all()
+    dst = torch.ones_like(states)
+    dWx, ds0 = torch.zeros_like(Wx), torch.zeros_like(s0)
+    ba = nv.FrnnBwdArgs(P(R), P(s0), P(states), P(cache), P(dst), P(dWx), P(ds0), P(ws))
+    plan.test_drop_exchange = 1
+    nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 1
+    plan.test_drop_exchange = 0
+    nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 0 and torch.isfinite(dWx.float()).all()
