@@ -291,11 +291,20 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   // recurrent part of dh for item i: sum of the partial products of the previous step (`pbuf` = its buffer index)
   auto recurrent_sum = [&](int i, int pbuf, float (&rec)[2]) {
     if constexpr (RS) {
-      const float* src = recv_buf + (size_t)pbuf * CS * PSL + part_it[i];
-      for (int c = 0; c < CS; ++c) {
-        const float2 v = *reinterpret_cast<const float2*>(src + (size_t)c * PSL);
-        rec[0] += v.x; rec[1] += v.y;
+      // the cluster size of this exchange scheme is a constant of the instantiation: all loads are issued before the
+      // first addition, and the additions form two short chains instead of one of CS links
+      constexpr int CSC = (RS ? MPW : 1) * Gr;
+      const float* src = recv_buf + (size_t)pbuf * CSC * PSL + part_it[i];
+      float2 v[CSC];
+#pragma unroll
+      for (int c = 0; c < CSC; ++c) v[c] = *reinterpret_cast<const float2*>(src + (size_t)c * PSL);
+      float ax = 0.f, ay = 0.f, bx = 0.f, by = 0.f;
+#pragma unroll
+      for (int c = 0; c < CSC; c += 2) {
+        ax += v[c].x; ay += v[c].y;
+        if (c + 1 < CSC) { bx += v[c + 1].x; by += v[c + 1].y; }
       }
+      rec[0] += ax + bx; rec[1] += ay + by;
     } else {
 #pragma unroll
       for (int g = 0; g < Gr; ++g) {
