@@ -382,9 +382,15 @@ __device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const __nv_bfl
 
 // Development aid (off in the shipped library): with -DFRNN_PROFILE thread 0 of CTA 0 sums the SM clock
 // between up to 7 marks of the step loop and leaves the 7 sums (u64) at byte 64 of the status block.
+#ifndef FRNN_PROF_TID
+#define FRNN_PROF_TID 0  // profiled thread and cluster rank (CTA x index)
+#endif
+#ifndef FRNN_PROF_CTA
+#define FRNN_PROF_CTA 0
+#endif
 #ifdef FRNN_PROFILE
 #define FRNN_PROF_DECL                                                                         \
-  const bool prof_on = (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0); \
+  const bool prof_on = (threadIdx.x == FRNN_PROF_TID && blockIdx.x == FRNN_PROF_CTA && blockIdx.y == 0 && blockIdx.z == 0); \
   long long prof_sum[7] = {0, 0, 0, 0, 0, 0, 0};                                               \
   long long prof_last = clock64()
 #define FRNN_PROF_MARK(i)                                                                      \
