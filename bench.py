@@ -40,7 +40,7 @@ DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm
 METRIC = "fwd+bwd tokens/sec (B*T/s)"
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the reverse time loop, from an `ncu --set full` capture
 # of this command on a B200 (summary: profiles/ncu_full_C2_kernels.md).  Only workloads that were captured are listed.
-NCU_TRAFFIC_BYTES = {"C2": 237_058_816 + 107_600_128}
+NCU_TRAFFIC_BYTES = {"C2": 237_129_984 + 105_455_360}
 
 
 def measured_peaks():
