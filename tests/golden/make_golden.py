@@ -47,7 +47,7 @@ def make_inputs(function, B, T, N, D, random_init, dtype, seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds flashrnn/)")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
