@@ -271,7 +271,7 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   if (is_wide(*plan))
     return (int)launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,
                                     plan->test_drop_exchange, stream);
-  e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
+  if (!plan->keep_packed_r) e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
   if (e != cudaSuccess) return (int)e;
 
   LoopParams lp = {};

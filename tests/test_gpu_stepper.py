@@ -1,0 +1,76 @@
+"""GPU: step-by-step decoding through FlashRNNStepper equals the full-sequence forward of the same inputs, for every
+cell, with one-step and multi-step chunks, and when the step is replayed from a CUDA graph.  Inside one launch the
+cell states that do not feed the matrix product (c, n, m) are carried in fp32 registers and only their stored copy is
+rounded; across launches they pass through the state tensor.  So with float32 states the comparison is bit-exact, and
+with bfloat16 states it holds to bfloat16 rounding."""
+import pytest
+import torch
+
+from flashrnn_b200 import FlashRNNStepper, flashrnn
+from tests.util import make_inputs
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(function, B, T, N, D, dev, seed):
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=seed, random_init=True)
+    to = lambda x: x.to(torch.bfloat16).to(dev).contiguous()
+    return to(Wx), to(R), to(b), to(s0)
+
+
+@pytest.mark.parametrize("function", ["lstm", "gru", "elman", "slstm"])
+@pytest.mark.parametrize("chunk", [1, 4])
+@pytest.mark.parametrize("dtype_s", ["float32", "bfloat16"])
+def test_stepper_equals_full_sequence(cuda_device, function, chunk, dtype_s):
+    B, T, N, D = 16, 12, 3, 64
+    Wx, R, b, s0 = _inputs(function, B, T, N, D, cuda_device, seed=11)
+    exact = dtype_s == "float32"
+    if exact:
+        s0 = s0.float()
+    with torch.no_grad():
+        full, last = flashrnn(Wx, R, b, states=s0, function=function)
+    assert full.dtype == s0.dtype
+    st = FlashRNNStepper(R, b, function=function, batch_size=B, chunk=chunk, dtype_s=dtype_s, states=s0)
+    for t in range(0, T, chunk):
+        out = st.step(Wx[:, t:t + chunk].contiguous())
+        ref = full[:, :, t:t + chunk]
+        if exact:
+            assert torch.equal(out, ref), (function, chunk, t)
+        else:
+            torch.testing.assert_close(out.float(), ref.float(), atol=3e-2, rtol=3e-2)
+    if exact:
+        assert torch.equal(st.states, last)
+    st.reset()
+    assert float(st.states.abs().max()) == 0.0
+
+
+def test_stepper_replays_from_a_cuda_graph(cuda_device):
+    B, T, N, D = 8, 10, 4, 128
+    Wx, R, b, s0 = _inputs("lstm", B, T, N, D, cuda_device, seed=5)
+    s0 = s0.float()
+    with torch.no_grad():
+        full, _ = flashrnn(Wx, R, b, states=s0, function="lstm")
+    st = FlashRNNStepper(R, b, function="lstm", batch_size=B, dtype_s="float32", states=s0)
+    x = torch.empty_like(Wx[:, :1]).contiguous()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):       # first call packs R; done outside the graph
+        x.copy_(Wx[:, :1])
+        st.step(x)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = st.step(x)
+    st.reset(s0)
+    for t in range(T):
+        x.copy_(Wx[:, t:t + 1])
+        graph.replay()
+        assert torch.equal(out, full[:, :, t:t + 1]), t
+
+
+def test_stepper_refuses_wrong_shapes(cuda_device):
+    _, R, b, _ = _inputs("gru", 4, 1, 2, 64, cuda_device, seed=1)
+    st = FlashRNNStepper(R, b, function="gru", batch_size=4)
+    with pytest.raises(ValueError):
+        st.step(torch.zeros(4, 2, 3, 2, 64, dtype=torch.bfloat16, device=cuda_device))
+    with pytest.raises(ValueError):
+        FlashRNNStepper(R, b, function="lstm", batch_size=4)
