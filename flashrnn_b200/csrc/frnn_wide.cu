@@ -52,6 +52,12 @@ constexpr int W_THREADS = 160;
 // byte offset of 16-byte chunk `chunk` of row `row` inside a 128-byte-swizzled tile
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
 
+// the same inside a two-step buffer, where the 8-row groups of the two tiles interleave (group g of the tile in slot s at
+// g * 2048 + s * 1024): how a tensor-map box of [16 groups][2 steps][8 rows][128 bytes] lands in shared memory
+__device__ __forceinline__ uint32_t sw128_pair(uint32_t row, uint32_t chunk, uint32_t slot) {
+  return (row >> 3) * 2048u + slot * 1024u + (row & 7u) * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+
 __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
   return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
 }
@@ -68,13 +74,16 @@ struct WideFwdParams {
 
 constexpr uint32_t WF_OFF_WX = 0;
 constexpr uint32_t WF_OFF_H = WF_OFF_WX + WF_STAGES * WTILE;
-constexpr uint32_t WF_OFF_R = WF_OFF_H + 3 * WTILE;  // three h tiles: h_t lives in tile t % 3
+constexpr uint32_t WF_OFF_R = WF_OFF_H + 4 * WTILE;  // h tiles: h_t lives in tile t % 3, or in slot t & 1 of one of two two-step buffers
 constexpr uint32_t WF_OFF_I = WF_OFF_R + WMAT;
 constexpr uint32_t WF_OFF_ONES = WF_OFF_I + WMAT;       // A operand [128 rows][16 k], k = 0 holds 1.0 (no swizzle)
 constexpr uint32_t WF_OFF_BIAS = WF_OFF_ONES + 4096;    // B operand [64 rows][16 k], k = 0 holds b[row] (no swizzle)
 constexpr uint32_t WF_OFF_BAR = WF_OFF_BIAS + 2048;
 constexpr uint32_t WF_SMEM = WF_OFF_BAR + 8 * (WF_STAGES + 3) + 16 + 1024;  // + slack for the 1024-byte alignment
 
+// PAIR: every bulk copy moves two time steps of 8-row groups (maps of map_pairs): each batch row is its own 2 MB page
+// (rows lie T*N*128 bytes apart), and touching a page twice in a row halves the address translations that miss.
+template <bool PAIR>
 __global__ void __launch_bounds__(W_THREADS, 1)
 wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states,
                       const WideFwdParams p) {
@@ -110,12 +119,13 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       *reinterpret_cast<uint4*>(q) = make_uint4((uint32_t)__bfloat16_as_ushort(p.bias[(size_t)n * WD + d]), 0u, 0u, 0u);
       *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
     }
-    if (tid < WM) {  // h_{-1} -> h tile 2 (step t reads tile (t + 2) % 3 and writes tile t % 3)
+    if (tid < WM) {  // h_{-1} -> h tile 2 (step t reads tile (t + 2) % 3 and writes tile t % 3); PAIR: slot 1 of buffer 0
       const int b = b0 + tid;
       const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)(b < p.B ? b : 0) * p.N + n) * WD);
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j)
-        *reinterpret_cast<uint4*>(sm + WF_OFF_H + 2 * WTILE + sw128(tid, j)) = (b < p.B) ? src[j] : make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(sm + WF_OFF_H + (PAIR ? sw128_pair(tid, j, 1) : 2 * WTILE + sw128(tid, j))) =
+            (b < p.B) ? src[j] : make_uint4(0u, 0u, 0u, 0u);
     }
   }
   if (tid == 0) {
@@ -143,6 +153,71 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       const uint32_t wx_lo = (base + WF_OFF_WX) >> 4, h_lo = (base + WF_OFF_H) >> 4, r_lo = (base + WF_OFF_R) >> 4,
                      i_lo = (base + WF_OFF_I) >> 4, ones_lo = ((base + WF_OFF_ONES) >> 4) | ((128u >> 4) << 16),
                      bias_lo = ((base + WF_OFF_BIAS) >> 4) | ((128u >> 4) << 16);
+      if constexpr (PAIR) {
+        // h_t: buffer ((t + 2) >> 1) & 1, slot t & 1;  Wx_t: buffer (t >> 1) % NP, slot t & 1
+        constexpr uint32_t HI2 = desc_hi(2048, true), PAIR16 = (2 * WTILE) >> 4, SLOT16 = 1024 >> 4;
+        constexpr int NP = WF_STAGES / 2;
+        const int P = (T + 1) >> 1, bh = b0 >> 3;
+        int loads = 0, seen = 0;  // two-step boxes of Wx requested / seen to land
+        auto load_pair = [&](int q) {
+          const int s = q % NP;
+          mbar_arrive_expect_tx(&wx_full[s], 2 * WTILE);
+          if (!(p.test_drop && q == 1)) tma_load_5d(base + WF_OFF_WX + s * 2 * WTILE, tmw, 0, 0, 2 * q, bh, n, &wx_full[s]);
+          ++loads;
+        };
+        auto wait_pair = [&](int q) {
+          if (!mbar_wait_bounded(&wx_full[q % NP], (uint32_t)((q / NP) & 1))) return false;
+          seen = q + 1;
+          return true;
+        };
+        auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I + ones * bias
+          const uint32_t a = wx_lo + ((t >> 1) % NP) * PAIR16 + (t & 1) * SLOT16, d = tmem + (t & 1) * WD;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI2, i_lo + 2 * k, HI, idesc, k);
+          umma_bf16_parts(d, ones_lo, HIP, bias_lo, HIP, idesc, 1u);
+        };
+        for (int q = 0; q < P && q < NP; ++q) load_pair(q);
+        bool ok = wait_pair(0);
+        if (ok) issue_pre(0);
+        else report_timeout(p.status, 0);
+        for (int t = 0; ok && t < T; ++t) {
+          if (t > 0) {
+            if (!mbar_wait_bounded(h_ready, (uint32_t)((t - 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
+            tc_fence_after();
+          }
+          // steps t and t+1 (t even) overwrite the buffer of h_{t-4}, h_{t-3}, whose store was issued two steps ago
+          if (!(t & 1)) bulk_wait_group_read<0>();
+          const uint32_t hb = (uint32_t)((t + 1) >> 1) & 1u;  // buffer of h_{t-1}
+          const uint32_t a = h_lo + hb * PAIR16 + ((t - 1) & 1) * SLOT16, d = tmem + (t & 1) * WD;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI2, r_lo + 2 * k, HI, idesc, 1u);
+          umma_commit(&acc_full[t & 1]);
+          if (t > 0 && !(t & 1)) {
+            // h_{t-2}, h_{t-1} -> states[0][b0.., t-2 .. t-1, n, :]; the Wx box of those steps was consumed by MMAs that
+            // completed before h_{t-1} could be computed
+            tma_store_5d(tms, base + WF_OFF_H + hb * 2 * WTILE, 0, 0, t - 2, bh, n);
+            bulk_commit_group();
+            const int q = (t >> 1) - 1 + NP;
+            if (q < P) load_pair(q);
+          }
+          if (t + 1 < T) {
+            if (!((t + 1) & 1) && !wait_pair((t + 1) >> 1)) { report_timeout(p.status, t); ok = false; break; }
+            issue_pre(t + 1);
+          }
+        }
+        if (ok) {
+          if (mbar_wait_bounded(h_ready, (uint32_t)((T - 1) & 1))) {
+            // the last box: steps T-2, T-1, or step T-1 alone (T odd; the store clips the second tile)
+            tma_store_5d(tms, base + WF_OFF_H + ((uint32_t)((T + 1) >> 1) & 1u) * 2 * WTILE, 0, 0, (T - 1) & ~1, bh, n);
+            bulk_commit_group();
+          } else {
+            report_timeout(p.status, T);
+          }
+        }
+        for (int i = (seen > loads - NP ? seen : loads - NP); i < loads; ++i)
+          mbar_wait_bounded(&wx_full[i % NP], (uint32_t)((i / NP) & 1));
+        bulk_wait_group<0>();
+      } else {
       int loads = 0, waited = 0;  // Wx tiles requested / seen to land (both in step order)
       int ls = 0;                 // ring slot of the next request
       int cs = 0;                 // ring slot and barrier parity of the next tile to consume
@@ -215,6 +290,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       for (int i = (waited > loads - WF_STAGES ? waited : loads - WF_STAGES); i < loads; ++i)
         mbar_wait_bounded(&wx_full[i % WF_STAGES], (uint32_t)((i / WF_STAGES) & 1));
       bulk_wait_group<0>();
+      }
     }
   } else {
     // ------------------------------------------------------------ row threads: h_t = tanh(acc)
@@ -228,14 +304,14 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (t & 1) * WD, r0, r1);
       WPROF_MARK(1);
-      unsigned char* dst = sm + WF_OFF_H + hw * WTILE;
+      unsigned char* dst = sm + WF_OFF_H + (PAIR ? (uint32_t)((t + 2) >> 1 & 1) * 2 * WTILE : hw * WTILE);
       hw = (hw == 2) ? 0 : hw + 1;
 #pragma unroll
       for (uint32_t j = 0; j < 8; ++j) {
         float v[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = fast_tanh(__uint_as_float(j < 4 ? r0[j * 8 + i] : r1[(j - 4) * 8 + i]));
-        *reinterpret_cast<uint4*>(dst + sw128(tid, j)) = pack8(v);
+        *reinterpret_cast<uint4*>(dst + (PAIR ? sw128_pair(tid, j, t & 1) : sw128(tid, j))) = pack8(v);
       }
       WPROF_MARK(2);
       fence_proxy_async_smem();  // the tile is read by the tensor core and by the bulk store
@@ -303,13 +379,19 @@ struct WideBwdParams {
 
 constexpr uint32_t WB_OFF_H = 0;                                  // h tiles: sequence index q <-> time T-1-q (q = T: h_{-1})
 constexpr uint32_t WB_OFF_E = WB_OFF_H + WB_STAGES * WTILE;       // cotangent tiles: sequence index j <-> time T-1-j
-constexpr uint32_t WB_OFF_D = WB_OFF_E + WB_STAGES * WTILE;       // delta tiles [3]: delta of step index j in tile j % 3
-constexpr uint32_t WB_OFF_R = WB_OFF_D + 3 * WTILE;               // R as [p][d] (K-major B operand of delta * R)
+constexpr uint32_t WB_OFF_D = WB_OFF_E + WB_STAGES * WTILE;       // delta tiles: step index j in tile j % 3, or (PAIR) time t in
+                                                                  // slot t & 1 of two-step buffer (t >> 1) & 1
+constexpr uint32_t WB_OFF_R = WB_OFF_D + 4 * WTILE;               // R as [p][d] (K-major B operand of delta * R)
 constexpr uint32_t WB_OFF_I = WB_OFF_R + WMAT;
 constexpr uint32_t WB_OFF_DB = WB_OFF_I + WMAT;                   // float[4][64]: per-warp sums of db
 constexpr uint32_t WB_OFF_BAR = WB_OFF_DB + 1024;
-constexpr uint32_t WB_SMEM = WB_OFF_BAR + 8 * (2 * WB_STAGES + 4) + 16 + 1024;
+constexpr uint32_t WB_SMEM = WB_OFF_BAR + 8 * (2 * WB_STAGES + 8) + 16 + 1024;
 
+// MODE 0: one time step per bulk copy.  MODE 1: the deltas of two time steps leave in one bulk store (map of map_pairs,
+// see the forward kernel).  MODE 2: the h tiles and cotangent tiles arrive two time steps per copy as well; box r of
+// either sequence holds times 2p, 2p+1 with p = P-1-r (P = ceil(T/2)) in slot time & 1 of buffer r & 1, and box P of the
+// h sequence is h_{-1} (one tile, plain layout).
+template <int MODE>
 __global__ void __launch_bounds__(W_THREADS, 1)
 wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __grid_constant__ CUtensorMap tm_s0,
                       const __grid_constant__ CUtensorMap tm_dstates, const __grid_constant__ CUtensorMap tm_dwx,
@@ -323,13 +405,16 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
   unsigned long long* wt = reinterpret_cast<unsigned long long*>(p.status) + 24;
   if (wt_on) wt[0] = global_timer_ns();
 #endif
+  constexpr bool PAIR = MODE >= 1, PAIRL = MODE == 2;
   float* sdb = reinterpret_cast<float*>(sm + WB_OFF_DB);
   uint64_t* h_full = reinterpret_cast<uint64_t*>(sm + WB_OFF_BAR);  // [WB_STAGES]
   uint64_t* e_full = h_full + WB_STAGES;                            // [WB_STAGES]
   uint64_t* acc_full = e_full + WB_STAGES;                          // [2]
   uint64_t* d_ready = acc_full + 2;                                 // 128 arrivals: delta tile written
   uint64_t* dr_done = d_ready + 1;                                  // all dR MMAs have completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dr_done + 1);
+  uint64_t* h_free = dr_done + 1;                                   // [2] MODE 2: the MMAs that read h buffer x have completed
+  uint64_t* e_free = h_free + 2;                                    // [2] MODE 2: ... cotangent buffer x ...
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(e_free + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T;
@@ -357,6 +442,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
     mbar_init(&acc_full[1], 1);
     mbar_init(d_ready, WM);
     mbar_init(dr_done, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&h_free[s], 1); mbar_init(&e_free[s], 1); }
     fence_mbar_init();
   }
   if (warp == 4) tmem_alloc(tmem_slot, 256);  // columns [0,128): two dh accumulators; [128,192): dR
@@ -375,6 +461,130 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       const void* tm0 = &tm_s0;
       const void* tme = &tm_dstates;
       const void* tmd = &tm_dwx;
+      if constexpr (PAIRL) {
+        constexpr uint32_t HI = desc_hi(1024, true), HI2 = desc_hi(2048, true), PAIR16 = (2 * WTILE) >> 4;
+        const uint32_t hr_lo = (base + WB_OFF_H) >> 4, er_lo = (base + WB_OFF_E) >> 4, d_lo = (base + WB_OFF_D) >> 4,
+                       r_lo = (base + WB_OFF_R) >> 4, i_lo = (base + WB_OFF_I) >> 4;
+        const int P = (T + 1) >> 1, bh = b0 >> 3;
+        int h_loads = 0, h_seen = 0, e_loads = 0, e_seen = 0;  // boxes requested / known to have landed
+        auto load_h = [&](int r) {
+          const int s = r & 1;
+          if (r < P) {
+            mbar_arrive_expect_tx(&h_full[s], 2 * WTILE);
+            tma_load_5d(base + WB_OFF_H + s * 2 * WTILE, tmh, 0, 0, 2 * (P - 1 - r), bh, n, &h_full[s]);
+          } else {
+            mbar_arrive_expect_tx(&h_full[s], WTILE);
+            tma_load_5d(base + WB_OFF_H + s * 2 * WTILE, tm0, 0, n, 0, b0, 0, &h_full[s]);
+          }
+          ++h_loads;
+        };
+        auto load_e = [&](int r) {
+          const int s = r & 1;
+          mbar_arrive_expect_tx(&e_full[s], 2 * WTILE);
+          if (!(p.test_drop && r == 1)) tma_load_5d(base + WB_OFF_E + s * 2 * WTILE, tme, 0, 0, 2 * (P - 1 - r), bh, n, &e_full[s]);
+          ++e_loads;
+        };
+        auto wait_h = [&](int r) {
+          if (r < h_seen) return true;
+          if (!mbar_wait_bounded(&h_full[r & 1], (uint32_t)((r >> 1) & 1))) return false;
+          h_seen = r + 1;
+          return true;
+        };
+        auto wait_e = [&](int r) {
+          if (r < e_seen) return true;
+          if (!mbar_wait_bounded(&e_full[r & 1], (uint32_t)((r >> 1) & 1))) return false;
+          e_seen = r + 1;
+          return true;
+        };
+        int e_reload = -1;  // cotangent box whose last tile went into an accumulator during the previous iteration
+        auto issue_pre = [&](int j) {  // acc[j & 1] = dh_ext(time T-1-j) * I
+          const int te = T - 1 - j, r = P - 1 - (te >> 1);
+          const uint32_t a = er_lo + (uint32_t)(r & 1) * PAIR16 + (uint32_t)(te & 1) * 64u, d = tmem + (j & 1) * WD;
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI2, i_lo + 2 * k, HI, idesc_kk, k);
+          if (!(te & 1)) {  // both tiles of the box are consumed once these MMAs complete
+            umma_commit(&e_free[r & 1]);
+            e_reload = r;
+          }
+        };
+        auto reload_e = [&]() {  // hand the buffer of a consumed box to the box two ahead
+          if (e_reload < 0) return true;
+          if (!mbar_wait_bounded(&e_free[e_reload & 1], (uint32_t)((e_reload >> 1) & 1))) return false;
+          if (e_reload + 2 < P) load_e(e_reload + 2);
+          e_reload = -1;
+          return true;
+        };
+        load_h(0);
+        load_h(1);  // box P (h_{-1}) when T <= 2
+        load_e(0);
+        if (P > 1) load_e(1);
+        bool ok = true;
+        int where = 0;
+        // T odd: h box 0 holds h_{T-1} only, which no MMA reads; give its buffer the completion the later boxes get
+        if (T & 1) umma_commit(&h_free[0]);
+        do {
+          if (!wait_e(0)) { ok = false; break; }
+          issue_pre(0);
+          umma_commit(&acc_full[0]);  // step 0 (t = T-1) has no recurrent part
+          if (T > 1) {
+            if (!wait_e(P - 1 - ((T - 2) >> 1))) { ok = false; break; }
+            issue_pre(1);
+          }
+          for (int j = 0; j < T; ++j) {
+            where = j;
+            if (!mbar_wait_bounded(d_ready, (uint32_t)(j & 1))) { ok = false; break; }
+            tc_fence_after();
+            const int tt = T - 1 - j;  // time of step index j
+            // time tt-1 lands where time tt+3 was: stored at time tt+3 (tt odd, one younger store) or tt+2 (the youngest)
+            if (tt & 1) bulk_wait_group_read<1>();
+            else bulk_wait_group_read<0>();
+            const uint32_t dbuf = (uint32_t)((tt >> 1) & 1) * 2 * WTILE;
+            const uint32_t dt = base + WB_OFF_D + dbuf, dl = d_lo + (dbuf >> 4) + (uint32_t)(tt & 1) * 64u;
+            // dh accumulator of step j+1 (+)= delta_j * R; step T (the cotangent of h_{-1}) has no external part
+            const uint32_t acc = tmem + ((j + 1) & 1) * WD;
+#pragma unroll
+            for (uint32_t k = 0; k < 4; ++k)
+              umma_bf16_parts(acc, dl + 2 * k, HI2, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
+            umma_commit(&acc_full[(j + 1) & 1]);
+            if (!(tt & 1)) {  // deltas of times tt, tt+1 -> dWx[b0.., tt .. tt+1, 0, n, :] (tt = T-1: the second tile is clipped)
+              tma_store_5d(tmd, dt, 0, 0, tt, bh, n);
+              bulk_commit_group();
+              // the h box of times tt, tt+1: its row threads are done (step j), and so are the dR MMAs that read it (the
+              // last ones were issued in iteration j-1 and committed to h_free)
+              const int r = P - 1 - (tt >> 1);
+              if (!mbar_wait_bounded(&h_free[r & 1], (uint32_t)((r >> 1) & 1))) { ok = false; break; }
+              if (r + 2 <= P) load_h(r + 2);
+            }
+            // dR += delta_j^T * h_{tt-1}
+            const int rq = tt >= 1 ? P - 1 - ((tt - 1) >> 1) : P;
+            if (!wait_h(rq)) { ok = false; break; }
+            if (tt >= 1) {
+              const uint32_t hl = hr_lo + (uint32_t)(rq & 1) * PAIR16 + (uint32_t)((tt - 1) & 1) * 64u;
+#pragma unroll
+              for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = two 8-row groups, 4096 bytes apart per k-step
+                umma_bf16_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 256 * ks, HI2, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+              if (!((tt - 1) & 1)) umma_commit(&h_free[rq & 1]);  // that was the last read of the box by an MMA
+            } else {
+              const uint32_t hl = hr_lo + (uint32_t)(rq & 1) * PAIR16;
+#pragma unroll
+              for (uint32_t ks = 0; ks < 8; ++ks)
+                umma_bf16_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+            }
+            if (!reload_e()) { ok = false; break; }
+            if (j + 2 < T) {
+              if (!wait_e(P - 1 - ((tt - 2) >> 1))) { ok = false; break; }
+              issue_pre(j + 2);
+            }
+          }
+        } while (false);
+        if (!ok) report_timeout(p.status, where);
+        umma_commit(dr_done);
+        for (int i = (h_seen > h_loads - 2 ? h_seen : h_loads - 2); i < h_loads; ++i)
+          mbar_wait_bounded(&h_full[i & 1], (uint32_t)((i >> 1) & 1));
+        for (int i = (e_seen > e_loads - 2 ? e_seen : e_loads - 2); i < e_loads; ++i)
+          mbar_wait_bounded(&e_full[i & 1], (uint32_t)((i >> 1) & 1));
+        bulk_wait_group<0>();
+      } else {
       int h_loads = 0, h_seen = 0, e_loads = 0, e_seen = 0;  // tiles requested / known to have landed, in sequence order
       auto load_h = [&](int q) {
         const int s = q % WB_STAGES;
@@ -390,6 +600,8 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         ++e_loads;
       };
       constexpr uint32_t HI = desc_hi(1024, true), TILE16 = WTILE >> 4;  // descriptor halves as in the forward kernel
+      constexpr uint32_t HID = PAIR ? desc_hi(2048, true) : HI;          // delta tiles: 8-row groups 2048 bytes apart if PAIR
+      constexpr uint32_t DKS = PAIR ? 256u : 128u;                       // 16 rows of a delta tile, in 16-byte units
       const uint32_t hr_lo = (base + WB_OFF_H) >> 4, er_lo = (base + WB_OFF_E) >> 4, d_lo = (base + WB_OFF_D) >> 4,
                      r_lo = (base + WB_OFF_R) >> 4, i_lo = (base + WB_OFF_I) >> 4;
       auto issue_pre = [&](int j) {  // acc[j & 1] = dh_ext_j * I
@@ -420,18 +632,33 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           WPROF_MARK(0);
           if (h_seen < j + 1) h_seen = j + 1;  // the row threads of step j have read h tile j
           // step j+1 overwrites the tile of delta_{j-2}: that store (two groups back) must have left shared memory
-          bulk_wait_group_read<1>();
+          const int tt = T - 1 - j;  // time of step index j
+          if constexpr (PAIR) {
+            // time tt-1 lands where time tt+3 was: stored at time tt+3 (tt odd, one younger store) or tt+2 (the youngest)
+            if (tt & 1) bulk_wait_group_read<1>();
+            else bulk_wait_group_read<0>();
+          } else {
+            bulk_wait_group_read<1>();
+          }
           WPROF_MARK(1);
-          const uint32_t dt = base + WB_OFF_D + dj * WTILE, dl = d_lo + dj * TILE16;
+          const uint32_t dbuf = PAIR ? (uint32_t)((tt >> 1) & 1) * 2 * WTILE : dj * WTILE;
+          const uint32_t dt = base + WB_OFF_D + dbuf, dl = d_lo + (dbuf >> 4) + (PAIR ? (uint32_t)(tt & 1) * 64u : 0u);
           // dh accumulator of step j+1 (+)= delta_j * R; step T (the cotangent of h_{-1}) has no external part
           const uint32_t acc = tmem + ((j + 1) & 1) * WD;
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            umma_bf16_parts(acc, dl + 2 * k, HI, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
+            umma_bf16_parts(acc, dl + 2 * k, HID, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
           umma_commit(&acc_full[(j + 1) & 1]);
           WPROF_MARK(2);
-          tma_store_5d(tmd, dt, 0, n, 0, T - 1 - j, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
-          bulk_commit_group();
+          if constexpr (PAIR) {
+            if (!(tt & 1)) {  // deltas of times tt, tt+1 -> dWx[b0.., tt .. tt+1, 0, n, :] (tt = T-1: the second tile is clipped)
+              tma_store_5d(tmd, dt, 0, 0, tt, b0 >> 3, n);
+              bulk_commit_group();
+            }
+          } else {
+            tma_store_5d(tmd, dt, 0, n, 0, tt, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
+            bulk_commit_group();
+          }
           WPROF_MARK(3);
           // dR += delta_j^T * h_{t-1}  (h tile of sequence index j + 1)
           if (!mbar_wait_bounded(&h_full[(j + 1) % WB_STAGES], (uint32_t)(((j + 1) / WB_STAGES) & 1))) { ok = false; break; }
@@ -440,7 +667,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           const uint32_t hl = hr_lo + ((j + 1) % WB_STAGES) * TILE16;
 #pragma unroll
           for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = 2048 bytes per k-step
-            umma_bf16_parts(tmem + 2 * WD, dl + 128 * ks, HI, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+            umma_bf16_parts(tmem + 2 * WD, dl + DKS * ks, HID, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
           WPROF_MARK(5);
           // h tile j-1: its row threads (step j-1) and its dR MMAs (step j-2, completed before the accumulator of
           // step j was signalled) are done; cotangent tile j: consumed by MMAs that completed before step j started
@@ -463,6 +690,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       for (int i = (e_seen > e_loads - WB_STAGES ? e_seen : e_loads - WB_STAGES); i < e_loads; ++i)
         mbar_wait_bounded(&e_full[i % WB_STAGES], (uint32_t)((i / WB_STAGES) & 1));
       bulk_wait_group<0>();
+      }
     }
   } else {
     // ------------------------------------------------------------ row threads: delta_t = dh_t * (1 - h_t^2)
@@ -477,8 +705,10 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
 #endif
     WPROF_DECL(tid == 0);
     for (int j = 0; j < T; ++j) {
+      const int tt = T - 1 - j, hr = ((T + 1) >> 1) - 1 - (tt >> 1);  // time of the step; MODE 2: its h box
       if (!mbar_wait_bounded(&acc_full[j & 1], (uint32_t)((j >> 1) & 1)) ||
-          !mbar_wait_bounded(&h_full[j % WB_STAGES], (uint32_t)((j / WB_STAGES) & 1))) {
+          !(PAIRL ? mbar_wait_bounded(&h_full[hr & 1], (uint32_t)((hr >> 1) & 1))
+                  : mbar_wait_bounded(&h_full[j % WB_STAGES], (uint32_t)((j / WB_STAGES) & 1)))) {
         report_timeout(p.status, j);
         ok = false;
         break;
@@ -488,13 +718,13 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (j & 1) * WD, r0, r1);
       WPROF_MARK(1);
-      const unsigned char* hsrc = sm + WB_OFF_H + (j % WB_STAGES) * WTILE;
-      unsigned char* dst = sm + WB_OFF_D + dw * WTILE;
+      const unsigned char* hsrc = sm + WB_OFF_H + (PAIRL ? (uint32_t)(hr & 1) * 2 * WTILE : (j % WB_STAGES) * WTILE);
+      unsigned char* dst = sm + WB_OFF_D + (PAIR ? (uint32_t)((tt >> 1) & 1) * 2 * WTILE : dw * WTILE);
       dw = (dw == 2) ? 0 : dw + 1;
 #pragma unroll
       for (uint32_t c = 0; c < 8; ++c) {
         const uint32_t off = sw128(tid, c);
-        const uint4 hv = *reinterpret_cast<const uint4*>(hsrc + off);
+        const uint4 hv = *reinterpret_cast<const uint4*>(hsrc + (PAIRL ? sw128_pair(tid, c, tt & 1) : off));
         const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
         float v[8];
 #pragma unroll
@@ -507,7 +737,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           db[c * 8 + 2 * i] += v[2 * i];
           db[c * 8 + 2 * i + 1] += v[2 * i + 1];
         }
-        *reinterpret_cast<uint4*>(dst + off) = pack8(v);
+        *reinterpret_cast<uint4*>(dst + (PAIR ? sw128_pair(tid, c, tt & 1) : off)) = pack8(v);
       }
       WPROF_MARK(2);
       fence_proxy_async_smem();
@@ -606,6 +836,25 @@ bool map_sbtnd(CUtensorMap* tm, const void* base, int B, int T, int N) {
   return encode_tiles(tm, base, dims, strides, 3);
 }
 
+// Both layouts ([B,T,1,N,64] and [1,B,T,N,64]) with B a multiple of 8, two time steps per box: coordinates
+// (0, 0, t, b / 8, n); a box is [16 groups of 8 rows][2 steps][8 rows][64], so each group's pages are touched twice in a row
+bool map_pairs(CUtensorMap* tm, const void* base, int B, int T, int N) {
+  const uint64_t row = WD * 2, st = row * N, sb = st * T;
+  const uint64_t dims[5] = {WD, 8, (uint64_t)T, (uint64_t)B / 8, (uint64_t)N};
+  const uint64_t strides[4] = {sb, st, sb * 8, row};
+  const uint32_t box[5] = {WD, 8, 2, WM / 8, 1};
+  return encode_bf16_tiles(tm, base, dims, strides, box);
+}
+#ifdef FRNN_WIDE_NOPAIR  // development aid: one time step per copy everywhere
+bool pairs_ok(int, int) { return false; }
+#else
+bool pairs_ok(int B, int T) { return B % 8 == 0 && T >= 2; }
+#endif
+#ifndef FRNN_WIDE_BWD_MODE
+#define FRNN_WIDE_BWD_MODE 0
+#endif
+int bwd_pair_mode() { return FRNN_WIDE_BWD_MODE; }
+
 }  // namespace
 
 bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, int grad_cut) {
@@ -615,7 +864,10 @@ bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, in
 cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
                                 unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream) {
   CUtensorMap tm_wx, tm_st;
-  if (!map_btgnd(&tm_wx, Wx, B, T, N) || !map_sbtnd(&tm_st, states, B, T, N)) return cudaErrorNotSupported;
+  const bool pair = pairs_ok(B, T);
+  if (pair ? (!map_pairs(&tm_wx, Wx, B, T, N) || !map_pairs(&tm_st, states, B, T, N))
+           : (!map_btgnd(&tm_wx, Wx, B, T, N) || !map_sbtnd(&tm_st, states, B, T, N)))
+    return cudaErrorNotSupported;
   WideFwdParams p;
   p.R = static_cast<const __nv_bfloat16*>(R);
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -623,7 +875,8 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
   p.status = status;
   p.B = B; p.T = T; p.N = N;
   p.test_drop = test_drop;
-  cudaError_t e = cudaFuncSetAttribute(wide_fwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
+  auto kern = pair ? wide_fwd_elman_kernel<true> : wide_fwd_elman_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
   if (e != cudaSuccess) return e;
 #ifdef FRNN_WIDE_COPYONLY
   e = cudaFuncSetAttribute(wide_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 10 * (int)WTILE + 2048);
@@ -631,7 +884,7 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
   wide_copy_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, 10 * WTILE + 2048, stream>>>(tm_wx, tm_st, p);
   return cudaGetLastError();
 #endif
-  wide_fwd_elman_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WF_SMEM, stream>>>(tm_wx, tm_st, p);
+  kern<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WF_SMEM, stream>>>(tm_wx, tm_st, p);
   return cudaGetLastError();
 }
 
@@ -639,8 +892,10 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
                                  void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N, int test_drop,
                                  cudaStream_t stream) {
   CUtensorMap tm_st, tm_s0, tm_dst, tm_dwx;
-  if (!map_sbtnd(&tm_st, states, B, T, N) || !map_sbtnd(&tm_s0, s0, B, 1, N) || !map_sbtnd(&tm_dst, dstates, B, T, N) ||
-      !map_btgnd(&tm_dwx, dWx, B, T, N))
+  const int mode = pairs_ok(B, T) ? bwd_pair_mode() : 0;
+  if (!(mode == 2 ? map_pairs(&tm_st, states, B, T, N) : map_sbtnd(&tm_st, states, B, T, N)) || !map_sbtnd(&tm_s0, s0, B, 1, N) ||
+      !(mode == 2 ? map_pairs(&tm_dst, dstates, B, T, N) : map_sbtnd(&tm_dst, dstates, B, T, N)) ||
+      !(mode >= 1 ? map_pairs(&tm_dwx, dWx, B, T, N) : map_btgnd(&tm_dwx, dWx, B, T, N)))
     return cudaErrorNotSupported;
   WideBwdParams p;
   p.R = static_cast<const __nv_bfloat16*>(R);
@@ -650,9 +905,10 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
   p.status = status;
   p.B = B; p.T = T; p.N = N;
   p.test_drop = test_drop;
-  cudaError_t e = cudaFuncSetAttribute(wide_bwd_elman_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WB_SMEM);
+  auto kern = mode == 2 ? wide_bwd_elman_kernel<2> : mode == 1 ? wide_bwd_elman_kernel<1> : wide_bwd_elman_kernel<0>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WB_SMEM);
   if (e != cudaSuccess) return e;
-  wide_bwd_elman_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WB_SMEM, stream>>>(tm_st, tm_s0, tm_dst,
+  kern<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WB_SMEM, stream>>>(tm_st, tm_s0, tm_dst,
                                                                                                           tm_dwx, p);
   return cudaGetLastError();
 }
