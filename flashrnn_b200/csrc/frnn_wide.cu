@@ -387,11 +387,11 @@ constexpr uint32_t WB_OFF_DB = WB_OFF_I + WMAT;                   // float[4][64
 constexpr uint32_t WB_OFF_BAR = WB_OFF_DB + 1024;
 constexpr uint32_t WB_SMEM = WB_OFF_BAR + 8 * (2 * WB_STAGES + 8) + 16 + 1024;
 
-// MODE 0: one time step per bulk copy.  MODE 1: the deltas of two time steps leave in one bulk store (map of map_pairs,
-// see the forward kernel).  MODE 2: the h tiles and cotangent tiles arrive two time steps per copy as well; box r of
-// either sequence holds times 2p, 2p+1 with p = P-1-r (P = ceil(T/2)) in slot time & 1 of buffer r & 1, and box P of the
-// h sequence is h_{-1} (one tile, plain layout).
-template <int MODE>
+// PAIR: two time steps per bulk copy (maps of map_pairs, see the forward kernel).  The deltas of times 2p, 2p+1 leave in
+// one store from slot time & 1 of buffer p & 1; box r of the h sequence and of the cotangent sequence holds times 2p, 2p+1
+// with p = P-1-r (P = ceil(T/2)) in slot time & 1 of buffer r & 1, and box P of the h sequence is h_{-1} (one tile, plain
+// layout).  A buffer goes back to the copy engine once the MMAs that read it have signalled h_free / e_free.
+template <bool PAIR>
 __global__ void __launch_bounds__(W_THREADS, 1)
 wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __grid_constant__ CUtensorMap tm_s0,
                       const __grid_constant__ CUtensorMap tm_dstates, const __grid_constant__ CUtensorMap tm_dwx,
@@ -405,15 +405,14 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
   unsigned long long* wt = reinterpret_cast<unsigned long long*>(p.status) + 24;
   if (wt_on) wt[0] = global_timer_ns();
 #endif
-  constexpr bool PAIR = MODE >= 1, PAIRL = MODE == 2;
   float* sdb = reinterpret_cast<float*>(sm + WB_OFF_DB);
   uint64_t* h_full = reinterpret_cast<uint64_t*>(sm + WB_OFF_BAR);  // [WB_STAGES]
   uint64_t* e_full = h_full + WB_STAGES;                            // [WB_STAGES]
   uint64_t* acc_full = e_full + WB_STAGES;                          // [2]
   uint64_t* d_ready = acc_full + 2;                                 // 128 arrivals: delta tile written
   uint64_t* dr_done = d_ready + 1;                                  // all dR MMAs have completed
-  uint64_t* h_free = dr_done + 1;                                   // [2] MODE 2: the MMAs that read h buffer x have completed
-  uint64_t* e_free = h_free + 2;                                    // [2] MODE 2: ... cotangent buffer x ...
+  uint64_t* h_free = dr_done + 1;                                   // [2] PAIR: the MMAs that read h buffer x have completed
+  uint64_t* e_free = h_free + 2;                                    // [2] PAIR: ... cotangent buffer x ...
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(e_free + 2);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -461,7 +460,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       const void* tm0 = &tm_s0;
       const void* tme = &tm_dstates;
       const void* tmd = &tm_dwx;
-      if constexpr (PAIRL) {
+      if constexpr (PAIR) {
         constexpr uint32_t HI = desc_hi(1024, true), HI2 = desc_hi(2048, true), PAIR16 = (2 * WTILE) >> 4;
         const uint32_t hr_lo = (base + WB_OFF_H) >> 4, er_lo = (base + WB_OFF_E) >> 4, d_lo = (base + WB_OFF_D) >> 4,
                        r_lo = (base + WB_OFF_R) >> 4, i_lo = (base + WB_OFF_I) >> 4;
@@ -600,8 +599,6 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         ++e_loads;
       };
       constexpr uint32_t HI = desc_hi(1024, true), TILE16 = WTILE >> 4;  // descriptor halves as in the forward kernel
-      constexpr uint32_t HID = PAIR ? desc_hi(2048, true) : HI;          // delta tiles: 8-row groups 2048 bytes apart if PAIR
-      constexpr uint32_t DKS = PAIR ? 256u : 128u;                       // 16 rows of a delta tile, in 16-byte units
       const uint32_t hr_lo = (base + WB_OFF_H) >> 4, er_lo = (base + WB_OFF_E) >> 4, d_lo = (base + WB_OFF_D) >> 4,
                      r_lo = (base + WB_OFF_R) >> 4, i_lo = (base + WB_OFF_I) >> 4;
       auto issue_pre = [&](int j) {  // acc[j & 1] = dh_ext_j * I
@@ -632,33 +629,18 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           WPROF_MARK(0);
           if (h_seen < j + 1) h_seen = j + 1;  // the row threads of step j have read h tile j
           // step j+1 overwrites the tile of delta_{j-2}: that store (two groups back) must have left shared memory
-          const int tt = T - 1 - j;  // time of step index j
-          if constexpr (PAIR) {
-            // time tt-1 lands where time tt+3 was: stored at time tt+3 (tt odd, one younger store) or tt+2 (the youngest)
-            if (tt & 1) bulk_wait_group_read<1>();
-            else bulk_wait_group_read<0>();
-          } else {
-            bulk_wait_group_read<1>();
-          }
+          bulk_wait_group_read<1>();
           WPROF_MARK(1);
-          const uint32_t dbuf = PAIR ? (uint32_t)((tt >> 1) & 1) * 2 * WTILE : dj * WTILE;
-          const uint32_t dt = base + WB_OFF_D + dbuf, dl = d_lo + (dbuf >> 4) + (PAIR ? (uint32_t)(tt & 1) * 64u : 0u);
+          const uint32_t dt = base + WB_OFF_D + dj * WTILE, dl = d_lo + dj * TILE16;
           // dh accumulator of step j+1 (+)= delta_j * R; step T (the cotangent of h_{-1}) has no external part
           const uint32_t acc = tmem + ((j + 1) & 1) * WD;
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            umma_bf16_parts(acc, dl + 2 * k, HID, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
+            umma_bf16_parts(acc, dl + 2 * k, HI, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
           umma_commit(&acc_full[(j + 1) & 1]);
           WPROF_MARK(2);
-          if constexpr (PAIR) {
-            if (!(tt & 1)) {  // deltas of times tt, tt+1 -> dWx[b0.., tt .. tt+1, 0, n, :] (tt = T-1: the second tile is clipped)
-              tma_store_5d(tmd, dt, 0, 0, tt, b0 >> 3, n);
-              bulk_commit_group();
-            }
-          } else {
-            tma_store_5d(tmd, dt, 0, n, 0, tt, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
-            bulk_commit_group();
-          }
+          tma_store_5d(tmd, dt, 0, n, 0, T - 1 - j, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
+          bulk_commit_group();
           WPROF_MARK(3);
           // dR += delta_j^T * h_{t-1}  (h tile of sequence index j + 1)
           if (!mbar_wait_bounded(&h_full[(j + 1) % WB_STAGES], (uint32_t)(((j + 1) / WB_STAGES) & 1))) { ok = false; break; }
@@ -667,7 +649,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           const uint32_t hl = hr_lo + ((j + 1) % WB_STAGES) * TILE16;
 #pragma unroll
           for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = 2048 bytes per k-step
-            umma_bf16_parts(tmem + 2 * WD, dl + DKS * ks, HID, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+            umma_bf16_parts(tmem + 2 * WD, dl + 128 * ks, HI, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
           WPROF_MARK(5);
           // h tile j-1: its row threads (step j-1) and its dR MMAs (step j-2, completed before the accumulator of
           // step j was signalled) are done; cotangent tile j: consumed by MMAs that completed before step j started
@@ -705,9 +687,9 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
 #endif
     WPROF_DECL(tid == 0);
     for (int j = 0; j < T; ++j) {
-      const int tt = T - 1 - j, hr = ((T + 1) >> 1) - 1 - (tt >> 1);  // time of the step; MODE 2: its h box
+      const int tt = T - 1 - j, hr = ((T + 1) >> 1) - 1 - (tt >> 1);  // time of the step; PAIR: its h box
       if (!mbar_wait_bounded(&acc_full[j & 1], (uint32_t)((j >> 1) & 1)) ||
-          !(PAIRL ? mbar_wait_bounded(&h_full[hr & 1], (uint32_t)((hr >> 1) & 1))
+          !(PAIR ? mbar_wait_bounded(&h_full[hr & 1], (uint32_t)((hr >> 1) & 1))
                   : mbar_wait_bounded(&h_full[j % WB_STAGES], (uint32_t)((j / WB_STAGES) & 1)))) {
         report_timeout(p.status, j);
         ok = false;
@@ -718,13 +700,13 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (j & 1) * WD, r0, r1);
       WPROF_MARK(1);
-      const unsigned char* hsrc = sm + WB_OFF_H + (PAIRL ? (uint32_t)(hr & 1) * 2 * WTILE : (j % WB_STAGES) * WTILE);
+      const unsigned char* hsrc = sm + WB_OFF_H + (PAIR ? (uint32_t)(hr & 1) * 2 * WTILE : (j % WB_STAGES) * WTILE);
       unsigned char* dst = sm + WB_OFF_D + (PAIR ? (uint32_t)((tt >> 1) & 1) * 2 * WTILE : dw * WTILE);
       dw = (dw == 2) ? 0 : dw + 1;
 #pragma unroll
       for (uint32_t c = 0; c < 8; ++c) {
         const uint32_t off = sw128(tid, c);
-        const uint4 hv = *reinterpret_cast<const uint4*>(hsrc + (PAIRL ? sw128_pair(tid, c, tt & 1) : off));
+        const uint4 hv = *reinterpret_cast<const uint4*>(hsrc + (PAIR ? sw128_pair(tid, c, tt & 1) : off));
         const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
         float v[8];
 #pragma unroll
@@ -850,10 +832,7 @@ bool pairs_ok(int, int) { return false; }
 #else
 bool pairs_ok(int B, int T) { return B % 8 == 0 && T >= 2; }
 #endif
-#ifndef FRNN_WIDE_BWD_MODE
-#define FRNN_WIDE_BWD_MODE 0
-#endif
-int bwd_pair_mode() { return FRNN_WIDE_BWD_MODE; }
+
 
 }  // namespace
 
@@ -892,10 +871,10 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
                                  void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N, int test_drop,
                                  cudaStream_t stream) {
   CUtensorMap tm_st, tm_s0, tm_dst, tm_dwx;
-  const int mode = pairs_ok(B, T) ? bwd_pair_mode() : 0;
-  if (!(mode == 2 ? map_pairs(&tm_st, states, B, T, N) : map_sbtnd(&tm_st, states, B, T, N)) || !map_sbtnd(&tm_s0, s0, B, 1, N) ||
-      !(mode == 2 ? map_pairs(&tm_dst, dstates, B, T, N) : map_sbtnd(&tm_dst, dstates, B, T, N)) ||
-      !(mode >= 1 ? map_pairs(&tm_dwx, dWx, B, T, N) : map_btgnd(&tm_dwx, dWx, B, T, N)))
+  const bool pair = pairs_ok(B, T);
+  if (!(pair ? map_pairs(&tm_st, states, B, T, N) : map_sbtnd(&tm_st, states, B, T, N)) || !map_sbtnd(&tm_s0, s0, B, 1, N) ||
+      !(pair ? map_pairs(&tm_dst, dstates, B, T, N) : map_sbtnd(&tm_dst, dstates, B, T, N)) ||
+      !(pair ? map_pairs(&tm_dwx, dWx, B, T, N) : map_btgnd(&tm_dwx, dWx, B, T, N)))
     return cudaErrorNotSupported;
   WideBwdParams p;
   p.R = static_cast<const __nv_bfloat16*>(R);
@@ -905,7 +884,7 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
   p.status = status;
   p.B = B; p.T = T; p.N = N;
   p.test_drop = test_drop;
-  auto kern = mode == 2 ? wide_bwd_elman_kernel<2> : mode == 1 ? wide_bwd_elman_kernel<1> : wide_bwd_elman_kernel<0>;
+  auto kern = pair ? wide_bwd_elman_kernel<true> : wide_bwd_elman_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WB_SMEM);
   if (e != cudaSuccess) return e;
   kern<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WB_SMEM, stream>>>(tm_st, tm_s0, tm_dst,
