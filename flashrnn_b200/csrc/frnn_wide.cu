@@ -12,6 +12,9 @@
 //                     db in registers.  No separate dR pass over HBM: the delta and h tiles are in shared memory anyway.
 // Warps 0-3: one batch row per thread.  Warp 4, one lane: issues every bulk copy and every MMA.  All tiles are
 // [128 rows][64 bf16] = rows of 128 bytes in the 128-byte-swizzle layout shared by the bulk copies and the MMA descriptors.
+// When the batch is a multiple of 8 (and T >= 2) every bulk copy moves TWO time steps: batch rows lie T*N*128 bytes apart
+// (one 2 MB page each at the sizes this path is for), address translation bounds the copies, and the second touch of a
+// page right after the first one is cheap.  The tiles of the two steps then interleave in shared memory by 8-row group.
 //
 // Replaces, for these shapes, FLASHRNNCellFusedForward / FLASHRNNCellFusedBackward and the dR GEMM + bias reduction that
 // follow the reverse loop (flashrnn/flashrnn/fused/flashrnn_fused_forward.cu:146-659, flashrnn_fused_backward.cu:129-624,
