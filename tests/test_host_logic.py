@@ -119,6 +119,17 @@ def test_no_cpu_fallback_and_removed_backends():
         flashrnn(Wx, R, b, function="lstm", dtype="float16")
 
 
+def test_stepper_has_no_cpu_path_and_checks_shapes():
+    from flashrnn_b200 import FlashRNNStepper
+    R, b = torch.zeros(4, 1, 32, 32, dtype=torch.bfloat16), torch.zeros(4, 1, 32, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        FlashRNNStepper(R, b, function="lstm", batch_size=2)
+    with pytest.raises(AssertionError):
+        FlashRNNStepper(R, b, function="rnn", batch_size=2)
+    plan = _native.query(_native.make_problem("lstm", 2, 1, 1, 32, False, False))
+    assert plan.keep_packed_r == 0  # frnn_forward repacks R unless the caller says the workspace still holds it
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "_lib", None)
     monkeypatch.setattr(_native, "LIB_PATH", tmp_path / "nope.so")
