@@ -17,7 +17,7 @@ LIB_PATH = Path(os.environ.get("FRNN_B200_LIB") or PKG / "libfrnn_b200.so")
 ABI_VERSION = 1
 NOALLOC_MAX_SCRATCH_BYTES = 8 << 20  # FRNN_NOALLOC_MAX_SCRATCH_BYTES
 CELL_IDS = {"lstm": 0, "gru": 1, "elman": 2, "slstm": 3}
-DTYPE_BF16, DTYPE_F32 = 0, 1
+DTYPE_BF16, DTYPE_F32, DTYPE_F16 = 0, 1, 2
 
 # every symbol include/frnn.h declares
 EXPORTS = (
@@ -113,10 +113,13 @@ def check(what: str, code: int) -> None:
 
 
 def make_problem(function: str, B: int, T: int, N: int, D: int, state_f32: bool, training: bool,
-                 forward_clip: float | None = None, grad_clip: float | None = None, grad_cut: bool = False) -> FrnnProblem:
+                 forward_clip: float | None = None, grad_clip: float | None = None, grad_cut: bool = False,
+                 f16: bool = False) -> FrnnProblem:
+    """``f16``: Wx, R, b, the gradients and (unless ``state_f32``) the states are float16 instead of bfloat16."""
     if function not in CELL_IDS:
         raise AssertionError(f"RNN function {function} not in registry")
-    return FrnnProblem(CELL_IDS[function], B, T, N, D, DTYPE_BF16, DTYPE_F32 if state_f32 else DTYPE_BF16,
+    io = DTYPE_F16 if f16 else DTYPE_BF16
+    return FrnnProblem(CELL_IDS[function], B, T, N, D, io, DTYPE_F32 if state_f32 else io,
                        1 if training else 0, float(forward_clip or 0.0), float(grad_clip or 0.0), 1 if grad_cut else 0)
 
 

@@ -41,12 +41,14 @@ def _stale(out: Path, deps: list[Path]) -> bool:
     return not out.exists() or any(d.stat().st_mtime > out.stat().st_mtime for d in deps)
 
 
-def _compile(src: Path, headers: list[Path], force: bool) -> Path:
-    obj = OBJ / (src.stem + ".o")
+def _compile(src: Path, headers: list[Path], force: bool, f16: bool = False) -> Path:
+    """One object per (source, element type): as is = bfloat16, with -DFRNN_F16 = float16 (csrc/frnn_elem.cuh)."""
+    stem = src.stem + ("_f16" if f16 else "")
+    obj = OBJ / (stem + ".o")
     if force or _stale(obj, [src] + headers):
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *(["-DFRNN_F16"] if f16 else []), "-c", str(src), "-o", str(obj)]
         res = subprocess.run(cmd, capture_output=True, text=True)
-        (OBJ / (src.stem + ".log")).write_text(res.stdout + res.stderr)
+        (OBJ / (stem + ".log")).write_text(res.stdout + res.stderr)
         if res.returncode != 0:
             raise RuntimeError(f"nvcc failed for {src.name}:\n{res.stderr[-4000:]}")
     return obj
@@ -67,9 +69,10 @@ def build(force: bool = False, jobs: int | None = None, extra_flags: tuple[str, 
     OBJ.mkdir(exist_ok=True, parents=True)
     headers = sorted(CSRC.glob("*.cuh")) + [PKG.parent / "include" / "frnn.h"]
     srcs = _sources()
-    jobs = jobs or min(len(srcs), os.cpu_count() or 4)
+    units = [(s, f16) for f16 in (False, True) for s in srcs]
+    jobs = jobs or min(len(units), os.cpu_count() or 4)
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
-        objs = list(ex.map(lambda s: _compile(s, headers, force), srcs))
+        objs = list(ex.map(lambda u: _compile(u[0], headers, force, u[1]), units))
     if force or _stale(LIB, objs):
         cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs), "-cudart", "static"]
         res = subprocess.run(cmd, capture_output=True, text=True)

@@ -7,7 +7,7 @@
 
 #include "frnn_aux.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 struct CellDims { int Gr, Gw, Gt, S, GC; };
 static bool cell_dims(int cell, CellDims* d) {
@@ -145,8 +145,9 @@ static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs,
 static int validate_problem(const frnn_problem* pr, CellDims* cd) {
   if (!pr) return FRNN_ERR_NULL;
   if (!cell_dims(pr->cell, cd)) return FRNN_ERR_CELL;
-  if (pr->dtype_io != FRNN_DTYPE_BF16) return FRNN_ERR_DTYPE;
-  if (pr->dtype_state != FRNN_DTYPE_BF16 && pr->dtype_state != FRNN_DTYPE_F32) return FRNN_ERR_DTYPE;
+  constexpr int io = kF16 ? FRNN_DTYPE_F16 : FRNN_DTYPE_BF16;  // the element type this build of the kernels computes in
+  if (pr->dtype_io != io) return FRNN_ERR_DTYPE;
+  if (pr->dtype_state != io && pr->dtype_state != FRNN_DTYPE_F32) return FRNN_ERR_DTYPE;
   if (pr->B < 1 || pr->T < 1 || pr->N < 1 || pr->D < 1) return FRNN_ERR_SHAPE;
   if (pr->N > 65535) return FRNN_ERR_SHAPE;
   if (pr->D % 16) return FRNN_ERR_SHAPE;
@@ -238,21 +239,48 @@ static int sm_count_cached() {
   return cached[dev];
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS
 
-using namespace frnn;
+using namespace FRNN_NS;
+
+// This file is compiled twice (see frnn_elem.cuh).  The bfloat16 build owns the public names and forwards float16
+// problems to the float16 build, whose entry points carry the suffix _f16 and stay private to the library.
+#ifdef FRNN_F16
+#define FRNN_ENTRY(name) __attribute__((visibility("hidden"))) name##_f16
+#define FRNN_FORWARD_F16(is_f16, call)
+#else
+#define FRNN_ENTRY(name) name
+#define FRNN_FORWARD_F16(is_f16, call) \
+  if (is_f16) return call
+extern "C" {
+int frnn_query_f16(const frnn_problem*, frnn_plan*);
+int frnn_query_tile_f16(const frnn_problem*, int, int, int, frnn_plan*);
+int frnn_forward_f16(const frnn_plan*, const frnn_fwd_args*, void*);
+int frnn_backward_parts_f16(const frnn_plan*, const frnn_bwd_args*, void*, int);
+int frnn_finalize_grads_f16(const frnn_plan*, const void*, void*, void*, void*);
+}
+#endif
+static inline bool wants_f16(const frnn_problem* pr) { return pr && pr->dtype_io == FRNN_DTYPE_F16; }
+static inline bool wants_f16(const frnn_plan* pl) { return pl && pl->prob.dtype_io == FRNN_DTYPE_F16; }
 
 extern "C" {
 
+#ifndef FRNN_F16
 int frnn_abi_version(void) { return FRNN_ABI_VERSION; }
+#endif
 
-int frnn_query(const frnn_problem* problem, frnn_plan* out) { return fill_plan(problem, 0, 0, 0, out); }
+int FRNN_ENTRY(frnn_query)(const frnn_problem* problem, frnn_plan* out) {
+  FRNN_FORWARD_F16(wants_f16(problem), frnn_query_f16(problem, out));
+  return fill_plan(problem, 0, 0, 0, out);
+}
 
-int frnn_query_tile(const frnn_problem* problem, int cluster_size, int batch_tile, int wx_stages, frnn_plan* out) {
+int FRNN_ENTRY(frnn_query_tile)(const frnn_problem* problem, int cluster_size, int batch_tile, int wx_stages, frnn_plan* out) {
+  FRNN_FORWARD_F16(wants_f16(problem), frnn_query_tile_f16(problem, cluster_size, batch_tile, wx_stages, out));
   return fill_plan(problem, cluster_size, batch_tile, wx_stages, out);
 }
 
-int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
+int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
+  FRNN_FORWARD_F16(wants_f16(plan), frnn_forward_f16(plan, a, stream_));
   CellDims cd;
   int rc = check_plan(plan, &cd);
   if (rc) return rc;
@@ -275,12 +303,12 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   if (e != cudaSuccess) return (int)e;
 
   LoopParams lp = {};
-  lp.Wx = static_cast<const __nv_bfloat16*>(a->Wx);
+  lp.Wx = static_cast<const elem_t*>(a->Wx);
   lp.Rpack = reinterpret_cast<const uint4*>(ws + w.rpack_fwd);
-  lp.bias = static_cast<const __nv_bfloat16*>(a->b);
+  lp.bias = static_cast<const elem_t*>(a->b);
   lp.s0 = a->s0;
   lp.states = a->states;
-  lp.cache = pr.training ? static_cast<__nv_bfloat16*>(a->cache) : nullptr;
+  lp.cache = pr.training ? static_cast<elem_t*>(a->cache) : nullptr;
   lp.status = reinterpret_cast<unsigned*>(ws);
   lp.B = pr.B; lp.T = pr.T; lp.N = pr.N; lp.D = pr.D;
   lp.U = plan->units_per_cta; lp.CS = plan->cluster_size;
@@ -292,11 +320,14 @@ int frnn_forward(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   return (int)e;
 }
 
+#ifndef FRNN_F16
 int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_) {
   return frnn_backward_parts(plan, a, stream_, FRNN_PART_LOOP | FRNN_PART_DR);
 }
+#endif
 
-int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_, int parts) {
+int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_, int parts) {
+  FRNN_FORWARD_F16(wants_f16(plan), frnn_backward_parts_f16(plan, a, stream_, parts));
   CellDims cd;
   int rc = check_plan(plan, &cd);
   if (rc) return rc;
@@ -333,10 +364,10 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   lp.Rpack = reinterpret_cast<const uint4*>(ws + w.rpack_bwd);
   lp.s0 = a->s0;
   lp.states = const_cast<void*>(a->states);
-  lp.cache = static_cast<__nv_bfloat16*>(const_cast<void*>(a->cache));
+  lp.cache = static_cast<elem_t*>(const_cast<void*>(a->cache));
   lp.dstates = a->dstates;
-  lp.dWx = static_cast<__nv_bfloat16*>(a->dWx);
-  lp.dg0 = reinterpret_cast<__nv_bfloat16*>(ws + w.dg0);
+  lp.dWx = static_cast<elem_t*>(a->dWx);
+  lp.dg0 = reinterpret_cast<elem_t*>(ws + w.dg0);
   lp.ds0 = a->ds0;
   lp.dbias = grads + nR;
   lp.status = reinterpret_cast<unsigned*>(ws);
@@ -368,7 +399,8 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* a, void* str
   return (int)e;
 }
 
-int frnn_finalize_grads(const frnn_plan* plan, const void* grads_f32, void* dR, void* db, void* stream_) {
+int FRNN_ENTRY(frnn_finalize_grads)(const frnn_plan* plan, const void* grads_f32, void* dR, void* db, void* stream_) {
+  FRNN_FORWARD_F16(wants_f16(plan), frnn_finalize_grads_f16(plan, grads_f32, dR, db, stream_));
   CellDims cd;
   int rc = check_plan(plan, &cd);
   if (rc) return rc;
@@ -378,6 +410,7 @@ int frnn_finalize_grads(const frnn_plan* plan, const void* grads_f32, void* dR, 
   return (int)launch_cast_grads(static_cast<const float*>(grads_f32), dR, db, nR, nb, static_cast<cudaStream_t>(stream_));
 }
 
+#ifndef FRNN_F16
 int frnn_read_device_status(const void* workspace, void* stream_, frnn_dev_status* out) {
   if (!workspace || !out) return FRNN_ERR_NULL;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -392,7 +425,7 @@ const char* frnn_status_string(int code) {
     case FRNN_ERR_NULL: return "frnn: a required pointer is NULL";
     case FRNN_ERR_CELL: return "frnn: unknown cell (expected lstm, gru, elman or slstm)";
     case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256} or a multiple of 64 up to 1024)";
-    case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b must be bfloat16; states bfloat16 or float32)";
+    case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b bfloat16 or float16; states of the same type or float32)";
     case FRNN_ERR_ALIGN: return "frnn: tensor pointers must be 16-byte aligned";
     case FRNN_ERR_PLAN: return "frnn: invalid plan or tile for this problem";
     case FRNN_ERR_TRAINING: return "frnn: backward needs a plan made with training = 1";
@@ -403,5 +436,6 @@ const char* frnn_status_string(int code) {
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
   return "frnn: unknown status";
 }
+#endif
 
 }  // extern "C"

@@ -4,13 +4,13 @@
 //   cast_grads_kernel      fp32 dR || db -> parameter dtype
 #include "frnn_aux.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 // One thread builds one 16-byte fragment (what one lane holds of one 16x16 A tile of mma.m16n8k16):
 //   out[((n*Gr + g)*(D/16) + ut)*(D/16) + k][lane] ;  A[row][kk], row/kk in 0..15
 //   forward : A[row][kk] = R[g][n][ut*16 + row][k*16 + kk]
 //   backward: A[row][kk] = R[g][n][k*16 + kk][ut*16 + row]      (rows = input unit p)
-__global__ void pack_recurrent_kernel(const __nv_bfloat16* __restrict__ R, uint4* __restrict__ out, int Gr, int N, int D,
+__global__ void pack_recurrent_kernel(const elem_t* __restrict__ R, uint4* __restrict__ out, int Gr, int N, int D,
                                       int transpose) {
   const int KT = D / 16;
   const size_t total = (size_t)N * Gr * KT * KT * 32;
@@ -23,10 +23,10 @@ __global__ void pack_recurrent_kernel(const __nv_bfloat16* __restrict__ R, uint4
   const int g = (int)(r % Gr);
   const int n = (int)(r / Gr);
   const int gid = lane >> 2, tig = lane & 3;
-  const __nv_bfloat16* Rg = R + (((size_t)g * N + n) * D) * D;
+  const elem_t* Rg = R + (((size_t)g * N + n) * D) * D;
   auto at = [&](int row, int kk) -> unsigned short {
     const int a = ut * 16 + row, c = k * 16 + kk;
-    const __nv_bfloat16 v = transpose ? Rg[(size_t)c * D + a] : Rg[(size_t)a * D + c];
+    const elem_t v = transpose ? Rg[(size_t)c * D + a] : Rg[(size_t)a * D + c];
     return *reinterpret_cast<const unsigned short*>(&v);
   };
   auto pair = [&](int row, int kk) -> uint32_t { return (uint32_t)at(row, kk) | ((uint32_t)at(row, kk + 1) << 16); };
@@ -48,8 +48,8 @@ __global__ void pack_recurrent_kernel(const __nv_bfloat16* __restrict__ R, uint4
 constexpr int DR_TM = 64, DR_TN = 64, DR_KC = 32, DR_LD = 72;  // 72*2 B = 144 B row pitch: conflict-free ldmatrix
 
 struct DrParams {
-  const __nv_bfloat16* dWx;  // [B,T,Gw,N,D]
-  const __nv_bfloat16* dg0;  // [B,T,N,D] (GRU)
+  const elem_t* dWx;  // [B,T,Gw,N,D]
+  const elem_t* dg0;  // [B,T,N,D] (GRU)
   const void* states;        // [S,B,T,N,D]; only s = 0 is read
   const void* s0;            // [S,B,1,N,D]
   float* dR;                 // [Gr,N,D,D] fp32
@@ -60,8 +60,8 @@ struct DrParams {
 
 template <bool F32>
 __global__ void __launch_bounds__(128) recurrent_grad_kernel(const DrParams p) {
-  __shared__ __align__(16) __nv_bfloat16 As[2][DR_KC][DR_LD];
-  __shared__ __align__(16) __nv_bfloat16 Hs[2][DR_KC][DR_LD];
+  __shared__ __align__(16) elem_t As[2][DR_KC][DR_LD];
+  __shared__ __align__(16) elem_t Hs[2][DR_KC][DR_LD];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int D = p.D, N = p.N, T = p.T;
   const int tiles = (D + DR_TM - 1) / DR_TM;
@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(128) recurrent_grad_kernel(const DrParams p) {
   const size_t ND = (size_t)N * D;
 
   // source of the delta rows of R-gate g
-  const __nv_bfloat16* abase;
+  const elem_t* abase;
   size_t astride;
   if (p.cell == CELL_GRU) {
     if (g == 0) { abase = p.dg0 + (size_t)n * D; astride = ND; }
@@ -96,14 +96,14 @@ __global__ void __launch_bounds__(128) recurrent_grad_kernel(const DrParams p) {
       // delta rows
       {
         const int d = tm * DR_TM + c8;
-        __nv_bfloat16* dst = &As[buf][r][c8];
+        elem_t* dst = &As[buf][r][c8];
         if (krow && d < D) cp_async16(dst, abase + (size_t)k * astride + d);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
       }
       // h_{t-1} rows
       {
         const int pcol = tn * DR_TN + c8;
-        __nv_bfloat16* dst = &Hs[buf][r][c8];
+        elem_t* dst = &Hs[buf][r][c8];
         if (krow && pcol < D) {
           const long long b = k / T;
           const int t = (int)(k - b * T);
@@ -114,11 +114,11 @@ __global__ void __launch_bounds__(128) recurrent_grad_kernel(const DrParams p) {
             const float4 v0 = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + off);
             const float4 v1 = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + off + 4);
             uint4 w;
-            w.x = pack_bf16x2(v0.x, v0.y); w.y = pack_bf16x2(v0.z, v0.w);
-            w.z = pack_bf16x2(v1.x, v1.y); w.w = pack_bf16x2(v1.z, v1.w);
+            w.x = pack_x2(v0.x, v0.y); w.y = pack_x2(v0.z, v0.w);
+            w.z = pack_x2(v1.x, v1.y); w.w = pack_x2(v1.z, v1.w);
             *reinterpret_cast<uint4*>(dst) = w;
           } else {
-            cp_async16(dst, static_cast<const __nv_bfloat16*>(base) + off);
+            cp_async16(dst, static_cast<const elem_t*>(base) + off);
           }
         } else {
           *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(128) recurrent_grad_kernel(const DrParams p) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) mma_bf16_16816(acc[mt][nt], afr[mt], bfr[nt][0], bfr[nt][1]);
+        for (int nt = 0; nt < 4; ++nt) mma_16816(acc[mt][nt], afr[mt], bfr[nt][0], bfr[nt][1]);
     }
     __syncthreads();
   }
@@ -177,11 +177,11 @@ __global__ void __launch_bounds__(128) recurrent_grad_kernel(const DrParams p) {
       }
 }
 
-__global__ void cast_grads_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dR, __nv_bfloat16* __restrict__ db,
+__global__ void cast_grads_kernel(const float* __restrict__ src, elem_t* __restrict__ dR, elem_t* __restrict__ db,
                                   size_t nR, size_t nb) {
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < nR) dR[i] = __float2bfloat16_rn(src[i]);
-  else if (i < nR + nb) db[i - nR] = __float2bfloat16_rn(src[i]);
+  if (i < nR) dR[i] = float_to_elem(src[i]);
+  else if (i < nR + nb) db[i - nR] = float_to_elem(src[i]);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -190,7 +190,7 @@ cudaError_t launch_pack_recurrent(const void* R, void* out, int Gr, int N, int D
   const size_t total = (size_t)N * Gr * KT * KT * 32;
   const int threads = 256;
   pack_recurrent_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(R), static_cast<uint4*>(out), Gr, N, D, transpose);
+      static_cast<const elem_t*>(R), static_cast<uint4*>(out), Gr, N, D, transpose);
   return cudaGetLastError();
 }
 
@@ -198,8 +198,8 @@ cudaError_t launch_recurrent_grad(int cell, int B, int T, int N, int D, int Gr, 
                                   const void* dg0, const void* states, const void* s0, float* dR, int sm_count,
                                   cudaStream_t stream) {
   DrParams p;
-  p.dWx = static_cast<const __nv_bfloat16*>(dWx);
-  p.dg0 = static_cast<const __nv_bfloat16*>(dg0);
+  p.dWx = static_cast<const elem_t*>(dWx);
+  p.dg0 = static_cast<const elem_t*>(dg0);
   p.states = states; p.s0 = s0; p.dR = dR;
   p.cell = cell; p.B = B; p.T = T; p.N = N; p.D = D; p.Gr = Gr; p.Gw = Gw; p.state_f32 = state_f32;
   p.K = (long long)B * T;
@@ -223,8 +223,8 @@ cudaError_t launch_cast_grads(const float* src, void* dR, void* db, size_t nR, s
   const size_t total = nR + nb;
   const int threads = 256;
   cast_grads_kernel<<<(unsigned)((total + threads - 1) / threads), threads, 0, stream>>>(
-      src, static_cast<__nv_bfloat16*>(dR), static_cast<__nv_bfloat16*>(db), nR, nb);
+      src, static_cast<elem_t*>(dR), static_cast<elem_t*>(db), nR, nb);
   return cudaGetLastError();
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

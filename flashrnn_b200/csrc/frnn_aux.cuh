@@ -2,7 +2,7 @@
 #pragma once
 #include "frnn_common.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 // head dims (D = 16*KT) and batch tiles (BT = 8*NT) the time-loop kernels are instantiated for
 #define FRNN_FOREACH_KT(X, ...) X(2, __VA_ARGS__) X(4, __VA_ARGS__) X(6, __VA_ARGS__) X(8, __VA_ARGS__) X(12, __VA_ARGS__) X(16, __VA_ARGS__)
@@ -60,4 +60,4 @@ cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int 
                                       cudaStream_t stream);
 cudaError_t launch_cast_grads(const float* src, void* dR, void* db, size_t nR, size_t nb, cudaStream_t stream);
 
-}  // namespace frnn
+}  // namespace FRNN_NS

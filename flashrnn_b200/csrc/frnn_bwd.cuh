@@ -31,7 +31,7 @@
 #pragma once
 #include "frnn_common.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 // Closed-form backward of one cell update, fp32.
 //   dh        total cotangent of h_t (external + recurrent)
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // all-gather:      dgbuf [2][CS][BT][GS] bf16 | part [Gr][BT][PS] f32
   // reduce-scatter:  dgbuf [BT][GS] bf16        | stage [2][CS][BT][PS] f32 | recv [2][CS][BT][PS] f32
-  __nv_bfloat16* dgbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  elem_t* dgbuf = reinterpret_cast<elem_t*>(smem_raw);
   float* part = reinterpret_cast<float*>(smem_raw + (RS ? (size_t)SL * 2 : (size_t)2 * CS * SL * 2));
   float* stage_buf = part;                                  // RS only
   float* recv_buf = part + (size_t)2 * CS * PSL;            // RS only
@@ -185,8 +185,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   const unsigned char* st_pf[IPT];      // states[0][b][t-1] of the next step to prefetch
   const unsigned char* ds_pf[IPT];      // dstates[0][b][t]  of the next step to prefetch
   const unsigned char* s0_it[IPT];      // s0[0][b]
-  __nv_bfloat16* dwx_ptr[IPT];          // dWx[b][t][0][n][d] of the current step
-  __nv_bfloat16* dg0_ptr[IPT];
+  elem_t* dwx_ptr[IPT];          // dWx[b][t][0][n][d] of the current step
+  elem_t* dg0_ptr[IPT];
   size_t s0_off[IPT];
   float car[IPT][S][2], cur[IPT][NNEED][2], dbacc[IPT][Gt][2];
 #pragma unroll
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   auto ring_state = [&](int stage, int slot, int i) -> float2 {
     const uint2 w = rings[((size_t)(stage * NSS + slot) * IPT + i) * RL + tid];
     if (f32) return make_float2(__uint_as_float(w.x), __uint_as_float(w.y));
-    return unpack_bf16x2(w.x);
+    return unpack_x2(w.x);
   };
   // recurrent part of dh for item i: sum of the partial products of the previous step (`pbuf` = its buffer index)
   auto recurrent_sum = [&](int i, int pbuf, float (&rec)[2]) {
@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     if constexpr (RS) { if (j > 0) wait_exchange(buf ^ 1, j - 1, t, buf); }  // partial sums produced in step j-1
     FRNN_PROF_MARK(1);
     float dwv[IPT][Gw][2], dg0v[IPT][2];
-    __nv_bfloat16* ddst = RS ? dgbuf : dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
+    elem_t* ddst = RS ? dgbuf : dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
     // ---------------- phase B: pointwise backward; R-gate deltas (bf16) into the delta tile
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       for (int k = 0; k < NEXT; ++k) { const float2 v = ring_state(stage, NNEED + k, i); extv[k][0] = v.x; extv[k][1] = v.y; }
 #pragma unroll
       for (int k = 0; k < GC; ++k) {
-        const float2 v = unpack_bf16x2(ringc[((size_t)(stage * GCA + k) * IPT + i) * RL + tid]);
+        const float2 v = unpack_x2(ringc[((size_t)(stage * GCA + k) * IPT + i) * RL + tid]);
         chv[k][0] = v.x; chv[k][1] = v.y;
       }
       float dRv[2][Gr];
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       dg0v[i][0] = dRv[0][0]; dg0v[i][1] = dRv[1][0];
 #pragma unroll
       for (int g = 0; g < Gr; ++g)
-        *reinterpret_cast<uint32_t*>(ddst + dloc_it[i] + g * U) = pack_bf16x2(dRv[0][g], dRv[1][g]);
+        *reinterpret_cast<uint32_t*>(ddst + dloc_it[i] + g * U) = pack_x2(dRv[0][g], dRv[1][g]);
     }
     if (!RS && CS > 1) fence_proxy_async_smem();
     FRNN_PROF_MARK(2);
@@ -441,10 +441,10 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       if (!it_ok[i]) continue;
 #pragma unroll
       for (int g = 0; g < Gw; ++g)
-        *reinterpret_cast<uint32_t*>(dwx_ptr[i] + (size_t)g * ND) = pack_bf16x2(dwv[i][g][0], dwv[i][g][1]);
+        *reinterpret_cast<uint32_t*>(dwx_ptr[i] + (size_t)g * ND) = pack_x2(dwv[i][g][0], dwv[i][g][1]);
       dwx_ptr[i] -= (size_t)Gw * ND;
       if (CELL == CELL_GRU) {
-        *reinterpret_cast<uint32_t*>(dg0_ptr[i]) = pack_bf16x2(dg0v[i][0], dg0v[i][1]);
+        *reinterpret_cast<uint32_t*>(dg0_ptr[i]) = pack_x2(dg0v[i][0], dg0v[i][1]);
         dg0_ptr[i] -= ND;
       }
     }
@@ -500,4 +500,4 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

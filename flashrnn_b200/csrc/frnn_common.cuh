@@ -1,11 +1,11 @@
 // Shared device helpers of the sm_100a time-loop kernels: PTX wrappers (warp MMA, ldmatrix, cp.async,
 // cluster barrier / distributed shared memory), fp32 gate math and the per-cell traits.
 #pragma once
-#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include "frnn_elem.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 // 0..3 are the public cell ids of the C ABI.  CELL_ELMAN_CLIP is internal: Elman with forward_clip, whose backward
 // needs the tanh output from before the clamp and therefore caches it (plain Elman re-reads h and caches nothing).
@@ -43,15 +43,15 @@ constexpr int kStages = 4;
 
 // Arguments of both time-loop kernels (forward uses the first block, backward all of it).
 struct LoopParams {
-  const __nv_bfloat16* Wx;   // [B,T,Gw,N,D]
+  const elem_t* Wx;   // [B,T,Gw,N,D]
   const uint4* Rpack;        // recurrent matrix repacked into warp-MMA A fragments
-  const __nv_bfloat16* bias; // [Gt,N,D]
+  const elem_t* bias; // [Gt,N,D]
   const void* s0;            // [S,B,1,N,D]
   void* states;              // [S,B,T,N,D]  (forward: out, backward: in)
-  __nv_bfloat16* cache;      // [B,T,GC,N,D] (forward: out or null, backward: in)
+  elem_t* cache;      // [B,T,GC,N,D] (forward: out or null, backward: in)
   const void* dstates;       // [S,B,T,N,D]
-  __nv_bfloat16* dWx;        // [B,T,Gw,N,D]
-  __nv_bfloat16* dg0;        // [B,T,N,D]   GRU only: delta of the recurrent-only gate
+  elem_t* dWx;        // [B,T,Gw,N,D]
+  elem_t* dg0;        // [B,T,N,D]   GRU only: delta of the recurrent-only gate
   void* ds0;                 // [S,B,1,N,D]
   float* dbias;              // fp32 [Gt,N,D] accumulated with atomics
   unsigned* status;
@@ -76,9 +76,9 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
 }
-// D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col)
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+// D(16x8, fp32) += A(16x16, elem_t, row) * B(16x8, elem_t, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32." FRNN_MMA_TYPE "." FRNN_MMA_TYPE ".f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
@@ -209,23 +209,23 @@ __device__ __forceinline__ float fast_sigmoid(float x) {
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - __logf(1.f + __expf(-fabsf(x))); }
 __device__ __forceinline__ float clampf(float x, float v) { return fminf(fmaxf(x, -v), v); }
 
-__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+__device__ __forceinline__ uint32_t pack_x2(float lo, float hi) {
+  elem2_t v = floats_to_elem2(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ float2 unpack_bf16x2(uint32_t w) {
-  __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&w);
-  return __bfloat1622float2(v);
+__device__ __forceinline__ float2 unpack_x2(uint32_t w) {
+  elem2_t v = *reinterpret_cast<elem2_t*>(&w);
+  return elem2_to_floats(v);
 }
 
 // Loads / stores of a pair of adjacent state values in the run-time state dtype.
 __device__ __forceinline__ float2 load_state2(const void* base, size_t elem_off, int f32) {
   if (f32) return *reinterpret_cast<const float2*>(static_cast<const float*>(base) + elem_off);
-  return unpack_bf16x2(*reinterpret_cast<const uint32_t*>(static_cast<const __nv_bfloat16*>(base) + elem_off));
+  return unpack_x2(*reinterpret_cast<const uint32_t*>(static_cast<const elem_t*>(base) + elem_off));
 }
 __device__ __forceinline__ void store_state2(void* base, size_t elem_off, int f32, float lo, float hi) {
   if (f32) *reinterpret_cast<float2*>(static_cast<float*>(base) + elem_off) = make_float2(lo, hi);
-  else *reinterpret_cast<uint32_t*>(static_cast<__nv_bfloat16*>(base) + elem_off) = pack_bf16x2(lo, hi);
+  else *reinterpret_cast<uint32_t*>(static_cast<elem_t*>(base) + elem_off) = pack_x2(lo, hi);
 }
 
 // ------------------------------------------------------------------------------------------------ warp MMA
@@ -237,7 +237,7 @@ __device__ __forceinline__ void store_state2(void* base, size_t elem_off, int f3
 // * 16 k-columns that CTA c produces: element (b, k) sits at  (k16 >> ushift) * slice_elems + b * stride +
 // kofs + (k & (16 << ushift) - 1)  where k16 = k / 16.
 template <int KT, int NT>
-__device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __nv_bfloat16* opnd, int stride, int kofs,
+__device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const elem_t* opnd, int stride, int kofs,
                                               int ushift, int slice_elems, int lane, float (&out)[NT][4]) {
   constexpr int NACC = (NT >= 4) ? 1 : (4 / NT);
   float acc[NACC][NT][4];
@@ -257,8 +257,8 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
       uint32_t b0, b1, b2, b3;
       const int kk = k + (j >> 1);
       ldmatrix_x4(base + (uint32_t)(((kk >> ushift) * slice_elems + (kk & kmask) * 16) * 2), b0, b1, b2, b3);
-      mma_bf16_16816(acc[k % NACC][0], Areg[k], b0, b1);
-      if (k + 1 < KT) mma_bf16_16816(acc[(k + 1) % NACC][0], Areg[k + 1], b2, b3);  // odd KT: second half unused
+      mma_16816(acc[k % NACC][0], Areg[k], b0, b1);
+      if (k + 1 < KT) mma_16816(acc[(k + 1) % NACC][0], Areg[k + 1], b2, b3);  // odd KT: second half unused
     }
   } else {
     // one ldmatrix.x4 covers one k-step of two 8-row batch tiles
@@ -271,8 +271,8 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
       for (int np = 0; np < NT / 2; ++np) {
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(base + koff + (uint32_t)(np * 16 * stride * 2), b0, b1, b2, b3);
-        mma_bf16_16816(acc[k % NACC][2 * np], Areg[k], b0, b1);
-        mma_bf16_16816(acc[k % NACC][2 * np + 1], Areg[k], b2, b3);
+        mma_16816(acc[k % NACC][2 * np], Areg[k], b0, b1);
+        mma_16816(acc[k % NACC][2 * np + 1], Areg[k], b2, b3);
       }
     }
   }
@@ -291,7 +291,7 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const __n
 // from global memory every time step (head dims above 256): fragment k of this warp's row tile sits at asrc[k * 32]
 // (lane offset already applied).  Accumulates into `acc`.  k1 - k0 must be even.
 template <int NT>
-__device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k1, const __nv_bfloat16* opnd, int stride,
+__device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k1, const elem_t* opnd, int stride,
                                                 int kofs, int ushift, int slice_elems, int lane, float (&acc)[NT][4]) {
   const int j = lane >> 3, r = lane & 7;
   const int kmask = (1 << ushift) - 1;
@@ -303,8 +303,8 @@ __device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k
       uint32_t b0, b1, b2, b3;
       const int kk = k + (j >> 1);
       ldmatrix_x4(base + (uint32_t)(((kk >> ushift) * slice_elems + (kk & kmask) * 16) * 2), b0, b1, b2, b3);
-      mma_bf16_16816(acc[0], a0, b0, b1);
-      mma_bf16_16816(acc[0], a1, b2, b3);
+      mma_16816(acc[0], a0, b0, b1);
+      mma_16816(acc[0], a1, b2, b3);
     }
   } else {
     const uint32_t base = smem_u32(opnd + ((j >> 1) * 8 + r) * stride + kofs + (j & 1) * 8);
@@ -316,8 +316,8 @@ __device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k
       for (int np = 0; np < NT / 2; ++np) {
         uint32_t b0, b1, b2, b3;
         ldmatrix_x4(base + koff + (uint32_t)(np * 16 * stride * 2), b0, b1, b2, b3);
-        mma_bf16_16816(acc[2 * np], a, b0, b1);
-        mma_bf16_16816(acc[2 * np + 1], a, b2, b3);
+        mma_16816(acc[2 * np], a, b0, b1);
+        mma_16816(acc[2 * np + 1], a, b2, b3);
       }
     }
   }
@@ -326,7 +326,7 @@ __device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k
 // Same product for MT row tiles that share the operand: out[m] = A_m (16 x 16*KP, fragments Areg[m*KP + k]) times the
 // contiguous tile `opnd[batch row][k]`.  The operand fragments are loaded once per k-step and reused by all MT tiles.
 template <int MT, int KP, int NT>
-__device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const __nv_bfloat16* opnd, int stride, int lane,
+__device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const elem_t* opnd, int stride, int lane,
                                                float (&out)[MT][NT][4]) {
   constexpr int NACC = (MT * NT >= 4) ? 1 : (4 / (MT * NT));
   float acc[NACC][MT][NT][4];
@@ -347,8 +347,8 @@ __device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const __nv_bfl
       ldmatrix_x4(base + (uint32_t)(k * 32), b0, b1, b2, b3);  // k-steps k and k+1 (the latter unused when KP is odd)
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        mma_bf16_16816(acc[k % NACC][m][0], Areg[m * KP + k], b0, b1);
-        if (k + 1 < KP) mma_bf16_16816(acc[(k + 1) % NACC][m][0], Areg[m * KP + k + 1], b2, b3);
+        mma_16816(acc[k % NACC][m][0], Areg[m * KP + k], b0, b1);
+        if (k + 1 < KP) mma_16816(acc[(k + 1) % NACC][m][0], Areg[m * KP + k + 1], b2, b3);
       }
     }
   } else {
@@ -361,8 +361,8 @@ __device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const __nv_bfl
         ldmatrix_x4(base + (uint32_t)((np * 16 * stride + k * 16) * 2), b0, b1, b2, b3);
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-          mma_bf16_16816(acc[k % NACC][m][2 * np], Areg[m * KP + k], b0, b1);
-          mma_bf16_16816(acc[k % NACC][m][2 * np + 1], Areg[m * KP + k], b2, b3);
+          mma_16816(acc[k % NACC][m][2 * np], Areg[m * KP + k], b0, b1);
+          mma_16816(acc[k % NACC][m][2 * np + 1], Areg[m * KP + k], b2, b3);
         }
       }
     }
@@ -421,4 +421,4 @@ template <int CELL, int KT> struct LaunchBounds {
   static constexpr int min_blocks = 1;
 };
 
-}  // namespace frnn
+}  // namespace FRNN_NS

@@ -20,7 +20,7 @@
 #include "frnn_aux.cuh"
 #include "frnn_tc.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 namespace {
 
@@ -33,8 +33,8 @@ constexpr int TC_LBO = 128;          // bytes between core matrices adjacent in 
 constexpr int TC_SBO = TC_KG * 128 + 16;  // bytes between core matrices adjacent in (g,d) / p; +16 spreads the banks
 
 struct DrTcParams {
-  const __nv_bfloat16* dWx;  // [B,T,Gw,N,D]
-  const __nv_bfloat16* dg0;  // [B,T,N,D] (GRU)
+  const elem_t* dWx;  // [B,T,Gw,N,D]
+  const elem_t* dg0;  // [B,T,N,D] (GRU)
   const void* states;        // [S,B,T,N,D]; only s = 0 is read
   const void* s0;            // [S,B,1,N,D]
   float* dR;                 // [Gr,N,D,D] fp32
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
   // 32 consecutive rows (A) / columns (B): quad `sub` of A, quads `sub`, `sub + 4`, ... of B.
   const int kr = tid >> 2, sub = tid & 3;
   const uint32_t kr_off = (uint32_t)(kr >> 3) * TC_LBO + (uint32_t)(kr & 7) * 16;
-  const __nv_bfloat16* a_src[1];   // delta row of quad `sub` at k = 0
+  const elem_t* a_src[1];   // delta row of quad `sub` at k = 0
   size_t a_stride[1];
 #pragma unroll
   for (int j = 0; j < 1; ++j) {
@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
     for (int j = 0; j < 1; ++j) {
       unsigned char* dst = abase + (size_t)(sub * 4) * TC_SBO + kr_off;
       if (krow && a_src[j] != nullptr) {
-        const __nv_bfloat16* src = a_src[j] + (size_t)kk * a_stride[j];
+        const elem_t* src = a_src[j] + (size_t)kk * a_stride[j];
 #pragma unroll
         for (int q = 0; q < 4; ++q) cp_async16(dst + (size_t)q * TC_SBO, src + q * 8);
       } else {
@@ -132,8 +132,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
           for (int q = 0; q < 4; ++q) {
             const float4 v0 = src[2 * q], v1 = src[2 * q + 1];
             uint4 w;
-            w.x = pack_bf16x2(v0.x, v0.y); w.y = pack_bf16x2(v0.z, v0.w);
-            w.z = pack_bf16x2(v1.x, v1.y); w.w = pack_bf16x2(v1.z, v1.w);
+            w.x = pack_x2(v0.x, v0.y); w.y = pack_x2(v0.z, v0.w);
+            w.z = pack_x2(v1.x, v1.y); w.w = pack_x2(v1.z, v1.w);
             *reinterpret_cast<uint4*>(dst + (size_t)q * TC_SBO) = w;
           }
         } else {
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
     while (tt >= T) { tt -= T; ++bb; }
   };
 
-  const uint32_t idesc = instr_desc_bf16(TC_M, D, 1, 1);  // both operands MN-major
+  const uint32_t idesc = instr_desc_16(TC_M, D, 1, 1);  // both operands MN-major
   const uint32_t smem_base = smem_u32(smem);
   bool poisoned = false;
 
@@ -179,7 +179,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
       for (int i = 0; i < TC_KC / 16; ++i) {
         const uint64_t ad = smem_desc(a0 + i * 2 * TC_LBO, TC_LBO, TC_SBO);
         const uint64_t bd = smem_desc(b0 + i * 2 * TC_LBO, TC_LBO, TC_SBO);
-        umma_bf16(tmem_base, ad, bd, idesc, (c > 0 || i > 0) ? 1u : 0u);
+        umma_16(tmem_base, ad, bd, idesc, (c > 0 || i > 0) ? 1u : 0u);
       }
       umma_commit(&bars[s]);
     }
@@ -218,8 +218,8 @@ cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int G
                                      const void* dg0, const void* states, const void* s0, float* dR, unsigned* status,
                                      int sm_count, cudaStream_t stream) {
   DrTcParams p;
-  p.dWx = static_cast<const __nv_bfloat16*>(dWx);
-  p.dg0 = static_cast<const __nv_bfloat16*>(dg0);
+  p.dWx = static_cast<const elem_t*>(dWx);
+  p.dg0 = static_cast<const elem_t*>(dg0);
   p.states = states; p.s0 = s0; p.dR = dR; p.status = status;
   p.cell = cell; p.T = T; p.N = N; p.D = D; p.Gr = Gr; p.Gw = Gw; p.state_f32 = state_f32;
   p.K = (long long)B * T;
@@ -249,4 +249,4 @@ cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int G
   return cudaGetLastError();
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

@@ -20,7 +20,7 @@
 #include "frnn_tc.cuh"
 #include "frnn_tmap.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 namespace {
 
@@ -30,9 +30,9 @@ constexpr int DT_THREADS = 160;                // warps 0-3 drain tensor memory;
 constexpr uint32_t DT_BLK = 64 * DT_KC * 2;    // bytes of one [64 t][64] bf16 block
 
 struct DrTmaParams {
-  const __nv_bfloat16* dWx;  // [B,T,Gw,N,D]
-  const __nv_bfloat16* dg0;  // [B,T,N,D] (GRU)
-  const __nv_bfloat16* s0;   // [S,B,1,N,D]; only s = 0 is read
+  const elem_t* dWx;  // [B,T,Gw,N,D]
+  const elem_t* dg0;  // [B,T,N,D] (GRU)
+  const elem_t* s0;   // [S,B,1,N,D]; only s = 0 is read
   float* dR;                 // [Gr,N,D,D] fp32
   unsigned* status;
   int cell, B, T, N, D, Gr, Gw;
@@ -79,7 +79,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
 
   if (warp == 4) {
     if (lane == 0) {
-      const uint32_t idesc = instr_desc_bf16(128, D, 1, 1);  // both operands MN-major
+      const uint32_t idesc = instr_desc_16(128, D, 1, 1);  // both operands MN-major
       constexpr uint32_t HI = desc_hi(1024, true);
       constexpr uint32_t LBO = (DT_BLK >> 4) << 16;          // 64-wide blocks of m / n follow each other at 8 KB
       const void* tmw = &tm_dwx;
@@ -110,7 +110,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
         const uint32_t a_lo = ((base + (uint32_t)s * stage_bytes) >> 4) | LBO, b_lo = a_lo + ((2 * DT_BLK) >> 4);
 #pragma unroll
         for (uint32_t ks = 0; ks < DT_KC / 16; ++ks)  // 16 rows of a block = 2048 bytes per k-step
-          umma_bf16_parts(tmem, a_lo + 128 * ks, HI, b_lo + 128 * ks, HI, idesc, (ci > 0 || ks > 0) ? 1u : 0u);
+          umma_parts(tmem, a_lo + 128 * ks, HI, b_lo + 128 * ks, HI, idesc, (ci > 0 || ks > 0) ? 1u : 0u);
         umma_commit(&empty[s]);
         if (ci >= 1 && ci - 1 + DT_STAGES < nchunks) {  // refill the stage of the chunk before: its MMAs are done sooner
           if (!mbar_wait_bounded(&empty[(ci - 1) % DT_STAGES], (uint32_t)(((ci - 1) / DT_STAGES) & 1))) {
@@ -139,7 +139,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
     const int b_first = (int)((c_begin + p.chunks_per_b - 1) / p.chunks_per_b), b_last = (int)((c_end - 1) / p.chunks_per_b);
     const size_t ND = (size_t)N * D;
     const bool from_dg0 = p.cell == CELL_GRU && g == 0;
-    const __nv_bfloat16* d0src = from_dg0 ? p.dg0 + (size_t)n * D + d
+    const elem_t* d0src = from_dg0 ? p.dg0 + (size_t)n * D + d
                                           : p.dWx + (size_t)((p.cell == CELL_GRU) ? g - 1 : g) * ND + (size_t)n * D + d;
     const size_t d0stride = (from_dg0 ? (size_t)1 : (size_t)p.Gw) * ND * T;  // elements between batch rows at t = 0
     for (int col0 = 0; col0 < D; col0 += 32) {
@@ -150,7 +150,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
       for (int b = b_first; b <= b_last; ++b) {  // h_{-1}: the products the zero row at t = -1 left out
-        const float dv = __bfloat162float(d0src[(size_t)b * d0stride]);
+        const float dv = elem_to_float(d0src[(size_t)b * d0stride]);
         const uint4* hs = reinterpret_cast<const uint4*>(p.s0 + ((size_t)b * N + n) * D + col0);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -158,7 +158,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
           const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const float2 h2 = unpack_bf16x2(ww[e]);
+            const float2 h2 = unpack_x2(ww[e]);
             v[q * 8 + 2 * e] = fmaf(dv, h2.x, v[q * 8 + 2 * e]);
             v[q * 8 + 2 * e + 1] = fmaf(dv, h2.y, v[q * 8 + 2 * e + 1]);
           }
@@ -189,20 +189,20 @@ cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int 
     const uint64_t dims[5] = {(uint64_t)D, (uint64_t)N, (uint64_t)Gw, (uint64_t)T, (uint64_t)B};
     const uint64_t str[4] = {row, row * N, row * N * Gw, row * N * Gw * T};
     const uint32_t box[5] = {64, 1, 1, DT_KC, 1};
-    if (!encode_bf16_tiles(&tm_dwx, dWx, dims, str, box)) return cudaErrorNotSupported;
+    if (!encode_tiles16(&tm_dwx, dWx, dims, str, box)) return cudaErrorNotSupported;
   }
   {
     // [B,T,N,D] (GRU: delta of the recurrent-only gate) and states[0] = [B,T,N,D]: coordinates (d, n, t, b, 0)
     const uint64_t dims[5] = {(uint64_t)D, (uint64_t)N, (uint64_t)T, (uint64_t)B, 1};
     const uint64_t str[4] = {row, row * N, row * N * T, row * N * T * B};
     const uint32_t box[5] = {64, 1, DT_KC, 1, 1};
-    if (!encode_bf16_tiles(&tm_dg0, cell == CELL_GRU ? dg0 : states, dims, str, box)) return cudaErrorNotSupported;
-    if (!encode_bf16_tiles(&tm_st, states, dims, str, box)) return cudaErrorNotSupported;
+    if (!encode_tiles16(&tm_dg0, cell == CELL_GRU ? dg0 : states, dims, str, box)) return cudaErrorNotSupported;
+    if (!encode_tiles16(&tm_st, states, dims, str, box)) return cudaErrorNotSupported;
   }
   DrTmaParams p;
-  p.dWx = static_cast<const __nv_bfloat16*>(dWx);
-  p.dg0 = static_cast<const __nv_bfloat16*>(dg0);
-  p.s0 = static_cast<const __nv_bfloat16*>(s0);
+  p.dWx = static_cast<const elem_t*>(dWx);
+  p.dg0 = static_cast<const elem_t*>(dg0);
+  p.s0 = static_cast<const elem_t*>(s0);
   p.dR = dR;
   p.status = status;
   p.cell = cell; p.B = B; p.T = T; p.N = N; p.D = D; p.Gr = Gr; p.Gw = Gw;
@@ -227,4 +227,4 @@ cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int 
   return cudaGetLastError();
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

@@ -19,7 +19,7 @@
 #pragma once
 #include "frnn_common.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 // One cell update in fp32.  pre[g] = (R h)[g];  wx[g], bias[g] as laid out by the reference's gate orders
 // (vanilla/lstm.py:19, vanilla/gru.py:16-20, vanilla/elman.py:16-20, vanilla/slstm.py:16-18).
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   const int f32 = p.state_f32;
 
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __nv_bfloat16* hbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                   // [2][CS][BT][US]
+  elem_t* hbuf = reinterpret_cast<elem_t*>(smem_raw);                   // [2][CS][BT][US]
   float* pre = reinterpret_cast<float*>(smem_raw + (size_t)2 * CS * SL * 2);          // [BT][PS]
   const int RL = ring_row_len(U, BT, nthr);  // threads that own items: the ring has one slot row per such thread
   uint32_t* ring = reinterpret_cast<uint32_t*>(pre + (size_t)BT * PS);                // [kStages][Gw][IPT][RL]
@@ -121,7 +121,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   bool it_on[IPT], it_ok[IPT];
   const float* pre_it[IPT];            // &pre[bl][2*up]
   uint32_t hloc_it[IPT];               // element offset of (bl, 2*up) inside this CTA's slice
-  const __nv_bfloat16* wx_pf[IPT];     // Wx of the next step to prefetch
+  const elem_t* wx_pf[IPT];     // Wx of the next step to prefetch
   unsigned char* st_ptr[IPT];          // states[0][b][t][n][d] of the current step (bytes)
   uint32_t* ch_ptr[IPT];               // activation cache of the current step
   float bias[IPT][Gt][2], st[IPT][S][2];
@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     ch_ptr[i] = reinterpret_cast<uint32_t*>(p.cache) + cta_lin * GCA * nitems + (it_on[i] ? q : 0);
 #pragma unroll
     for (int g = 0; g < Gt; ++g) {
-      const float2 bv = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p.bias + ((size_t)g * N + n) * D + d));
+      const float2 bv = unpack_x2(*reinterpret_cast<const uint32_t*>(p.bias + ((size_t)g * N + n) * D + d));
       bias[i][g][0] = bv.x; bias[i][g][1] = bv.y;
     }
 #pragma unroll
@@ -160,7 +160,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     const int bg = bt0 + bl, k = 2 * dp;
     float2 v = make_float2(0.f, 0.f);
     if (bg < B) v = load_state2(p.s0, ((size_t)bg) * ND + (size_t)n * D + k, f32);
-    *reinterpret_cast<uint32_t*>(hbuf + (size_t)(k / U) * SL + bl * US + (k % U)) = pack_bf16x2(v.x, v.y);
+    *reinterpret_cast<uint32_t*>(hbuf + (size_t)(k / U) * SL + bl * US + (k % U)) = pack_x2(v.x, v.y);
   }
 
   // ---- Wx prefetch ring: stage s <- step s
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     cp_async_wait<kStages - 1>();
     FRNN_PROF_MARK(3);
     float cch[IPT][GCA][2];
-    __nv_bfloat16* hdst = hbuf + (size_t)nxt * CS * SL + (size_t)crank * SL;
+    elem_t* hdst = hbuf + (size_t)nxt * CS * SL + (size_t)crank * SL;
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_on[i]) continue;
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       }
 #pragma unroll
       for (int g = 0; g < Gw; ++g) {
-        const float2 v = unpack_bf16x2(ring[((size_t)(stage * Gw + g) * IPT + i) * RL + tid]);
+        const float2 v = unpack_x2(ring[((size_t)(stage * Gw + g) * IPT + i) * RL + tid]);
         wxv[0][g] = v.x; wxv[1][g] = v.y;
       }
 #pragma unroll
@@ -281,9 +281,9 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
 #pragma unroll
         for (int k = 0; k < GC; ++k) cch[i][k][e] = cv[k];
       }
-      const uint32_t hv = pack_bf16x2(st[i][0][0], st[i][0][1]);
+      const uint32_t hv = pack_x2(st[i][0][0], st[i][0][1]);
       // the recurrence continues from the bf16-rounded h, the value every consumer of `states` sees
-      if (!f32) { const float2 r = unpack_bf16x2(hv); st[i][0][0] = r.x; st[i][0][1] = r.y; }
+      if (!f32) { const float2 r = unpack_x2(hv); st[i][0][0] = r.x; st[i][0][1] = r.y; }
       *reinterpret_cast<uint32_t*>(hdst + hloc_it[i]) = hv;
     }
     if (CS > 1) fence_proxy_async_smem();  // make the slice visible to the bulk-copy engine
@@ -302,12 +302,12 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
 #pragma unroll
       for (int s = 0; s < S; ++s) {
         if (f32) *reinterpret_cast<float2*>(st_ptr[i] + s * st_sstride) = make_float2(st[i][s][0], st[i][s][1]);
-        else *reinterpret_cast<uint32_t*>(st_ptr[i] + s * st_sstride) = pack_bf16x2(st[i][s][0], st[i][s][1]);
+        else *reinterpret_cast<uint32_t*>(st_ptr[i] + s * st_sstride) = pack_x2(st[i][s][0], st[i][s][1]);
       }
       st_ptr[i] += ND * st_esz;
       if (GC > 0 && p.cache != nullptr) {
 #pragma unroll
-        for (int k = 0; k < GC; ++k) ch_ptr[i][(size_t)k * nitems] = pack_bf16x2(cch[i][k][0], cch[i][k][1]);
+        for (int k = 0; k < GC; ++k) ch_ptr[i][(size_t)k * nitems] = pack_x2(cch[i][k][0], cch[i][k][1]);
         ch_ptr[i] += ch_step;
       }
     }
@@ -323,4 +323,4 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   FRNN_PROF_DUMP(p.status);
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

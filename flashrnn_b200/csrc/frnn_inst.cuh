@@ -7,7 +7,7 @@
 #include "frnn_bwd.cuh"
 #include "frnn_fwd.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 #if FRNN_INST_BWD
 
@@ -71,4 +71,4 @@ LoopKernel FRNN_INST_NAME(int kt, int nt) {
 
 #endif
 
-}  // namespace frnn
+}  // namespace FRNN_NS

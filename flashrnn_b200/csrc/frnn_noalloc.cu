@@ -5,6 +5,7 @@
 // or an embedding runtime that forbids cudaMalloc on its hot path because the call synchronises the device.
 // For them the forward's scratch (status block + the recurrent matrix repacked into tensor-core fragments)
 // lives in a fixed array inside the library image instead of a caller-provided workspace.
+#ifndef FRNN_F16  // compiled once: frnn_query / frnn_forward below pick the kernels by frnn_problem.dtype_io
 #include "../../include/frnn.h"
 
 #include <cuda_runtime.h>
@@ -48,7 +49,7 @@ extern "C" int frnn_forward_noalloc(const frnn_problem* problem, const frnn_fwd_
   frnn_plan plan;
   const int rc = frnn_query(problem, &plan);
   if (rc != FRNN_OK) return rc;
-  // what the forward touches of a workspace: the 256-byte status block followed by R as fragments (bf16, same
+  // what the forward touches of a workspace: the 256-byte status block followed by R as fragments (16-bit elements, same
   // size as R).  Gate count of R: 4 (lstm, slstm), 3 (gru), 1 (elman).
   const size_t gr = problem->cell == FRNN_CELL_GRU ? 3 : (problem->cell == FRNN_CELL_ELMAN ? 1 : 4);
   const size_t need = 256 + align_up(gr * (size_t)problem->N * problem->D * problem->D * 2, 256);
@@ -60,3 +61,5 @@ extern "C" int frnn_forward_noalloc(const frnn_problem* problem, const frnn_fwd_
   a.workspace = scratch;  // frnn_forward clears the status block and rewrites the fragments on every call
   return frnn_forward(&plan, &a, stream);
 }
+
+#endif  // FRNN_F16

@@ -3,7 +3,7 @@
 #pragma once
 #include "frnn_common.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 // ---- tensor memory
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
@@ -17,7 +17,7 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // D(tmem, fp32) (+)= A(smem) * B(smem), bf16 operands; `accumulate` == 0 overwrites D
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -25,7 +25,7 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
 }
 // Same, descriptors given as 32-bit halves: `lo` = (address >> 4) | (lbo >> 4) << 16 changes from MMA to MMA, `hi`
 // (sbo >> 4, version, swizzle mode: desc_hi()) is a constant of the operand's layout.
-__device__ __forceinline__ void umma_bf16_parts(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+__device__ __forceinline__ void umma_parts(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                                 uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
@@ -77,9 +77,10 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
   return smem_desc(saddr, lbo, sbo) | ((uint64_t)2 << 61);
 }
-// instruction descriptor of kind::f16: fp32 accumulate, bf16 A and B; a_mn / b_mn = 1 for MN-major operands
-__host__ __device__ constexpr uint32_t instr_desc_bf16(int M, int N, int a_mn, int b_mn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) |
+// instruction descriptor of kind::f16: fp32 accumulate, A and B of the element type (format field 1 = bf16, 0 = f16);
+// a_mn / b_mn = 1 for MN-major operands
+__host__ __device__ constexpr uint32_t instr_desc_16(int M, int N, int a_mn, int b_mn) {
+  return (1u << 4) | ((kF16 ? 0u : 1u) << 7) | ((kF16 ? 0u : 1u) << 10) | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) |
          ((uint32_t)(M >> 4) << 24);
 }
 
@@ -109,4 +110,4 @@ template <int N> __device__ __forceinline__ void bulk_wait_group() {
   asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

@@ -23,7 +23,7 @@
 #include "frnn_tc.cuh"
 #include "frnn_tmap.cuh"
 
-namespace frnn {
+namespace FRNN_NS {
 
 namespace {
 
@@ -62,14 +62,14 @@ __device__ __forceinline__ uint32_t sw128_pair(uint32_t row, uint32_t chunk, uin
 }
 
 __device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
-  return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+  return make_uint4(pack_x2(v[0], v[1]), pack_x2(v[2], v[3]), pack_x2(v[4], v[5]), pack_x2(v[6], v[7]));
 }
 
 // ================================================================================================ forward
 struct WideFwdParams {
-  const __nv_bfloat16* R;     // [1,N,64,64]
-  const __nv_bfloat16* bias;  // [1,N,64]
-  const __nv_bfloat16* s0;    // [1,B,1,N,64]
+  const elem_t* R;     // [1,N,64,64]
+  const elem_t* bias;  // [1,N,64]
+  const elem_t* s0;    // [1,B,1,N,64]
   unsigned* status;
   int B, T, N;
   int test_drop;  // test hook: the copy of one tile (step index 2) is announced to its barrier but never issued
@@ -104,22 +104,22 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 
   // ---- operands written once: R (as [d][p], K-major), the identity, the ones column, the bias row, h_{-1}
   {
-    const __nv_bfloat16* Rn = p.R + (size_t)n * WD * WD;
+    const elem_t* Rn = p.R + (size_t)n * WD * WD;
     for (int c = tid; c < WD * 8; c += W_THREADS) {
       const uint32_t d = c >> 3, j = c & 7;
       *reinterpret_cast<uint4*>(sm + WF_OFF_R + sw128(d, j)) = *reinterpret_cast<const uint4*>(Rn + d * WD + j * 8);
-      const uint32_t w = (d & 7) >> 1, one = ((d >> 3) == j) ? (0x3F80u << (16 * (d & 1))) : 0u;  // bf16 1.0 at k = d
+      const uint32_t w = (d & 7) >> 1, one = ((d >> 3) == j) ? (kOneBits << (16 * (d & 1))) : 0u;  // 1.0 at k = d
       *reinterpret_cast<uint4*>(sm + WF_OFF_I + sw128(d, j)) =
           make_uint4(w == 0 ? one : 0u, w == 1 ? one : 0u, w == 2 ? one : 0u, w == 3 ? one : 0u);
     }
     for (int r = tid; r < WM; r += W_THREADS) {
       unsigned char* q = sm + WF_OFF_ONES + (r >> 3) * 256 + (r & 7) * 16;
-      *reinterpret_cast<uint4*>(q) = make_uint4(0x3F80u, 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(q) = make_uint4(kOneBits, 0u, 0u, 0u);
       *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
     }
     for (int d = tid; d < WD; d += W_THREADS) {
       unsigned char* q = sm + WF_OFF_BIAS + (d >> 3) * 256 + (d & 7) * 16;
-      *reinterpret_cast<uint4*>(q) = make_uint4((uint32_t)__bfloat16_as_ushort(p.bias[(size_t)n * WD + d]), 0u, 0u, 0u);
+      *reinterpret_cast<uint4*>(q) = make_uint4(elem_bits(p.bias[(size_t)n * WD + d]), 0u, 0u, 0u);
       *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
     }
     if (tid < WM) {  // h_{-1} -> h tile 2 (step t reads tile (t + 2) % 3 and writes tile t % 3); PAIR: slot 1 of buffer 0
@@ -148,7 +148,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
   if (warp == 4) {
     if (lane == 0) {
       // ------------------------------------------------------------ producer: bulk copies and MMAs
-      const uint32_t idesc = instr_desc_bf16(WM, WD, 0, 0);
+      const uint32_t idesc = instr_desc_16(WM, WD, 0, 0);
       const void* tmw = &tm_wx;
       const void* tms = &tm_states;
       // descriptor halves: the low word carries the address (16-byte units), the high word is a constant of the layout
@@ -176,8 +176,8 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I + ones * bias
           const uint32_t a = wx_lo + ((t >> 1) % NP) * PAIR16 + (t & 1) * SLOT16, d = tmem + (t & 1) * WD;
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI2, i_lo + 2 * k, HI, idesc, k);
-          umma_bf16_parts(d, ones_lo, HIP, bias_lo, HIP, idesc, 1u);
+          for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI2, i_lo + 2 * k, HI, idesc, k);
+          umma_parts(d, ones_lo, HIP, bias_lo, HIP, idesc, 1u);
         };
         for (int q = 0; q < P && q < NP; ++q) load_pair(q);
         bool ok = wait_pair(0);
@@ -193,7 +193,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
           const uint32_t hb = (uint32_t)((t + 1) >> 1) & 1u;  // buffer of h_{t-1}
           const uint32_t a = h_lo + hb * PAIR16 + ((t - 1) & 1) * SLOT16, d = tmem + (t & 1) * WD;
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI2, r_lo + 2 * k, HI, idesc, 1u);
+          for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI2, r_lo + 2 * k, HI, idesc, 1u);
           umma_commit(&acc_full[t & 1]);
           if (t > 0 && !(t & 1)) {
             // h_{t-2}, h_{t-1} -> states[0][b0.., t-2 .. t-1, n, :]; the Wx box of those steps was consumed by MMAs that
@@ -235,8 +235,8 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I + ones * bias, from ring slot cs
         const uint32_t a = wx_lo + cs * TILE16, d = tmem + (t & 1) * WD;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI, i_lo + 2 * k, HI, idesc, k);
-        umma_bf16_parts(d, ones_lo, HIP, bias_lo, HIP, idesc, 1u);
+        for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, i_lo + 2 * k, HI, idesc, k);
+        umma_parts(d, ones_lo, HIP, bias_lo, HIP, idesc, 1u);
         ++waited;
         if (++cs == WF_STAGES) { cs = 0; cpar ^= 1u; }
       };
@@ -258,7 +258,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         WPROF_MARK(1);
         const uint32_t a = h_lo + hr * TILE16, d = tmem + (t & 1) * WD;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc, 1u);
+        for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc, 1u);
         umma_commit(&acc_full[t & 1]);
         WPROF_MARK(2);
         if (t > 0) {  // h_{t-1} -> states[0][b0.., t-1, n, :]
@@ -371,8 +371,8 @@ wide_copy_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constan
 
 // ================================================================================================ backward
 struct WideBwdParams {
-  const __nv_bfloat16* R;  // [1,N,64,64]
-  __nv_bfloat16* ds0;      // [1,B,1,N,64]
+  const elem_t* R;  // [1,N,64,64]
+  elem_t* ds0;      // [1,B,1,N,64]
   float* dR;               // fp32 [1,N,64,64], accumulated with atomics
   float* dbias;            // fp32 [1,N,64]
   unsigned* status;
@@ -422,18 +422,18 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
   const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T;
 
   {
-    const __nv_bfloat16* Rn = p.R + (size_t)n * WD * WD;
+    const elem_t* Rn = p.R + (size_t)n * WD * WD;
     for (int c = tid; c < WD * 8; c += W_THREADS) {
       const uint32_t pp = c >> 3, j = c & 7;  // row p, chunk of d = 8j .. 8j+7:  Rk[p][d] = R[d][p]
       uint32_t w[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const uint32_t lo = __bfloat16_as_ushort(Rn[(j * 8 + 2 * i) * WD + pp]);
-        const uint32_t hi = __bfloat16_as_ushort(Rn[(j * 8 + 2 * i + 1) * WD + pp]);
+        const uint32_t lo = elem_bits(Rn[(j * 8 + 2 * i) * WD + pp]);
+        const uint32_t hi = elem_bits(Rn[(j * 8 + 2 * i + 1) * WD + pp]);
         w[i] = lo | (hi << 16);
       }
       *reinterpret_cast<uint4*>(sm + WB_OFF_R + sw128(pp, j)) = make_uint4(w[0], w[1], w[2], w[3]);
-      const uint32_t wi = (pp & 7) >> 1, one = ((pp >> 3) == j) ? (0x3F80u << (16 * (pp & 1))) : 0u;
+      const uint32_t wi = (pp & 7) >> 1, one = ((pp >> 3) == j) ? (kOneBits << (16 * (pp & 1))) : 0u;
       *reinterpret_cast<uint4*>(sm + WB_OFF_I + sw128(pp, j)) =
           make_uint4(wi == 0 ? one : 0u, wi == 1 ? one : 0u, wi == 2 ? one : 0u, wi == 3 ? one : 0u);
     }
@@ -457,8 +457,8 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
   if (warp == 4) {
     if (lane == 0) {
       // ------------------------------------------------------------ producer
-      const uint32_t idesc_kk = instr_desc_bf16(WM, WD, 0, 0);  // dh: [128 b] x [64 p], K = d
-      const uint32_t idesc_mm = instr_desc_bf16(WD, WD, 1, 1);  // dR: [64 d] x [64 p], K = b; both operands MN-major
+      const uint32_t idesc_kk = instr_desc_16(WM, WD, 0, 0);  // dh: [128 b] x [64 p], K = d
+      const uint32_t idesc_mm = instr_desc_16(WD, WD, 1, 1);  // dR: [64 d] x [64 p], K = b; both operands MN-major
       const void* tmh = &tm_states;
       const void* tm0 = &tm_s0;
       const void* tme = &tm_dstates;
@@ -503,7 +503,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           const int te = T - 1 - j, r = P - 1 - (te >> 1);
           const uint32_t a = er_lo + (uint32_t)(r & 1) * PAIR16 + (uint32_t)(te & 1) * 64u, d = tmem + (j & 1) * WD;
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI2, i_lo + 2 * k, HI, idesc_kk, k);
+          for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI2, i_lo + 2 * k, HI, idesc_kk, k);
           if (!(te & 1)) {  // both tiles of the box are consumed once these MMAs complete
             umma_commit(&e_free[r & 1]);
             e_reload = r;
@@ -546,7 +546,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
             const uint32_t acc = tmem + ((j + 1) & 1) * WD;
 #pragma unroll
             for (uint32_t k = 0; k < 4; ++k)
-              umma_bf16_parts(acc, dl + 2 * k, HI2, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
+              umma_parts(acc, dl + 2 * k, HI2, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
             umma_commit(&acc_full[(j + 1) & 1]);
             if (!(tt & 1)) {  // deltas of times tt, tt+1 -> dWx[b0.., tt .. tt+1, 0, n, :] (tt = T-1: the second tile is clipped)
               tma_store_5d(tmd, dt, 0, 0, tt, bh, n);
@@ -564,13 +564,13 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
               const uint32_t hl = hr_lo + (uint32_t)(rq & 1) * PAIR16 + (uint32_t)((tt - 1) & 1) * 64u;
 #pragma unroll
               for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = two 8-row groups, 4096 bytes apart per k-step
-                umma_bf16_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 256 * ks, HI2, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+                umma_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 256 * ks, HI2, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
               if (!((tt - 1) & 1)) umma_commit(&h_free[rq & 1]);  // that was the last read of the box by an MMA
             } else {
               const uint32_t hl = hr_lo + (uint32_t)(rq & 1) * PAIR16;
 #pragma unroll
               for (uint32_t ks = 0; ks < 8; ++ks)
-                umma_bf16_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+                umma_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
             }
             if (!reload_e()) { ok = false; break; }
             if (j + 2 < T) {
@@ -607,7 +607,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       auto issue_pre = [&](int j) {  // acc[j & 1] = dh_ext_j * I
         const uint32_t a = er_lo + (j % WB_STAGES) * TILE16, d = tmem + (j & 1) * WD;
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) umma_bf16_parts(d, a + 2 * k, HI, i_lo + 2 * k, HI, idesc_kk, k);
+        for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, i_lo + 2 * k, HI, idesc_kk, k);
       };
       for (int q = 0; q <= T && q < WB_STAGES; ++q) load_h(q);
       for (int j = 0; j < T && j < WB_STAGES; ++j) load_e(j);
@@ -639,7 +639,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           const uint32_t acc = tmem + ((j + 1) & 1) * WD;
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k)
-            umma_bf16_parts(acc, dl + 2 * k, HI, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
+            umma_parts(acc, dl + 2 * k, HI, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
           umma_commit(&acc_full[(j + 1) & 1]);
           WPROF_MARK(2);
           tma_store_5d(tmd, dt, 0, n, 0, T - 1 - j, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
@@ -652,7 +652,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           const uint32_t hl = hr_lo + ((j + 1) % WB_STAGES) * TILE16;
 #pragma unroll
           for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = 2048 bytes per k-step
-            umma_bf16_parts(tmem + 2 * WD, dl + 128 * ks, HI, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
+            umma_parts(tmem + 2 * WD, dl + 128 * ks, HI, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
           WPROF_MARK(5);
           // h tile j-1: its row threads (step j-1) and its dR MMAs (step j-2, completed before the accumulator of
           // step j was signalled) are done; cotangent tile j: consumed by MMAs that completed before step j started
@@ -714,7 +714,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         float v[8];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float2 h2 = unpack_bf16x2(hw[i]);
+          const float2 h2 = unpack_x2(hw[i]);
           const float g0 = __uint_as_float(c < 4 ? r0[c * 8 + 2 * i] : r1[(c - 4) * 8 + 2 * i]);
           const float g1 = __uint_as_float(c < 4 ? r0[c * 8 + 2 * i + 1] : r1[(c - 4) * 8 + 2 * i + 1]);
           v[2 * i] = g0 * (1.f - h2.x * h2.x);
@@ -803,7 +803,7 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
 bool encode_tiles(CUtensorMap* tm, const void* base, const uint64_t (&dims)[5], const uint64_t (&strides)[4], int batch_dim) {
   uint32_t box[5] = {WD, 1, 1, 1, 1};
   box[batch_dim] = WM;
-  return encode_bf16_tiles(tm, base, dims, strides, box);
+  return encode_tiles16(tm, base, dims, strides, box);
 }
 
 // [B,T,1,N,64] (Wx, dWx): coordinates (0, n, 0, t, b)
@@ -828,7 +828,7 @@ bool map_pairs(CUtensorMap* tm, const void* base, int B, int T, int N) {
   const uint64_t dims[5] = {WD, 8, (uint64_t)T, (uint64_t)B / 8, (uint64_t)N};
   const uint64_t strides[4] = {sb, st, sb * 8, row};
   const uint32_t box[5] = {WD, 8, 2, WM / 8, 1};
-  return encode_bf16_tiles(tm, base, dims, strides, box);
+  return encode_tiles16(tm, base, dims, strides, box);
 }
 #ifdef FRNN_WIDE_NOPAIR  // development aid: one time step per copy everywhere
 bool pairs_ok(int, int) { return false; }
@@ -851,9 +851,9 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
            : (!map_btgnd(&tm_wx, Wx, B, T, N) || !map_sbtnd(&tm_st, states, B, T, N)))
     return cudaErrorNotSupported;
   WideFwdParams p;
-  p.R = static_cast<const __nv_bfloat16*>(R);
-  p.bias = static_cast<const __nv_bfloat16*>(bias);
-  p.s0 = static_cast<const __nv_bfloat16*>(s0);
+  p.R = static_cast<const elem_t*>(R);
+  p.bias = static_cast<const elem_t*>(bias);
+  p.s0 = static_cast<const elem_t*>(s0);
   p.status = status;
   p.B = B; p.T = T; p.N = N;
   p.test_drop = test_drop;
@@ -880,8 +880,8 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
       !(pair ? map_pairs(&tm_dwx, dWx, B, T, N) : map_btgnd(&tm_dwx, dWx, B, T, N)))
     return cudaErrorNotSupported;
   WideBwdParams p;
-  p.R = static_cast<const __nv_bfloat16*>(R);
-  p.ds0 = static_cast<__nv_bfloat16*>(ds0);
+  p.R = static_cast<const elem_t*>(R);
+  p.ds0 = static_cast<elem_t*>(ds0);
   p.dR = dR;
   p.dbias = dbias;
   p.status = status;
@@ -895,4 +895,4 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
   return cudaGetLastError();
 }
 
-}  // namespace frnn
+}  // namespace FRNN_NS

@@ -8,8 +8,10 @@ reference (flashrnn/flashrnn/flashrnn.py:124-207, 1093-1135).  What changed on p
 * tensors are consumed and produced in the user layouts directly (no permute + ``.contiguous()`` copies,
   reference flashrnn.py:1049-1057, 1130-1135);
 * GRU runs fused (the reference silently switches it to the alternating backend, flashrnn.py:280-284);
-* states may be kept in float32 while Wx/R/b are bfloat16 (``dtype_s="float32"`` or by passing float32
-  ``states``), which the reference's fused kernel cannot express.
+* states may be kept in float32 while Wx/R/b are bfloat16 / float16 (``dtype_s="float32"`` or by passing float32
+  ``states``), which the reference's fused kernel cannot express;
+* ``dtype`` is ``"bfloat16"`` or ``"float16"`` (the MMA operand type); accumulation and gate math are fp32 for both
+  (the reference accumulates float16 in float16, fused/flashrnn_fused_forward.cu), ``"float32"`` raises.
 """
 from __future__ import annotations
 
@@ -172,13 +174,15 @@ class _FrnnFunction(torch.autograd.Function):
     def forward(ctx, Wx, R, b, s0, cfg: FlashRNNConfig, training: bool, grad_group):
         B, T, _, N, D = Wx.shape
         state_dtype = cfg.torch_dtype_s
+        kdt = cfg.torch_dtype  # element type the kernels compute in: bfloat16 or float16
         in_dtypes = (Wx.dtype, R.dtype, b.dtype, s0.dtype)
-        Wx_k = Wx.to(torch.bfloat16).contiguous()
-        R_k = R.to(torch.bfloat16).contiguous()
-        b_k = b.to(torch.bfloat16).contiguous()
+        Wx_k = Wx.to(kdt).contiguous()
+        R_k = R.to(kdt).contiguous()
+        b_k = b.to(kdt).contiguous()
         s0_k = s0.to(state_dtype).contiguous()
         prob = _native.make_problem(cfg.function, B, T, N, D, state_dtype == torch.float32, training,
-                                    cfg.forward_clipval, cfg.gradient_recurrent_clipval, cfg.gradient_recurrent_cut)
+                                    cfg.forward_clipval, cfg.gradient_recurrent_clipval, cfg.gradient_recurrent_cut,
+                                    f16=kdt == torch.float16)
         plan = _native.query(prob, cfg.cluster_size, cfg.batch_tile)
         plan.test_drop_exchange = 1 if cfg._test_drop_exchange else 0
         dev = Wx.device
@@ -206,7 +210,7 @@ class _FrnnFunction(torch.autograd.Function):
         plan, ws = ctx.plan, ctx.ws
         dev = states.device
         dstates = dstates.to(states.dtype).contiguous()
-        dWx = torch.empty(ctx.wx_shape, dtype=torch.bfloat16, device=dev)
+        dWx = torch.empty(ctx.wx_shape, dtype=R_k.dtype, device=dev)
         ds0 = torch.empty_like(s0_k)
         args = _native.FrnnBwdArgs(_ptr(R_k), _ptr(s0_k), _ptr(states), _ptr(cache), _ptr(dstates), _ptr(dWx), _ptr(ds0), _ptr(ws))
         L = _native.lib()
@@ -220,7 +224,7 @@ class _FrnnFunction(torch.autograd.Function):
                 # batch sharding: every rank holds the gradient of its batch slice; sum them (fp32, one packed buffer)
                 torch.distributed.all_reduce(grads, group=ctx.grad_group if ctx.grad_group is not True else None)
             dR = torch.empty_like(R_k)
-            db = torch.empty(ctx.b_shape, dtype=torch.bfloat16, device=dev)
+            db = torch.empty(ctx.b_shape, dtype=R_k.dtype, device=dev)
             _native.check("frnn_finalize_grads",
                           L.frnn_finalize_grads(ctypes.byref(plan), _ptr(grads), _ptr(dR), _ptr(db), _stream_ptr(dev)))
         dt = ctx.in_dtypes
@@ -254,8 +258,12 @@ def flashrnn(
             f"{_NATIVE_BACKENDS} is provided (no Triton, no alternating cuBLAS backend, no CPU/PyTorch path)")
     if config.backend not in _NATIVE_BACKENDS:
         raise ValueError(f"Unknown backend {config.backend}")
-    if config.dtype != "bfloat16":
-        raise NotImplementedError(f"dtype '{config.dtype}': the sm_100a kernels compute in bfloat16 with fp32 accumulation")
+    if config.dtype not in ("bfloat16", "float16"):
+        raise NotImplementedError(f"dtype '{config.dtype}': the sm_100a kernels compute in bfloat16 or float16 with fp32 accumulation")
+    if config.dtype_s in ("bfloat16", "float16"):
+        config.dtype_s = config.dtype  # 16-bit states live in the kernel dtype (inputs of the other 16-bit type are cast)
+    elif config.dtype_s != "float32":
+        raise NotImplementedError(f"states in '{config.dtype_s}': states are kept in the kernel dtype or in float32")
     if not Wx.is_cuda:
         raise RuntimeError("flashrnn_b200 runs on CUDA tensors only; there is no CPU fallback")
     if Wx.dim() != 5 or R.dim() != 4 or b.dim() != 3:

@@ -26,7 +26,7 @@ class FlashRNNStepper:
     internal buffer, overwritten by the next call) and carries the last state into the next call."""
 
     def __init__(self, R: torch.Tensor, b: torch.Tensor, function: str = "lstm", batch_size: int = 1, chunk: int = 1,
-                 dtype_s: str = "bfloat16", states: Optional[torch.Tensor] = None):
+                 dtype_s: Optional[str] = None, states: Optional[torch.Tensor] = None, dtype: str = "bfloat16"):
         if function not in rnn_function_registry:
             raise AssertionError(f"unknown function {function}")
         if not R.is_cuda:
@@ -37,12 +37,15 @@ class FlashRNNStepper:
             raise ValueError(f"shape mismatch for function '{function}': R{tuple(R.shape)} b{tuple(b.shape)}")
         self.function, self.B, self.chunk, self.N, self.D, self.S, self.Gw = function, batch_size, chunk, N, D, S, Gw
         dev = R.device
-        sdt = DTYPE_DICT[dtype_s]
-        if sdt not in (torch.bfloat16, torch.float32):
-            raise NotImplementedError("states are bfloat16 or float32")
-        self._R = R.detach().to(torch.bfloat16).contiguous()
-        self._b = b.detach().to(torch.bfloat16).contiguous()
-        prob = _native.make_problem(function, batch_size, chunk, N, D, sdt == torch.float32, False)
+        if dtype not in ("bfloat16", "float16"):
+            raise NotImplementedError(f"dtype '{dtype}': the sm_100a kernels compute in bfloat16 or float16")
+        self._kdt = DTYPE_DICT[dtype]
+        sdt = DTYPE_DICT[dtype_s or dtype]
+        if sdt not in (self._kdt, torch.float32):
+            raise NotImplementedError("states are kept in the kernel dtype or in float32")
+        self._R = R.detach().to(self._kdt).contiguous()
+        self._b = b.detach().to(self._kdt).contiguous()
+        prob = _native.make_problem(function, batch_size, chunk, N, D, sdt == torch.float32, False, f16=self._kdt == torch.float16)
         self._plan = _native.query(prob)
         self._s0 = torch.zeros((S, batch_size, 1, N, D), dtype=sdt, device=dev)
         self._out = torch.empty((S, batch_size, chunk, N, D), dtype=sdt, device=dev)
@@ -64,8 +67,8 @@ class FlashRNNStepper:
         return self._s0
 
     def step(self, Wx: torch.Tensor) -> torch.Tensor:
-        if tuple(Wx.shape) != (self.B, self.chunk, self.Gw, self.N, self.D) or Wx.dtype != torch.bfloat16 or not Wx.is_contiguous():
-            raise ValueError(f"expected contiguous bfloat16 Wx{(self.B, self.chunk, self.Gw, self.N, self.D)}")
+        if tuple(Wx.shape) != (self.B, self.chunk, self.Gw, self.N, self.D) or Wx.dtype != self._kdt or not Wx.is_contiguous():
+            raise ValueError(f"expected contiguous {self._kdt} Wx{(self.B, self.chunk, self.Gw, self.N, self.D)}")
         dev = Wx.device
         self._plan.keep_packed_r = 1 if self._packed else 0
         args = _native.FrnnFwdArgs(_ptr(Wx), _ptr(self._R), _ptr(self._b), _ptr(self._s0), _ptr(self._out), None, _ptr(self._ws))

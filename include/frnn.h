@@ -31,7 +31,7 @@ extern "C" {
 
 /* cells: gate/state counts follow the reference registry flashrnn/flashrnn/flashrnn.py:49-71 */
 enum { FRNN_CELL_LSTM = 0, FRNN_CELL_GRU = 1, FRNN_CELL_ELMAN = 2, FRNN_CELL_SLSTM = 3 };
-enum { FRNN_DTYPE_BF16 = 0, FRNN_DTYPE_F32 = 1 };
+enum { FRNN_DTYPE_BF16 = 0, FRNN_DTYPE_F32 = 1, FRNN_DTYPE_F16 = 2 };
 
 /* status codes (negative = validation) */
 enum {
@@ -53,8 +53,9 @@ enum {
 typedef struct frnn_problem {
   int32_t cell;          /* FRNN_CELL_*                                             */
   int32_t B, T, N, D;    /* batch, time steps, heads, head dim                     */
-  int32_t dtype_io;      /* dtype of Wx, R, b, dWx, dR, db : FRNN_DTYPE_BF16        */
-  int32_t dtype_state;   /* dtype of s0, states, dstates, ds0 : BF16 or F32         */
+  int32_t dtype_io;      /* dtype of Wx, R, b, dWx, dR, db : FRNN_DTYPE_BF16 or _F16 (MMA operand type; accumulation and
+                            gate math are fp32 either way)                           */
+  int32_t dtype_state;   /* dtype of s0, states, dstates, ds0 : same as dtype_io, or F32 */
   int32_t training;      /* 1: forward writes the activation cache for backward     */
   float forward_clip;    /* > 0: clamp the new h to [-v, v]   (forward_clipval)     */
   float grad_clip;       /* > 0: clamp the recurrent dh to [-v, v] (gradient_recurrent_clipval) */

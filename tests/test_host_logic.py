@@ -116,7 +116,9 @@ def test_no_cpu_fallback_and_removed_backends():
     with pytest.raises(ValueError):
         flashrnn(Wx, R, b, function="lstm", backend="tpu")
     with pytest.raises(NotImplementedError):
-        flashrnn(Wx, R, b, function="lstm", dtype="float16")
+        flashrnn(Wx, R, b, function="lstm", dtype="float32")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):  # float16 is a kernel dtype; still no CPU path
+        flashrnn(Wx.half(), R.half(), b.half(), function="lstm", dtype="float16")
 
 
 def test_stepper_has_no_cpu_path_and_checks_shapes():

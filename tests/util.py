@@ -17,26 +17,27 @@ H_MAX_ABS = 2e-2
 GRAD_REL_L2 = 1e-2
 
 
-def bf16_round(x: torch.Tensor) -> torch.Tensor:
-    return x.to(torch.bfloat16).to(torch.float64)
+def bf16_round(x: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    return x.to(dtype).to(torch.float64)
 
 
-def make_inputs(function, B, T, N, D, seed=0, random_init=False, bias_scale=0.1, state_f32=False):
-    """fp64 tensors already rounded to bf16 values (states rounded to bf16 unless ``state_f32``)."""
+def make_inputs(function, B, T, N, D, seed=0, random_init=False, bias_scale=0.1, state_f32=False, dtype=torch.bfloat16):
+    """fp64 tensors already rounded to values of ``dtype`` (bfloat16 or float16; states too unless ``state_f32``)."""
+    rnd = lambda x: bf16_round(x, dtype)
     Gr, Gw, Gt, S = cell_dims(function)
     g = torch.Generator().manual_seed(seed)
-    Wx = bf16_round(torch.randn(B, T, Gw, N, D, generator=g, dtype=torch.float64))
-    R = bf16_round(torch.randn(Gr, N, D, D, generator=g, dtype=torch.float64) / D ** 0.5)
+    Wx = rnd(torch.randn(B, T, Gw, N, D, generator=g, dtype=torch.float64))
+    R = rnd(torch.randn(Gr, N, D, D, generator=g, dtype=torch.float64) / D ** 0.5)
     b = bias_scale * torch.randn(Gt, N, D, generator=g, dtype=torch.float64)
     if function == "slstm":
         b[1] = 3.0 + 3.0 * torch.rand(N, D, generator=g, dtype=torch.float64)
-    b = bf16_round(b)
+    b = rnd(b)
     s0 = torch.zeros(S, B, 1, N, D, dtype=torch.float64)
     if random_init:
         s0 = 0.1 * torch.randn(S, B, 1, N, D, generator=g, dtype=torch.float64)
         if function == "slstm":
             s0[2] = s0[2].abs() + 1.0
-        s0 = s0.to(torch.float32).to(torch.float64) if state_f32 else bf16_round(s0)
+        s0 = s0.to(torch.float32).to(torch.float64) if state_f32 else rnd(s0)
     return Wx, R, b, s0
 
 
@@ -51,18 +52,19 @@ def max_abs(a, ref) -> float:
     return float(np.max(np.abs(np.asarray(a, dtype=np.float64) - np.asarray(ref, dtype=np.float64)))) if np.size(ref) else 0.0
 
 
-def run_native(function, Wx, R, b, s0, cot=None, state_f32=False, device="cuda", **cfg_kw):
+def run_native(function, Wx, R, b, s0, cot=None, state_f32=False, device="cuda", dtype=torch.bfloat16, **cfg_kw):
     """Runs the CUDA path through the public API; returns numpy float64 dict like oracle_fwbw."""
     from flashrnn_b200 import FlashRNNConfig, flashrnn
 
-    sdt = torch.float32 if state_f32 else torch.bfloat16
-    Wx_d = Wx.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
-    R_d = R.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
-    b_d = b.to(device=device, dtype=torch.bfloat16).requires_grad_(True)
+    name = {torch.bfloat16: "bfloat16", torch.float16: "float16"}[dtype]
+    sdt = torch.float32 if state_f32 else dtype
+    Wx_d = Wx.to(device=device, dtype=dtype).requires_grad_(True)
+    R_d = R.to(device=device, dtype=dtype).requires_grad_(True)
+    b_d = b.to(device=device, dtype=dtype).requires_grad_(True)
     s_d = s0.to(device=device, dtype=sdt).requires_grad_(True)
     B, T, _, N, D = Wx.shape
-    cfg = FlashRNNConfig(function=function, head_dim=D, num_heads=N, batch_size=B, dtype="bfloat16",
-                         dtype_s="float32" if state_f32 else "bfloat16", **cfg_kw)
+    cfg = FlashRNNConfig(function=function, head_dim=D, num_heads=N, batch_size=B, dtype=name,
+                         dtype_s="float32" if state_f32 else name, **cfg_kw)
     states, last = flashrnn(Wx_d, R_d, b_d, s_d, function=function, config=cfg)
     if cot is None:
         loss = states[0].float().sum()
