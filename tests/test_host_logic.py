@@ -132,6 +132,25 @@ def test_stepper_has_no_cpu_path_and_checks_shapes():
     assert plan.keep_packed_r == 0  # frnn_forward repacks R unless the caller says the workspace still holds it
 
 
+def test_float16_problems_reach_the_float16_build():
+    """Same tile table for both 16-bit element types; states must be of the same type or float32."""
+    for fn, B, T, N, D in [("lstm", 16, 1024, 4, 256), ("elman", 1024, 2048, 16, 64), ("gru", 32, 64, 8, 128)]:
+        a = _native.query(_native.make_problem(fn, B, T, N, D, False, True))
+        h = _native.query(_native.make_problem(fn, B, T, N, D, False, True, f16=True))
+        assert h.prob.dtype_io == _native.DTYPE_F16 and h.prob.dtype_state == _native.DTYPE_F16
+        assert (a.cluster_size, a.batch_tile, a.threads, a.workspace_bytes, a.cache_bytes) == \
+               (h.cluster_size, h.batch_tile, h.threads, h.workspace_bytes, h.cache_bytes)
+    mixed = _native.make_problem("lstm", 8, 4, 1, 64, False, True, f16=True)
+    mixed.dtype_state = _native.DTYPE_BF16
+    with pytest.raises(_native.FrnnError) as e:
+        _native.query(mixed)
+    assert e.value.code == -4
+    mixed.dtype_io, mixed.dtype_state = _native.DTYPE_BF16, _native.DTYPE_F16
+    with pytest.raises(_native.FrnnError) as e:
+        _native.query(mixed)
+    assert e.value.code == -4
+
+
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "_lib", None)
     monkeypatch.setattr(_native, "LIB_PATH", tmp_path / "nope.so")
