@@ -51,20 +51,20 @@ def measured_peaks():
     return 6650.0, 1400.0, "fallback"
 
 
-def make_inputs(function, B, T, N, D, f32_states, device, seed=0):
-    """Seeded synthetic inputs with the shapes and distributions of the named configuration."""
+def make_inputs(function, B, T, N, D, f32_states, device, seed=0, edt=torch.bfloat16):
+    """Seeded synthetic inputs with the shapes and distributions of the named configuration (``edt``: the 16-bit type)."""
     Gr, Gw, Gt, S = DIMS[function]
     g = torch.Generator(device="cpu").manual_seed(seed)
-    Wx = torch.randn(B, T, Gw, N, D, generator=g).to(torch.bfloat16)
-    R = (torch.randn(Gr, N, D, D, generator=g) / D ** 0.5).to(torch.bfloat16)
+    Wx = torch.randn(B, T, Gw, N, D, generator=g).to(edt)
+    R = (torch.randn(Gr, N, D, D, generator=g) / D ** 0.5).to(edt)
     b = 0.1 * torch.randn(Gt, N, D, generator=g)
     if function == "gru":
         b.zero_()
     if function == "slstm":
         b.zero_()
         b[1] = 3.0 + 3.0 * torch.rand(N, D, generator=g)
-    b = b.to(torch.bfloat16)
-    sdt = torch.float32 if f32_states else torch.bfloat16
+    b = b.to(edt)
+    sdt = torch.float32 if f32_states else edt
     s0 = (0.1 * torch.randn(S, B, 1, N, D, generator=g) if function == "lstm" else torch.zeros(S, B, 1, N, D)).to(sdt)
     return [t.to(device) if device != "cpu" else t for t in (Wx, R, b, s0)]
 
@@ -200,13 +200,15 @@ def run_ours(args):
         if N % world:
             raise SystemExit(f"--shard heads needs the {N} heads of {args.workload} to divide by {world} ranks")
         N = N // world
-    Wx, R, b, s0 = make_inputs(function, B, T, N, D, f32, dev, seed=rank)
-    sdt = torch.float32 if f32 else torch.bfloat16
+    f16 = args.dtype == "float16"
+    edt = torch.float16 if f16 else torch.bfloat16
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, f32, dev, seed=rank, edt=edt)
+    sdt = torch.float32 if f32 else edt
     esz, ssz = 2, (4 if f32 else 2)
     E = B * T * N * D
 
     # ---- C-ABI step on resident buffers
-    prob = nv.make_problem(function, B, T, N, D, f32, True)
+    prob = nv.make_problem(function, B, T, N, D, f32, True, f16=f16)
     plan = nv.query(prob, args.cluster_size, args.batch_tile)
     states = torch.empty(S, B, T, N, D, device=dev, dtype=sdt)
     cache = torch.empty(max(16, int(plan.cache_bytes)), device=dev, dtype=torch.uint8)
@@ -269,7 +271,7 @@ def run_ours(args):
 
     # ---- end to end through the public API with host inputs
     hostW = [t.cpu().pin_memory() for t in (Wx, R, b, s0)]
-    host_out = torch.empty(gcnt, dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(gcnt, dtype=edt).pin_memory()
     loss_host = torch.empty(1, dtype=torch.float32).pin_memory()
 
     # Inputs are double-buffered on the device: the H2D copy of step i+1 (own stream) overlaps the kernels of step i,
@@ -291,7 +293,7 @@ def run_ours(args):
         stream.wait_event(ready[slot])
         w, r, bb, s = (t.detach() for t in bufs[slot])
         w.requires_grad_(True); r.requires_grad_(True); bb.requires_grad_(True)
-        out, _ = flashrnn(w, r, bb, s, function=function,
+        out, _ = flashrnn(w, r, bb, s, function=function, dtype=args.dtype,
                           grad_allreduce_group=(True if dist is not None and not by_heads else None))
         loss = out[0].float().sum()
         loss.backward()
@@ -341,9 +343,9 @@ def run_ours(args):
         "metric": METRIC, "value": tok_ranks * B * T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if by_heads else "weak",
         "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
+        "dtype": "f16" if f16 else "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {function} fwd+bwd B={B} T={T} N={N} D={D} per GPU, loss=sum(h), "
-                               f"states {'f32' if f32 else 'bf16'}", "global_batch": tok_ranks * B,
+                               f"states {'f32' if f32 else ('f16' if f16 else 'bf16')}", "global_batch": tok_ranks * B,
                    "parallelism": (f"head-sharded x{world} ({N} of {N * world} heads per GPU), no collective" if by_heads else
                                    f"batch-sharded x{world}, NCCL all-reduce of fp32 dR||db") if world > 1 else "single GPU",
                    "tile": {"cluster_size": plan.cluster_size, "units_per_cta": plan.units_per_cta, "batch_tile": plan.batch_tile,
@@ -385,6 +387,8 @@ def main():
     ap.add_argument("--shard", default="batch", choices=["batch", "heads"],
                     help="N > 1 GPUs: batch shards (weak scaling, default) or head shards of one workload (strong scaling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16"],
+                    help="16-bit element type of Wx/R/b/gradients (the baseline metric is quoted in bfloat16)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
