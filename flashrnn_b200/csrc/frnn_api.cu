@@ -294,7 +294,9 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   const WsLayout w = workspace_layout(pr, cd);
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
 
-  cudaError_t e = cudaMemsetAsync(ws, 0, kStatusBytes, stream);
+  // keep_packed_r: the workspace is left as the previous call left it (R fragments kept, status block not cleared, so
+  // an expired wait of an earlier step stays on record until the caller reads it)
+  cudaError_t e = plan->keep_packed_r ? cudaSuccess : cudaMemsetAsync(ws, 0, kStatusBytes, stream);
   if (e != cudaSuccess) return (int)e;
   if (is_wide(*plan))
     return (int)launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,

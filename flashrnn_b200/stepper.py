@@ -1,8 +1,8 @@
 """Step-by-step (decoding) use of the forward loop.
 
 ``FlashRNNStepper`` keeps R, b, the carried states and every scratch buffer on the device and advances the recurrence
-by one chunk of time steps (default: one) per call: no allocation and no repacking of R per call, two launches (status
-reset + time loop), all on the caller's current stream, so a step can be captured in a CUDA graph.  It is the
+by one chunk of time steps (default: one) per call: no allocation and no repacking of R per call, two launches (time
+loop + carry copy), all on the caller's current stream, so a step can be captured in a CUDA graph.  It is the
 counterpart of the reference's per-step kernel selection (``_get_kernel_step``, flashrnn/flashrnn/flashrnn.py:957-983;
 ``flashrnn_forward_step``, flashrnn/flashrnn/vanilla/__init__.py:73-121): same cells, same state layout, forward only.
 """

@@ -80,9 +80,10 @@ typedef struct frnn_plan {
                                  status block.  With the 128-row loops (batch_tile 128): one tile copy (step index 2)
                                  is announced to its barrier and never issued.  Exercises the failure-detection path
                                  without faulting the GPU.                                                          */
-  int32_t keep_packed_r;      /* 0: frnn_forward repacks R into the workspace (default).  1: the workspace still holds R
-                                 as repacked by an earlier frnn_forward with this plan and R has not changed since:
-                                 skip that launch (step-by-step decoding calls frnn_forward once per token)        */
+  int32_t keep_packed_r;      /* 0: frnn_forward clears the status block and repacks R into the workspace (default).
+                                 1: the workspace is as an earlier frnn_forward with this plan left it and R has not
+                                 changed since: skip both launches (step-by-step decoding calls frnn_forward once per
+                                 token); a device status recorded by an earlier step stays until the caller reads it */
   int32_t reserved[4];
   uint64_t cache_bytes;     /* size of the activation cache (opaque layout, tied to this plan) */
   uint64_t workspace_bytes; /* size of the scratch workspace                                  */
