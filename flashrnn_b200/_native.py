@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 # FRNN_B200_LIB points the binding at another build of the same library (development variants)
 LIB_PATH = Path(os.environ.get("FRNN_B200_LIB") or PKG / "libfrnn_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 NOALLOC_MAX_SCRATCH_BYTES = 8 << 20  # FRNN_NOALLOC_MAX_SCRATCH_BYTES
 CELL_IDS = {"lstm": 0, "gru": 1, "elman": 2, "slstm": 3}
 DTYPE_BF16, DTYPE_F32, DTYPE_F16 = 0, 1, 2
@@ -48,7 +48,7 @@ class FrnnPlan(ctypes.Structure):
 
 
 class FrnnFwdArgs(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_void_p) for n in ("Wx", "R", "b", "s0", "states", "cache", "workspace")]
+    _fields_ = [(n, ctypes.c_void_p) for n in ("Wx", "R", "b", "s0", "states", "cache", "workspace", "last")]
 
 
 class FrnnBwdArgs(ctypes.Structure):

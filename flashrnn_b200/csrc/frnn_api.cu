@@ -298,9 +298,20 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   // an expired wait of an earlier step stays on record until the caller reads it)
   cudaError_t e = plan->keep_packed_r ? cudaSuccess : cudaMemsetAsync(ws, 0, kStatusBytes, stream);
   if (e != cudaSuccess) return (int)e;
-  if (is_wide(*plan))
-    return (int)launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,
-                                    plan->test_drop_exchange, stream);
+  if (a->last && !aligned16(a->last)) return FRNN_ERR_ALIGN;
+  // `last`: one strided device copy of states[:, :, T-1] behind the time loop.  (Storing it from inside the forward
+  // kernel, after the loop, cost the C2 forward loop 6 %: the longer live ranges changed its register allocation.)
+  auto copy_last = [&]() -> cudaError_t {
+    if (!a->last) return cudaSuccess;
+    const size_t row = (size_t)pr.N * pr.D * (pr.dtype_state == FRNN_DTYPE_F32 ? 4 : 2);
+    return cudaMemcpy2DAsync(a->last, row, static_cast<const unsigned char*>(a->states) + (size_t)(pr.T - 1) * row,
+                             (size_t)pr.T * row, row, (size_t)cd.S * pr.B, cudaMemcpyDeviceToDevice, stream);
+  };
+  if (is_wide(*plan)) {
+    e = launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,
+                            plan->test_drop_exchange, stream);
+    return (int)(e == cudaSuccess ? copy_last() : e);
+  }
   if (!plan->keep_packed_r) e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
   if (e != cudaSuccess) return (int)e;
 
@@ -319,7 +330,7 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   lp.test_drop = plan->test_drop_exchange;
   const LoopKernel k = get_fwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8);
   e = launch_loop(k, *plan, lp, stream);
-  return (int)e;
+  return (int)(e == cudaSuccess ? copy_last() : e);
 }
 
 #ifndef FRNN_F16

@@ -1,8 +1,8 @@
 """Step-by-step (decoding) use of the forward loop.
 
 ``FlashRNNStepper`` keeps R, b, the carried states and every scratch buffer on the device and advances the recurrence
-by one chunk of time steps (default: one) per call: no allocation and no repacking of R per call, two launches (time
-loop + carry copy), all on the caller's current stream, so a step can be captured in a CUDA graph.  It is the
+by one chunk of time steps (default: one) per call: no allocation and no repacking of R per call -- the time loop and
+one strided copy that carries the last states in place, on the caller's current stream, so a step can be captured in a CUDA graph.  It is the
 counterpart of the reference's per-step kernel selection (``_get_kernel_step``, flashrnn/flashrnn/flashrnn.py:957-983;
 ``flashrnn_forward_step``, flashrnn/flashrnn/vanilla/__init__.py:73-121): same cells, same state layout, forward only.
 """
@@ -71,10 +71,11 @@ class FlashRNNStepper:
             raise ValueError(f"expected contiguous {self._kdt} Wx{(self.B, self.chunk, self.Gw, self.N, self.D)}")
         dev = Wx.device
         self._plan.keep_packed_r = 1 if self._packed else 0
-        args = _native.FrnnFwdArgs(_ptr(Wx), _ptr(self._R), _ptr(self._b), _ptr(self._s0), _ptr(self._out), None, _ptr(self._ws))
+        # `last` = the s0 buffer itself: the carried states are updated in place by the library call
+        args = _native.FrnnFwdArgs(_ptr(Wx), _ptr(self._R), _ptr(self._b), _ptr(self._s0), _ptr(self._out), None, _ptr(self._ws),
+                                   _ptr(self._s0))
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         with torch.cuda.device(dev):
             _native.check("frnn_forward", _native.lib().frnn_forward(ctypes.byref(self._plan), ctypes.byref(args), stream))
         self._packed = True
-        self._s0.copy_(self._out[:, :, -1:])  # carry (same stream; S*B*N*D elements)
         return self._out

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define FRNN_ABI_VERSION 1
+#define FRNN_ABI_VERSION 2
 
 /* cells: gate/state counts follow the reference registry flashrnn/flashrnn/flashrnn.py:49-71 */
 enum { FRNN_CELL_LSTM = 0, FRNN_CELL_GRU = 1, FRNN_CELL_ELMAN = 2, FRNN_CELL_SLSTM = 3 };
@@ -102,6 +102,9 @@ typedef struct frnn_fwd_args {
   void* states;        /* [S,B,T,N,D]  dtype_state (output)          */
   void* cache;         /* cache_bytes, output; may be NULL when training == 0 */
   void* workspace;     /* workspace_bytes                            */
+  void* last;          /* optional (NULL: off) [S,B,1,N,D] dtype_state (output): the states after step T-1 (one strided
+                          device copy behind the time loop).  May be the very buffer `s0` points to: chunked or
+                          token-by-token calls then carry their states in place                              */
 } frnn_fwd_args;
 
 /* Backward arguments.  Replaces FlashRNNFuncFused::backward(R_t, b, s, g_r, g_i, ds_new) ->

@@ -67,6 +67,32 @@ def test_stepper_replays_from_a_cuda_graph(cuda_device):
         assert torch.equal(out, full[:, :, t:t + 1]), t
 
 
+@pytest.mark.parametrize("function,B,N,D,tile", [("lstm", 12, 2, 128, 0), ("slstm", 8, 1, 64, 0), ("gru", 40, 3, 64, 0),
+                                                 ("elman", 136, 2, 64, 128)])
+def test_last_states_output_of_the_c_abi(cuda_device, function, B, N, D, tile):
+    """frnn_fwd_args.last receives states[:, :, T-1], into a separate buffer and in place over s0 (cluster kernels and
+    the 128-row loops, which serve it with a strided copy)."""
+    import ctypes
+    from flashrnn_b200 import _native as nv
+    T = 5
+    Wx, R, b, s0 = _inputs(function, B, T, N, D, cuda_device, seed=9)
+    S = s0.shape[0]
+    plan = nv.query(nv.make_problem(function, B, T, N, D, False, False), 0, tile)
+    assert plan.batch_tile == (tile or plan.batch_tile)
+    states = torch.empty(S, B, T, N, D, dtype=torch.bfloat16, device=cuda_device)
+    ws = torch.empty(int(plan.workspace_bytes), dtype=torch.uint8, device=cuda_device)
+    last = torch.full((S, B, 1, N, D), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    L = nv.lib()
+    nv.check("fwd", L.frnn_forward(ctypes.byref(plan), ctypes.byref(nv.FrnnFwdArgs(P(Wx), P(R), P(b), P(s0), P(states), None, P(ws), P(last))), stream))
+    assert torch.equal(last, states[:, :, -1:])
+    ref = states.clone()
+    carried = s0.clone()
+    nv.check("fwd", L.frnn_forward(ctypes.byref(plan), ctypes.byref(nv.FrnnFwdArgs(P(Wx), P(R), P(b), P(carried), P(states), None, P(ws), P(carried))), stream))
+    assert torch.equal(states, ref) and torch.equal(carried, ref[:, :, -1:])
+
+
 def test_stepper_refuses_wrong_shapes(cuda_device):
     _, R, b, _ = _inputs("gru", 4, 1, 2, 64, cuda_device, seed=1)
     st = FlashRNNStepper(R, b, function="gru", batch_size=4)

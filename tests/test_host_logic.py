@@ -27,7 +27,7 @@ def test_struct_sizes_match_header():
     # int32 x 8 + float x 2; plan = 4 + 40 + 6*4 + 6*4 (reserved) padded to 8 + 4 * 8
     assert ctypes.sizeof(_native.FrnnProblem) == 44
     assert ctypes.sizeof(_native.FrnnPlan) == 128
-    assert ctypes.sizeof(_native.FrnnFwdArgs) == 7 * 8 and ctypes.sizeof(_native.FrnnBwdArgs) == 8 * 8
+    assert ctypes.sizeof(_native.FrnnFwdArgs) == 8 * 8 and ctypes.sizeof(_native.FrnnBwdArgs) == 8 * 8
 
 
 @pytest.mark.parametrize("function,B,T,N,D,f32", [
