@@ -5,10 +5,12 @@
 // Same GEMM as frnn_dr_tc.cu (C[(g,d), p] = A^T B per head, both operands MN-major exactly as the time loops left them
 // in HBM), for bf16 states and head dims that are multiples of 64: a 64-step stretch of one batch row is, for every 64
 // consecutive d (or p), one [64 t][64] tile with 128-byte rows -- the box of a tensor-map copy with 128-byte swizzle
-// and, unchanged, one block of a UMMA operand.  One CTA owns 128 rows of (g,d) (two such blocks), all D columns of p and
-// a range of 64-step chunks (split-K over gridDim.z):
-//   * warp 4, one lane: per chunk 2 + D/64 bulk loads into a 4-stage ring (mbarrier byte counts), then 4 tcgen05.mma
-//     (M128, N = D, K16) accumulating in tensor memory; tcgen05.commit frees the stage;
+// and, unchanged, one block of a UMMA operand.  One CTA owns MT tiles of 128 rows of (g,d) (two such blocks each), all D
+// columns of p and a range of 64-step chunks (split-K over gridDim.z); the MT accumulators share every h block that is
+// fetched, so h crosses L2 -> shared memory once per MT * 128 rows (MT = 2 for D = 256, 3 for D = 128: the tensor
+// memory holds MT * D <= 512 fp32 columns):
+//   * warp 4, one lane: per chunk 2 MT + D/64 bulk loads into a 3- or 4-stage ring (mbarrier byte counts), then 4 MT
+//     tcgen05.mma (M128, N = D, K16) accumulating in tensor memory; tcgen05.commit frees the stage;
 //   * h_{t-1} of t = 0 is the initial state, which is not a row of `states`: the copy starts at t = -1, that row reads
 //     as zero, and the missing products delta[b,0] * h_{-1}[b] are added by the draining threads from global memory;
 //   * warps 0-3 read their tensor-memory lanes and add the tile into the fp32 gradient workspace with atomics.
@@ -38,7 +40,9 @@ struct DrTmaParams {
   int cell, B, T, N, D, Gr, Gw;
   int chunks_per_b;          // ceil(T / 64)
   int chunks_per_split;
-  int tmem_cols;             // power of two >= D, >= 32
+  int tmem_cols;             // power of two >= mt * D, >= 32
+  int mt;                    // 128-row tiles of (g,d) per CTA
+  int stages;                // ring depth (<= DT_STAGES)
 };
 
 __global__ void __launch_bounds__(DT_THREADS, 1)
@@ -49,8 +53,9 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = smem_raw + (base - raw);
   const int D = p.D, N = p.N, T = p.T, nb = D >> 6;  // nb = 64-wide blocks per gate (rows) / of p (columns)
-  const uint32_t stage_bytes = (uint32_t)(2 + nb) * DT_BLK;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sm + (size_t)DT_STAGES * stage_bytes);  // [DT_STAGES] bytes have landed
+  const int MT = p.mt, NS = p.stages;
+  const uint32_t stage_bytes = (uint32_t)(2 * MT + nb) * DT_BLK;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sm + (size_t)NS * stage_bytes);          // [DT_STAGES] bytes have landed
   uint64_t* empty = full + DT_STAGES;                                                  // [DT_STAGES] MMAs have read the stage
   uint64_t* done = empty + DT_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done + 1);
@@ -58,7 +63,8 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.y;
   const int RB = p.Gr * nb;                            // 64-row blocks of (g,d)
-  const int rb0 = 2 * blockIdx.x, rb1 = (rb0 + 1 < RB) ? rb0 + 1 : rb0;  // an odd last block is computed twice, stored once
+  const int rbase = 2 * MT * blockIdx.x;               // blocks rbase .. rbase + 2 MT - 1; those beyond RB repeat the last one
+                                                       // (computed again, not stored)
   const long long total_chunks = (long long)p.B * p.chunks_per_b;
   const long long c_begin = (long long)blockIdx.z * p.chunks_per_split;
   long long c_end = c_begin + p.chunks_per_split;
@@ -86,65 +92,75 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
       const void* tmg = &tm_dg0;
       const void* tmh = &tm_states;
       int loads = 0, seen = 0;  // chunks requested / seen to land
-      auto load = [&](int ci) {
-        const long long c = c_begin + ci;
-        const int b = (int)(c / p.chunks_per_b), t0 = (int)(c - (long long)b * p.chunks_per_b) * DT_KC;
-        const int s = ci % DT_STAGES;
+      int ls = 0;               // ring stage of the next request (requests go out in chunk order)
+      int lb = (int)(c_begin / p.chunks_per_b), lc = (int)(c_begin - (long long)lb * p.chunks_per_b);  // its batch row, chunk
+      auto load = [&](int) {
+        const int b = lb, t0 = lc * DT_KC;
+        if (++lc == p.chunks_per_b) { lc = 0; ++lb; }
+        const int s = ls;
+        ls = (ls + 1 == NS) ? 0 : ls + 1;
         const uint32_t dst = base + (uint32_t)s * stage_bytes;
         mbar_arrive_expect_tx(&full[s], stage_bytes);
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int rb = i ? rb1 : rb0, g = rb / nb, d0 = (rb - g * nb) * 64;
+        for (int i = 0; i < 2 * MT; ++i) {
+          const int rb = (rbase + i < RB) ? rbase + i : RB - 1, g = rb / nb, d0 = (rb - g * nb) * 64;
           if (p.cell == CELL_GRU && g == 0) tma_load_5d(dst + i * DT_BLK, tmg, d0, n, t0, b, 0, &full[s]);
           else tma_load_5d(dst + i * DT_BLK, tmw, d0, n, (p.cell == CELL_GRU) ? g - 1 : g, t0, b, &full[s]);
         }
-        for (int pb = 0; pb < nb; ++pb) tma_load_5d(dst + (2 + pb) * DT_BLK, tmh, pb * 64, n, t0 - 1, b, 0, &full[s]);
+        for (int pb = 0; pb < nb; ++pb) tma_load_5d(dst + (2 * MT + pb) * DT_BLK, tmh, pb * 64, n, t0 - 1, b, 0, &full[s]);
         ++loads;
       };
-      for (int ci = 0; ci < nchunks && ci < DT_STAGES; ++ci) load(ci);
+      for (int ci = 0; ci < nchunks && ci < NS; ++ci) load(ci);
       bool ok = true;
+      int s = 0, ps = 0;         // ring stage of chunk ci and of chunk ci - 1
+      uint32_t par = 0, ppar = 0;  // and the parities of their barrier phases
       for (int ci = 0; ci < nchunks; ++ci) {
-        const int s = ci % DT_STAGES;
-        if (!mbar_wait_bounded(&full[s], (uint32_t)((ci / DT_STAGES) & 1))) { ok = false; report_timeout(p.status, ci); break; }
+        if (!mbar_wait_bounded(&full[s], par)) { ok = false; report_timeout(p.status, ci); break; }
         seen = ci + 1;
-        const uint32_t a_lo = ((base + (uint32_t)s * stage_bytes) >> 4) | LBO, b_lo = a_lo + ((2 * DT_BLK) >> 4);
+        const uint32_t s_lo = ((base + (uint32_t)s * stage_bytes) >> 4) | LBO, b_lo = s_lo + (uint32_t)MT * ((2 * DT_BLK) >> 4);
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint32_t a_lo = s_lo + (uint32_t)mt * ((2 * DT_BLK) >> 4), acc = tmem + (uint32_t)(mt * D);
 #pragma unroll
-        for (uint32_t ks = 0; ks < DT_KC / 16; ++ks)  // 16 rows of a block = 2048 bytes per k-step
-          umma_parts(tmem, a_lo + 128 * ks, HI, b_lo + 128 * ks, HI, idesc, (ci > 0 || ks > 0) ? 1u : 0u);
+          for (uint32_t ks = 0; ks < DT_KC / 16; ++ks)  // 16 rows of a block = 2048 bytes per k-step
+            umma_parts(acc, a_lo + 128 * ks, HI, b_lo + 128 * ks, HI, idesc, (ci > 0 || ks > 0) ? 1u : 0u);
+        }
         umma_commit(&empty[s]);
-        if (ci >= 1 && ci - 1 + DT_STAGES < nchunks) {  // refill the stage of the chunk before: its MMAs are done sooner
-          if (!mbar_wait_bounded(&empty[(ci - 1) % DT_STAGES], (uint32_t)(((ci - 1) / DT_STAGES) & 1))) {
+        if (ci >= 1 && ci - 1 + NS < nchunks) {  // refill the stage of the chunk before: its MMAs are done sooner
+          if (!mbar_wait_bounded(&empty[ps], ppar)) {
             ok = false;
             report_timeout(p.status, ci);
             break;
           }
-          load(ci - 1 + DT_STAGES);
+          load(ci - 1 + NS);
         }
+        ps = s; ppar = par;
+        if (++s == NS) { s = 0; par ^= 1u; }
       }
       umma_commit(done);
       if (!ok)  // never leave with copies in flight
-        for (int i = (seen > loads - DT_STAGES ? seen : loads - DT_STAGES); i < loads; ++i)
-          mbar_wait_bounded(&full[i % DT_STAGES], (uint32_t)((i / DT_STAGES) & 1));
+        for (int i = (seen > loads - NS ? seen : loads - NS); i < loads; ++i)
+          mbar_wait_bounded(&full[i % NS], (uint32_t)((i / NS) & 1));
     }
   } else {
-    // ---- drain: row m of the tile = (block i = m / 64, d = 64 * dblk + m % 64)
+    // ---- drain: row m of tile mt = (block 2 mt + m / 64, d = 64 * dblk + m % 64)
     const bool fin = mbar_wait_bounded(done, 0);
     if (!fin) report_timeout(p.status, nchunks);
     tc_fence_after();
-    const int m = warp * 32 + lane, i = m >> 6;
-    const int rb = i ? rb1 : rb0, g = rb / nb, d = (rb - g * nb) * 64 + (m & 63);
-    const bool row_ok = fin && !(i == 1 && rb0 + 1 >= RB);
-    float* out = p.dR + (((size_t)g * N + n) * D + d) * D;
-    // delta[b, t = 0] of this row, for the batch rows whose first chunk belongs to this CTA
+    const int m = warp * 32 + lane;
+    // delta[b, t = 0] of a row is needed for the batch rows whose first chunk belongs to this CTA
     const int b_first = (int)((c_begin + p.chunks_per_b - 1) / p.chunks_per_b), b_last = (int)((c_end - 1) / p.chunks_per_b);
     const size_t ND = (size_t)N * D;
+    for (int mt = 0; mt < MT; ++mt) {
+    const int rb = rbase + 2 * mt + (m >> 6);
+    const bool row_ok = fin && rb < RB;
+    const int rbc = row_ok ? rb : RB - 1, g = rbc / nb, d = (rbc - g * nb) * 64 + (m & 63);
+    float* out = p.dR + (((size_t)g * N + n) * D + d) * D;
     const bool from_dg0 = p.cell == CELL_GRU && g == 0;
     const elem_t* d0src = from_dg0 ? p.dg0 + (size_t)n * D + d
                                           : p.dWx + (size_t)((p.cell == CELL_GRU) ? g - 1 : g) * ND + (size_t)n * D + d;
     const size_t d0stride = (from_dg0 ? (size_t)1 : (size_t)p.Gw) * ND * T;  // elements between batch rows at t = 0
     for (int col0 = 0; col0 < D; col0 += 32) {
       uint32_t r[32];
-      tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, r);
+      tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(mt * D + col0), r);
       if (!row_ok) continue;
       float v[32];
 #pragma unroll
@@ -166,6 +182,7 @@ recurrent_grad_tma_kernel(const __grid_constant__ CUtensorMap tm_dwx, const __gr
       }
 #pragma unroll
       for (int j = 0; j < 32; j += 4) red_add_f32x4(out + col0 + j, v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
     }
   }
   tc_fence_before();
@@ -207,10 +224,24 @@ cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int 
   p.status = status;
   p.cell = cell; p.B = B; p.T = T; p.N = N; p.D = D; p.Gr = Gr; p.Gw = Gw;
   p.chunks_per_b = (T + DT_KC - 1) / DT_KC;
+  // tiles of 128 rows per CTA: as many as share one fetch of h, within 512 tensor-memory columns and a ring of at least
+  // three stages in shared memory
+  const int nb = D / 64, tiles = (Gr * nb + 1) / 2;
+  int mt = 512 / D;
+  if (mt > 3) mt = 3;
+  if (mt > tiles) mt = tiles;
+  while (mt > 1 && 3 * (size_t)(2 * mt + nb) * DT_BLK > (size_t)200 * 1024) --mt;
+  mt = (tiles + (tiles + mt - 1) / mt - 1) / ((tiles + mt - 1) / mt);  // same number of CTAs, evenly filled
+#ifdef FRNN_DR_ONE_TILE  // development aid: one tile per CTA
+  mt = 1;
+#endif
+  p.mt = mt;
+  int stages = (int)(((size_t)200 * 1024) / ((size_t)(2 * mt + nb) * DT_BLK));
+  p.stages = stages > DT_STAGES ? DT_STAGES : stages;
   int cols = 32;
-  while (cols < D) cols *= 2;
+  while (cols < mt * D) cols *= 2;
   p.tmem_cols = cols;
-  const int nb = D / 64, mtiles = (Gr * nb + 1) / 2;
+  const int mtiles = (tiles + mt - 1) / mt;
   const long long chunks = (long long)B * p.chunks_per_b;
   const long long base_ctas = (long long)mtiles * N;
   long long splits = sm_count / base_ctas;  // one CTA per SM (shared memory): stay within a single wave
@@ -219,7 +250,7 @@ cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int 
   if (splits > 65535) splits = 65535;
   p.chunks_per_split = (int)((chunks + splits - 1) / splits);
   splits = (chunks + p.chunks_per_split - 1) / p.chunks_per_split;
-  const size_t smem = (size_t)DT_STAGES * (2 + nb) * DT_BLK + 8 * (2 * DT_STAGES + 1) + 16 + 1024;
+  const size_t smem = (size_t)p.stages * (2 * mt + nb) * DT_BLK + 8 * (2 * DT_STAGES + 1) + 16 + 1024;
   cudaError_t e = cudaFuncSetAttribute(recurrent_grad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   recurrent_grad_tma_kernel<<<dim3((unsigned)mtiles, (unsigned)N, (unsigned)splits), DT_THREADS, smem, stream>>>(tm_dwx, tm_dg0,
