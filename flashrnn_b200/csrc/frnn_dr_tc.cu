@@ -42,21 +42,23 @@ struct DrTcParams {
   int cell, T, N, D, Gr, Gw, state_f32;
   long long K;               // B*T
   int chunks_per_split;
-  int tmem_cols;             // power of two >= D, >= 32
+  int tmem_cols;             // power of two >= J * D, >= 32
 };
 
-size_t tc_smem_bytes(int D) {
-  return (size_t)TC_STAGES * ((size_t)(TC_M / 8) * TC_SBO + (size_t)(D / 8) * TC_SBO) + 64;
+size_t tc_smem_bytes(int D, int J) {
+  return (size_t)TC_STAGES * ((size_t)(J * TC_M / 8) * TC_SBO + (size_t)(D / 8) * TC_SBO) + 64;
 }
 
-template <bool F32>
+// J: tiles of 128 rows of (g,d) per CTA.  Their accumulators (J * D <= 512 tensor-memory columns) share every h row that
+// is staged, so h is read from L2 once per J * 128 rows.
+template <bool F32, int J>
 __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const DrTcParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int D = p.D, N = p.N, T = p.T, Gr = p.Gr;
   const int mtile = blockIdx.x, n = blockIdx.y;
   const size_t ND = (size_t)N * D;
-  const uint32_t a_bytes = (uint32_t)(TC_M / 8) * TC_SBO, b_bytes = (uint32_t)(D / 8) * TC_SBO;
+  const uint32_t a_bytes = (uint32_t)(J * TC_M / 8) * TC_SBO, b_bytes = (uint32_t)(D / 8) * TC_SBO;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)TC_STAGES * stage_bytes);  // [TC_STAGES]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + TC_STAGES);
@@ -80,14 +82,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
   // rows of this tile: m = mtile*128 + r  ->  (g, d) = (m / D, m % D); rows beyond Gr*D are zero padding
   const int rows_total = Gr * D;
   // Loader mapping (no divisions in the loop): thread -> k-row kr = tid / 4 of the chunk and a 64-byte quad of
-  // 32 consecutive rows (A) / columns (B): quad `sub` of A, quads `sub`, `sub + 4`, ... of B.
+  // 32 consecutive rows (A) / columns (B): quads `sub`, `sub + 4`, .. of A (one per tile) and of B.
   const int kr = tid >> 2, sub = tid & 3;
   const uint32_t kr_off = (uint32_t)(kr >> 3) * TC_LBO + (uint32_t)(kr & 7) * 16;
-  const elem_t* a_src[1];   // delta row of quad `sub` at k = 0
-  size_t a_stride[1];
+  const elem_t* a_src[J];   // delta row of quad `sub + 4 j` at k = 0
+  size_t a_stride[J];
 #pragma unroll
-  for (int j = 0; j < 1; ++j) {
-    const int m = mtile * TC_M + sub * 32;
+  for (int j = 0; j < J; ++j) {
+    const int m = (mtile * J + j) * TC_M + sub * 32;
     a_src[j] = nullptr; a_stride[j] = 0;
     if (m < rows_total) {
       const int g = m / D, d = m - g * D;
@@ -109,8 +111,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
     unsigned char* bbase = abase + a_bytes;
     const bool krow = kk < k_end;
 #pragma unroll
-    for (int j = 0; j < 1; ++j) {
-      unsigned char* dst = abase + (size_t)(sub * 4) * TC_SBO + kr_off;
+    for (int j = 0; j < J; ++j) {
+      unsigned char* dst = abase + (size_t)((j * 4 + sub) * 4) * TC_SBO + kr_off;
       if (krow && a_src[j] != nullptr) {
         const elem_t* src = a_src[j] + (size_t)kk * a_stride[j];
 #pragma unroll
@@ -177,9 +179,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
       const uint32_t a0 = smem_base + (uint32_t)s * stage_bytes, b0 = a0 + a_bytes;
 #pragma unroll
       for (int i = 0; i < TC_KC / 16; ++i) {
-        const uint64_t ad = smem_desc(a0 + i * 2 * TC_LBO, TC_LBO, TC_SBO);
         const uint64_t bd = smem_desc(b0 + i * 2 * TC_LBO, TC_LBO, TC_SBO);
-        umma_16(tmem_base, ad, bd, idesc, (c > 0 || i > 0) ? 1u : 0u);
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          const uint64_t ad = smem_desc(a0 + (uint32_t)j * (TC_M / 8) * TC_SBO + i * 2 * TC_LBO, TC_LBO, TC_SBO);
+          umma_16(tmem_base + (uint32_t)(j * D), ad, bd, idesc, (c > 0 || i > 0) ? 1u : 0u);
+        }
       }
       umma_commit(&bars[s]);
     }
@@ -193,18 +198,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1) recurrent_grad_tc_kernel(const 
     }
   }
   tc_fence_after();
-  const int m = mtile * TC_M + (warp & 3) * 32 + lane;
-  const bool row_ok = m < rows_total && warp < 4;
-  const int g = row_ok ? m / D : 0, d = row_ok ? m - g * D : 0;
-  float* out = p.dR + (((size_t)g * N + n) * D + d) * D;
-  for (int col0 = 0; col0 < D; col0 += 32) {
-    uint32_t r[32];
-    if (warp < 4) tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)col0, r);
-    if (row_ok && !poisoned) {
+#pragma unroll 1
+  for (int jt = 0; jt < J; ++jt) {
+    const int m = (mtile * J + jt) * TC_M + (warp & 3) * 32 + lane;
+    const bool row_ok = m < rows_total && warp < 4;
+    const int g = row_ok ? m / D : 0, d = row_ok ? m - g * D : 0;
+    float* out = p.dR + (((size_t)g * N + n) * D + d) * D;
+    for (int col0 = 0; col0 < D; col0 += 32) {
+      uint32_t r[32];
+      if (warp < 4) tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(jt * D + col0), r);
+      if (row_ok && !poisoned) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)  // D is a multiple of 32 here (128, 192, 256)
-        red_add_f32x4(out + col0 + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                      __uint_as_float(r[j + 3]));
+        for (int j = 0; j < 32; j += 4)  // D is a multiple of 32 here (128, 192, 256)
+          red_add_f32x4(out + col0 + j, __uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                        __uint_as_float(r[j + 3]));
+      }
     }
   }
   tc_fence_before();
@@ -223,10 +231,12 @@ cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int G
   p.states = states; p.s0 = s0; p.dR = dR; p.status = status;
   p.cell = cell; p.T = T; p.N = N; p.D = D; p.Gr = Gr; p.Gw = Gw; p.state_f32 = state_f32;
   p.K = (long long)B * T;
+  const int tiles = (Gr * D + TC_M - 1) / TC_M;
+  const int J = (tiles >= 2 && 2 * D <= 512) ? 2 : 1;  // two tiles per CTA where there are two to share a fetch of h
   int cols = 32;
-  while (cols < D) cols *= 2;
+  while (cols < J * D) cols *= 2;
   p.tmem_cols = cols;
-  const int mtiles = (Gr * D + TC_M - 1) / TC_M;
+  const int mtiles = (tiles + J - 1) / J;
   const long long chunks = (p.K + TC_KC - 1) / TC_KC;
   const long long base_ctas = (long long)mtiles * N;
   long long splits = sm_count / base_ctas;  // one CTA per SM (shared memory): stay within a single wave
@@ -235,17 +245,18 @@ cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int G
   if (splits > 65535) splits = 65535;
   p.chunks_per_split = (int)((chunks + splits - 1) / splits);
   splits = (chunks + p.chunks_per_split - 1) / p.chunks_per_split;
-  const size_t smem = tc_smem_bytes(D);
+  const size_t smem = tc_smem_bytes(D, J);
+  const dim3 grid((unsigned)mtiles, (unsigned)N, (unsigned)splits);
+  auto launch = [&](auto kern) -> cudaError_t {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, TC_THREADS, smem, stream>>>(p);
+    return cudaSuccess;
+  };
   cudaError_t e;
-  if (state_f32) {
-    e = cudaFuncSetAttribute(recurrent_grad_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    recurrent_grad_tc_kernel<true><<<dim3((unsigned)mtiles, (unsigned)N, (unsigned)splits), TC_THREADS, smem, stream>>>(p);
-  } else {
-    e = cudaFuncSetAttribute(recurrent_grad_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-    recurrent_grad_tc_kernel<false><<<dim3((unsigned)mtiles, (unsigned)N, (unsigned)splits), TC_THREADS, smem, stream>>>(p);
-  }
+  if (state_f32) e = J == 2 ? launch(recurrent_grad_tc_kernel<true, 2>) : launch(recurrent_grad_tc_kernel<true, 1>);
+  else e = J == 2 ? launch(recurrent_grad_tc_kernel<false, 2>) : launch(recurrent_grad_tc_kernel<false, 1>);
+  if (e != cudaSuccess) return e;
   return cudaGetLastError();
 }
 
