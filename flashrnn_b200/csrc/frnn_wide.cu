@@ -557,6 +557,9 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
               if (!mbar_wait_bounded(&h_free[r & 1], (uint32_t)((r >> 1) & 1))) { ok = false; break; }
               if (r + 2 <= P) load_h(r + 2);
             }
+            // the cotangent box consumed during the previous iteration goes back to the copy engine before anything below
+            // can wait for data
+            if (!reload_e()) { ok = false; break; }
             // dR += delta_j^T * h_{tt-1}
             const int rq = tt >= 1 ? P - 1 - ((tt - 1) >> 1) : P;
             if (!wait_h(rq)) { ok = false; break; }
@@ -572,7 +575,6 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
               for (uint32_t ks = 0; ks < 8; ++ks)
                 umma_parts(tmem + 2 * WD, dl + 256 * ks, HI2, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
             }
-            if (!reload_e()) { ok = false; break; }
             if (j + 2 < T) {
               if (!wait_e(P - 1 - ((tt - 2) >> 1))) { ok = false; break; }
               issue_pre(j + 2);
