@@ -327,13 +327,10 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   };
 
   int stage = 0;
-  FRNN_PROF_DECL;
   for (int j = 0; j < T; ++j) {  // j-th step of the reverse loop, time index t = T-1-j
     const int t = T - 1 - j, buf = j & 1;
-    FRNN_PROF_MARK(0);
     cp_async_wait<kStages - 1>();
     if constexpr (RS) { if (j > 0) wait_exchange(buf ^ 1, j - 1, t, buf); }  // partial sums produced in step j-1
-    FRNN_PROF_MARK(1);
     float dwv[IPT][Gw][2], dg0v[IPT][2];
     elem_t* ddst = RS ? dgbuf : dgbuf + (size_t)buf * CS * SL + (size_t)crank * SL;
     // ---------------- phase B: pointwise backward; R-gate deltas (bf16) into the delta tile
@@ -386,7 +383,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         *reinterpret_cast<uint32_t*>(ddst + dloc_it[i] + g * U) = pack_x2(dRv[0][g], dRv[1][g]);
     }
     if (!RS && CS > 1) fence_proxy_async_smem();
-    FRNN_PROF_MARK(2);
     __syncthreads();
     // Set when a wait expired in some thread of this CTA: in this step before the barrier above (reduce-scatter), or in
     // the previous step (all-gather, whose wait follows this barrier).  Either way the write precedes the barrier and
@@ -415,7 +411,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         }
       }
       if (CS > 1) fence_proxy_async_smem();
-      FRNN_PROF_MARK(3);
       __syncthreads();
       // ---------------- push the partial sums of every peer's rows into that peer's receive slice [buf][me]
       if (CS > 1 && !(p.test_drop && crank == 0 && j == 0)) {  // (test hook: CTA 0 may withhold its first message)
@@ -428,7 +423,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
           if (elect_one_sync()) bulk_copy_to_cta(dsta, s0a + c * slice_bytes, slice_bytes, bara);
         }
       }
-      FRNN_PROF_MARK(4);
     } else {
       // ---------------- push this CTA's delta slice to every other CTA of the cluster
       if (CS > 1 && !(p.test_drop && crank == 0 && j == 0))  // uniform branch; one elected lane per warp copies
@@ -451,9 +445,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     issue(t - kStages, stage);
     stage = (stage + 1 == kStages) ? 0 : stage + 1;
     if constexpr (!RS) {
-      FRNN_PROF_MARK(3);
       wait_exchange(buf, j, t, buf);
-      FRNN_PROF_MARK(4);
       // ---------------- phase A (all-gather): part[g][b][p] = sum_d R[g][d][p] * delta_g[b][d]
       float acc[NT][4];
       warp_mma_rows<KT, NT>(Rreg, dgbuf + (size_t)buf * CS * SL, GS, g_w * U, ushift, SL, lane, acc);
@@ -468,10 +460,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         dst[(size_t)b0 * PS + 8] = acc[nt][2];
         dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
       }
-      FRNN_PROF_MARK(5);
       __syncthreads();
     }
-    FRNN_PROF_MARK(6);
     // After an expired wait the whole CTA leaves the time loop.  It sends nothing further, so every other CTA of the
     // cluster runs into its own bounded wait and leaves the same way; the byte counts of the barriers stay within the
     // few messages already in flight.
@@ -479,7 +469,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   }
   cp_async_wait<0>();
   if constexpr (RS) { if (T > 0) wait_exchange((T - 1) & 1, T - 1, -1, T & 1); }
-  FRNN_PROF_DUMP(p.status);
 
   // ---- cotangent of the initial states, bias gradient
 #pragma unroll

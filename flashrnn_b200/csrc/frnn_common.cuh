@@ -380,29 +380,6 @@ __device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const elem_t* 
       }
 }
 
-// Development aid (off in the shipped library): with -DFRNN_PROFILE thread 0 of CTA 0 sums the SM clock
-// between up to 7 marks of the step loop and leaves the 7 sums (u64) at byte 64 of the status block.
-#ifndef FRNN_PROF_TID
-#define FRNN_PROF_TID 0  // profiled thread and cluster rank (CTA x index)
-#endif
-#ifndef FRNN_PROF_CTA
-#define FRNN_PROF_CTA 0
-#endif
-#ifdef FRNN_PROFILE
-#define FRNN_PROF_DECL                                                                         \
-  const bool prof_on = (threadIdx.x == FRNN_PROF_TID && blockIdx.x == FRNN_PROF_CTA && blockIdx.y == 0 && blockIdx.z == 0); \
-  long long prof_sum[7] = {0, 0, 0, 0, 0, 0, 0};                                               \
-  long long prof_last = clock64()
-#define FRNN_PROF_MARK(i)                                                                      \
-  do { if (prof_on) { const long long c_ = clock64(); prof_sum[i] += c_ - prof_last; prof_last = c_; } } while (0)
-#define FRNN_PROF_DUMP(status)                                                                 \
-  do { if (prof_on) { for (int i_ = 0; i_ < 7; ++i_) reinterpret_cast<long long*>(status)[8 + i_] = prof_sum[i_]; } } while (0)
-#else
-#define FRNN_PROF_DECL do { } while (0)
-#define FRNN_PROF_MARK(i) do { } while (0)
-#define FRNN_PROF_DUMP(status) do { } while (0)
-#endif
-
 // Threads per CTA the kernels are compiled for, by k-steps held in registers per warp.
 // Slot rows of the per-thread prefetch rings: threads beyond the item count of the CTA own no items and no slots
 // (8-row batch tiles of the 4-gate cells keep only every second thread busy in the pointwise phase).

@@ -208,11 +208,9 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   const uint32_t my_slice0 = smem_u32(hbuf + (size_t)crank * SL);   // this CTA's slice in buffer 0
   const uint32_t buf_bytes = (uint32_t)(CS * SL * 2);               // distance to the same slice in buffer 1
   const uint32_t full_u32 = smem_u32(&full[0]);
-  FRNN_PROF_DECL;
 
   for (int t = 0; t < T; ++t) {
     const int cur = t & 1, nxt = cur ^ 1, stage = t % kStages;
-    FRNN_PROF_MARK(0);
     if (CS > 1 && t > 0) {
       if (!mbar_wait_bounded(&full[cur], ((t - 1) >> 1) & 1)) {
         poisoned = true;
@@ -222,7 +220,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       // re-arm for h_{t+1}; never after an expired wait: that phase is still open and has no arrival left to give
       if (tid == 0 && !poisoned && t + 2 < T) mbar_arrive_expect_tx(&full[cur], expect_bytes);
     }
-    FRNN_PROF_MARK(1);
     // ---------------- phase A: pre[b][g*U + u] = sum_k R[g][u][k] * h_{t-1}[b][k]
     {
       float acc[NT][4];
@@ -239,14 +236,12 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         dst[(size_t)(b0 + 1) * PS + 8] = acc[nt][3];
       }
     }
-    FRNN_PROF_MARK(2);
     __syncthreads();
     // Set when a wait of this step expired in some thread of the CTA.  The flag was written before the barrier above,
     // so every thread reads the same value; the CTA acts on it at the end of the step, where the load has long landed.
     const int quit = (CS > 1) ? *gave_up : 0;
     // ---------------- phase B: cell update of this thread's items; new h into this CTA's slice of hbuf[nxt]
     cp_async_wait<kStages - 1>();
-    FRNN_PROF_MARK(3);
     float cch[IPT][GCA][2];
     elem_t* hdst = hbuf + (size_t)nxt * CS * SL + (size_t)crank * SL;
 #pragma unroll
@@ -287,14 +282,12 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       *reinterpret_cast<uint32_t*>(hdst + hloc_it[i]) = hv;
     }
     if (CS > 1) fence_proxy_async_smem();  // make the slice visible to the bulk-copy engine
-    FRNN_PROF_MARK(4);
     __syncthreads();
     // ---------------- push: this CTA's slice of h_t -> hbuf[nxt] of every other CTA of the cluster
     // (test hook: CTA 0 may withhold its message of step 1 so that the peers' bounded waits can be seen to expire)
     if (CS > 1 && t + 1 < T && !(p.test_drop && crank == 0 && t == 1))  // uniform branch; one elected lane per warp copies
       push_slice_to_peers(my_slice0 + nxt * buf_bytes, slice_bytes, full_u32 + nxt * 8, crank, (uint32_t)CS,
                           (uint32_t)warp, (uint32_t)(nthr >> 5));
-    FRNN_PROF_MARK(5);
     // ---------------- off the critical path: results to global memory, next Wx prefetch
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
@@ -312,7 +305,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
       }
     }
     issue_wx(t + kStages < T, stage);
-    FRNN_PROF_MARK(6);
     // After an expired wait the whole CTA leaves the time loop.  It sends nothing further, so every other CTA of the
     // cluster runs into its own bounded wait and leaves the same way; the byte counts of the barriers stay within the
     // few messages already in flight.
@@ -320,7 +312,6 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   }
   cp_async_wait<0>();
   if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight
-  FRNN_PROF_DUMP(p.status);
 }
 
 }  // namespace FRNN_NS

@@ -35,23 +35,6 @@ constexpr int WF_STAGES = 8;                    // forward: Wx tiles in flight
 constexpr int WB_STAGES = 4;                    // backward: h tiles and cotangent tiles in flight (each)
 constexpr int W_THREADS = 160;
 
-// Development aid (off in the shipped library): with -DFRNN_PROFILE one row thread (slot 0) and the issuing thread
-// (slot 1) of CTA (0,0) sum the SM clock between marks of the step loop; the sums land at bytes 64 / 128 of the status block.
-#ifdef FRNN_PROFILE
-#define WPROF_DECL(on)                                                      \
-  const bool wprof_on = (on) && blockIdx.x == 0 && blockIdx.y == 0;         \
-  long long wprof_sum[7] = {0, 0, 0, 0, 0, 0, 0};                           \
-  long long wprof_last = clock64()
-#define WPROF_MARK(i) \
-  do { if (wprof_on) { const long long c_ = clock64(); wprof_sum[i] += c_ - wprof_last; wprof_last = c_; } } while (0)
-#define WPROF_DUMP(status, slot) \
-  do { if (wprof_on) for (int i_ = 0; i_ < 7; ++i_) reinterpret_cast<long long*>(status)[8 + 8 * (slot) + i_] = wprof_sum[i_]; } while (0)
-#else
-#define WPROF_DECL(on) do { } while (0)
-#define WPROF_MARK(i) do { } while (0)
-#define WPROF_DUMP(status, slot) do { } while (0)
-#endif
-
 // byte offset of 16-byte chunk `chunk` of row `row` inside a 128-byte-swizzled tile
 __device__ __forceinline__ uint32_t sw128(uint32_t row, uint32_t chunk) { return row * 128u + ((chunk ^ (row & 7u)) << 4); }
 
@@ -245,42 +228,34 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
       if (ok) issue_pre(0);
       else report_timeout(p.status, 0);
       int hr = 2;  // tile holding h_{t-1}
-      WPROF_DECL(true);
       for (int t = 0; ok && t < T; ++t) {
         if (t > 0) {
           if (!mbar_wait_bounded(h_ready, (uint32_t)((t - 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
           tc_fence_after();
         }
-        WPROF_MARK(0);
         // step t's threads overwrite the tile of h_{t-3}: its store (two groups back) must have left shared memory; with
         // three tiles the store gets two whole steps for that, and this wait is off the critical path
         bulk_wait_group_read<1>();
-        WPROF_MARK(1);
         const uint32_t a = h_lo + hr * TILE16, d = tmem + (t & 1) * WD;
 #pragma unroll
         for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc, 1u);
         umma_commit(&acc_full[t & 1]);
-        WPROF_MARK(2);
         if (t > 0) {  // h_{t-1} -> states[0][b0.., t-1, n, :]
           tma_store_5d(tms, base + WF_OFF_H + hr * WTILE, 0, n, t - 1, b0, 0);
           bulk_commit_group();
           // the Wx tile of step t-1 was consumed by MMAs that completed before h_{t-1} could be computed
           if (t - 1 + WF_STAGES < T) load_wx(t - 1 + WF_STAGES);
         }
-        WPROF_MARK(3);
         if (t + 1 < T) {
           if (!wait_wx()) {
             report_timeout(p.status, t);
             ok = false;
             break;
           }
-          WPROF_MARK(4);
           issue_pre(t + 1);
-          WPROF_MARK(5);
         }
         hr = (hr == 2) ? 0 : hr + 1;
       }
-      WPROF_DUMP(p.status, 1);
       if (ok) {
         if (mbar_wait_bounded(h_ready, (uint32_t)((T - 1) & 1))) {
           tma_store_5d(tms, base + WF_OFF_H + hr * WTILE, 0, n, T - 1, b0, 0);
@@ -299,14 +274,11 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
     // ------------------------------------------------------------ row threads: h_t = tanh(acc)
     const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
     int hw = 0;  // tile that receives h_t
-    WPROF_DECL(tid == 0);
     for (int t = 0; t < T; ++t) {
       if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); break; }
       tc_fence_after();
-      WPROF_MARK(0);
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (t & 1) * WD, r0, r1);
-      WPROF_MARK(1);
       unsigned char* dst = sm + WF_OFF_H + (PAIR ? (uint32_t)((t + 2) >> 1 & 1) * 2 * WTILE : hw * WTILE);
       hw = (hw == 2) ? 0 : hw + 1;
 #pragma unroll
@@ -316,13 +288,10 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
         for (int i = 0; i < 8; ++i) v[i] = fast_tanh(__uint_as_float(j < 4 ? r0[j * 8 + i] : r1[(j - 4) * 8 + i]));
         *reinterpret_cast<uint4*>(dst + (PAIR ? sw128_pair(tid, j, t & 1) : sw128(tid, j))) = pack8(v);
       }
-      WPROF_MARK(2);
       fence_proxy_async_smem();  // the tile is read by the tensor core and by the bulk store
       tc_fence_before();
       mbar_arrive(h_ready);
-      WPROF_MARK(3);
     }
-    WPROF_DUMP(p.status, 0);
   }
   tc_fence_before();
   __syncthreads();
@@ -332,42 +301,6 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
   }
 }
 
-#ifdef FRNN_WIDE_COPYONLY
-// Development aid: the streaming ceiling of the forward loop's access pattern -- every step one tile of Wx in, the same
-// tile out to `states`, no arithmetic.  Built only with -DFRNN_WIDE_COPYONLY, where it replaces the forward kernel.
-__global__ void __launch_bounds__(W_THREADS, 1)
-wide_copy_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states, const WideFwdParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  const uint32_t raw = smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  unsigned char* sm = smem_raw + (base - raw);
-  constexpr int S = 10;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sm + S * WTILE);
-  const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S; ++s) mbar_init(&full[s], 1);
-    fence_mbar_init();
-  }
-  __syncthreads();
-  if (threadIdx.x == 128) {
-    const void* tmw = &tm_wx;
-    const void* tms = &tm_states;
-    auto load = [&](int t) {
-      mbar_arrive_expect_tx(&full[t % S], WTILE);
-      tma_load_5d(base + (t % S) * WTILE, tmw, 0, n, 0, t, b0, &full[t % S]);
-    };
-    for (int t = 0; t < T && t < S; ++t) load(t);
-    for (int t = 0; t < T; ++t) {
-      if (!mbar_wait_bounded(&full[t % S], (uint32_t)((t / S) & 1))) { report_timeout(p.status, t); break; }
-      tma_store_5d(tms, base + (t % S) * WTILE, 0, n, t, b0, 0);
-      bulk_commit_group();
-      bulk_wait_group_read<3>();  // the store issued four steps ago has left its slot
-      if (t >= 3 && t - 3 + S < T) load(t - 3 + S);
-    }
-    bulk_wait_group<0>();
-  }
-}
-#endif
 
 // ================================================================================================ backward
 struct WideBwdParams {
@@ -403,11 +336,6 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = smem_raw + (base - raw);
-#ifdef FRNN_PROFILE
-  const bool wt_on = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0;  // wall-clock stamps at byte 192 of the status block
-  unsigned long long* wt = reinterpret_cast<unsigned long long*>(p.status) + 24;
-  if (wt_on) wt[0] = global_timer_ns();
-#endif
   float* sdb = reinterpret_cast<float*>(sm + WB_OFF_DB);
   uint64_t* h_full = reinterpret_cast<uint64_t*>(sm + WB_OFF_BAR);  // [WB_STAGES]
   uint64_t* e_full = h_full + WB_STAGES;                            // [WB_STAGES]
@@ -616,7 +544,6 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       bool ok = true;
       int where = 0;
       int dj = 0;  // delta tile of step index j
-      WPROF_DECL(true);
       do {
         if (!mbar_wait_bounded(&e_full[0], 0)) { ok = false; break; }
         e_seen = 1;
@@ -631,11 +558,9 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           where = j;
           if (!mbar_wait_bounded(d_ready, (uint32_t)(j & 1))) { ok = false; break; }
           tc_fence_after();
-          WPROF_MARK(0);
           if (h_seen < j + 1) h_seen = j + 1;  // the row threads of step j have read h tile j
           // step j+1 overwrites the tile of delta_{j-2}: that store (two groups back) must have left shared memory
           bulk_wait_group_read<1>();
-          WPROF_MARK(1);
           const uint32_t dt = base + WB_OFF_D + dj * WTILE, dl = d_lo + dj * TILE16;
           // dh accumulator of step j+1 (+)= delta_j * R; step T (the cotangent of h_{-1}) has no external part
           const uint32_t acc = tmem + ((j + 1) & 1) * WD;
@@ -643,19 +568,15 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
           for (uint32_t k = 0; k < 4; ++k)
             umma_parts(acc, dl + 2 * k, HI, r_lo + 2 * k, HI, idesc_kk, (j + 1 < T || k > 0) ? 1u : 0u);
           umma_commit(&acc_full[(j + 1) & 1]);
-          WPROF_MARK(2);
           tma_store_5d(tmd, dt, 0, n, 0, T - 1 - j, b0);  // delta_j -> dWx[b0.., t, 0, n, :]
           bulk_commit_group();
-          WPROF_MARK(3);
           // dR += delta_j^T * h_{t-1}  (h tile of sequence index j + 1)
           if (!mbar_wait_bounded(&h_full[(j + 1) % WB_STAGES], (uint32_t)(((j + 1) / WB_STAGES) & 1))) { ok = false; break; }
           h_seen = j + 2;
-          WPROF_MARK(4);
           const uint32_t hl = hr_lo + ((j + 1) % WB_STAGES) * TILE16;
 #pragma unroll
           for (uint32_t ks = 0; ks < 8; ++ks)  // 16 batch rows = 2048 bytes per k-step
             umma_parts(tmem + 2 * WD, dl + 128 * ks, HI, hl + 128 * ks, HI, idesc_mm, (j > 0 || ks > 0) ? 1u : 0u);
-          WPROF_MARK(5);
           // h tile j-1: its row threads (step j-1) and its dR MMAs (step j-2, completed before the accumulator of
           // step j was signalled) are done; cotangent tile j: consumed by MMAs that completed before step j started
           if (j >= 1 && j - 1 + WB_STAGES <= T) load_h(j - 1 + WB_STAGES);
@@ -665,11 +586,9 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
             e_seen = j + 3;
             issue_pre(j + 2);
           }
-          WPROF_MARK(6);
           dj = (dj == 2) ? 0 : dj + 1;
         }
       } while (false);
-      WPROF_DUMP(p.status, 1);
       if (!ok) report_timeout(p.status, where);
       umma_commit(dr_done);
       for (int i = (h_seen > h_loads - WB_STAGES ? h_seen : h_loads - WB_STAGES); i < h_loads; ++i)
@@ -687,10 +606,6 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
     for (int i = 0; i < WD; ++i) db[i] = 0.f;
     bool ok = true;
     int dw = 0;  // tile that receives delta of step index j
-#ifdef FRNN_PROFILE
-    if (wt_on) wt[1] = global_timer_ns();
-#endif
-    WPROF_DECL(tid == 0);
     for (int j = 0; j < T; ++j) {
       const int tt = T - 1 - j, hr = ((T + 1) >> 1) - 1 - (tt >> 1);  // time of the step; PAIR: its h box
       if (!mbar_wait_bounded(&acc_full[j & 1], (uint32_t)((j >> 1) & 1)) ||
@@ -701,10 +616,8 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         break;
       }
       tc_fence_after();
-      WPROF_MARK(0);
       uint32_t r0[32], r1[32];
       tmem_ld64(trow + (j & 1) * WD, r0, r1);
-      WPROF_MARK(1);
       const unsigned char* hsrc = sm + WB_OFF_H + (PAIR ? (uint32_t)(hr & 1) * 2 * WTILE : (j % WB_STAGES) * WTILE);
       unsigned char* dst = sm + WB_OFF_D + (PAIR ? (uint32_t)((tt >> 1) & 1) * 2 * WTILE : dw * WTILE);
       dw = (dw == 2) ? 0 : dw + 1;
@@ -726,16 +639,10 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
         }
         *reinterpret_cast<uint4*>(dst + (PAIR ? sw128_pair(tid, c, tt & 1) : off)) = pack8(v);
       }
-      WPROF_MARK(2);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(d_ready);
-      WPROF_MARK(3);
     }
-    WPROF_DUMP(p.status, 0);
-#ifdef FRNN_PROFILE
-    if (wt_on) wt[2] = global_timer_ns();
-#endif
     // cotangent of the initial state: the accumulator of "step T"
     if (ok && mbar_wait_bounded(&acc_full[T & 1], (uint32_t)((T >> 1) & 1))) {
       tc_fence_after();
@@ -775,25 +682,16 @@ wide_bwd_elman_kernel(const __grid_constant__ CUtensorMap tm_states, const __gri
       report_timeout(p.status, T + 1);
     }
 #pragma unroll
-#ifdef FRNN_PROFILE
-    if (wt_on) wt[3] = global_timer_ns();
-#endif
     for (int i = 0; i < WD; ++i) {  // db: sum over the 32 rows of the warp by shuffles, then one partial per warp
       float v = db[i];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
       if (lane == 0) sdb[warp * WD + i] = v;
     }
-#ifdef FRNN_PROFILE
-    if (wt_on) wt[4] = global_timer_ns();
-#endif
   }
   tc_fence_before();
   __syncthreads();
   if (tid < WD) atomicAdd(p.dbias + (size_t)n * WD + tid, sdb[tid] + sdb[WD + tid] + sdb[2 * WD + tid] + sdb[3 * WD + tid]);
-#ifdef FRNN_PROFILE
-  if (wt_on) wt[5] = global_timer_ns();
-#endif
   if (warp == 4) {
     __syncwarp();
     tmem_dealloc(tmem, 256);
@@ -862,12 +760,6 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
   auto kern = pair ? wide_fwd_elman_kernel<true> : wide_fwd_elman_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
   if (e != cudaSuccess) return e;
-#ifdef FRNN_WIDE_COPYONLY
-  e = cudaFuncSetAttribute(wide_copy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 10 * (int)WTILE + 2048);
-  if (e != cudaSuccess) return e;
-  wide_copy_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, 10 * WTILE + 2048, stream>>>(tm_wx, tm_st, p);
-  return cudaGetLastError();
-#endif
   kern<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WF_SMEM, stream>>>(tm_wx, tm_st, p);
   return cudaGetLastError();
 }

@@ -78,12 +78,15 @@ static inline REAL logsigm(REAL x) {
 }
 
 /* pre[g][d] = sum_p R[g][n][d][p] * h[p]   (vanilla/__init__.py:53-61) */
-HOT static void recurrent_matvec(const REAL* R, int Gr, int N, int D, int n, const REAL* h, REAL* pre) {
+HOT static void recurrent_matvec(const REAL* restrict R, int Gr, int N, int D, int n, const REAL* restrict h,
+                                 REAL* restrict pre) {
   for (int g = 0; g < Gr; ++g) {
     const REAL* Rg = R + (((size_t)g * N + n) * D) * D;
     for (int d = 0; d < D; ++d) {
       const REAL* row = Rg + (size_t)d * D;
       REAL acc = 0;
+      /* the sum may be formed in vector lanes (a different association than left to right: rounding-level effect) */
+#pragma omp simd reduction(+ : acc)
       for (int p = 0; p < D; ++p) acc += row[p] * h[p];
       pre[g * D + d] = acc;
     }
@@ -91,8 +94,8 @@ HOT static void recurrent_matvec(const REAL* R, int Gr, int N, int D, int n, con
 }
 
 /* dh[p] += sum_{g,d} delta[g][d] * R[g][n][d][p] ;  dRn[g][d][p] += delta[g][d] * hprev[p] */
-HOT static void recurrent_backward(const REAL* R, int Gr, int N, int D, int n, const REAL* delta,
-                                   const REAL* hprev, REAL* dh, REAL* dRn) {
+HOT static void recurrent_backward(const REAL* restrict R, int Gr, int N, int D, int n, const REAL* restrict delta,
+                                   const REAL* restrict hprev, REAL* restrict dh, REAL* restrict dRn) {
   for (int g = 0; g < Gr; ++g) {
     const REAL* Rg = R + (((size_t)g * N + n) * D) * D;
     REAL* dRg = dRn + (size_t)g * D * D;
@@ -100,6 +103,7 @@ HOT static void recurrent_backward(const REAL* R, int Gr, int N, int D, int n, c
       const REAL dl = delta[g * D + d];
       const REAL* row = Rg + (size_t)d * D;
       REAL* drow = dRg + (size_t)d * D;
+#pragma omp simd
       for (int p = 0; p < D; ++p) {
         dh[p] += dl * row[p];
         drow[p] += dl * hprev[p];

@@ -10,6 +10,13 @@ inputs, back-propagates a seeded random cotangent through autograd and stores in
 gradients in ``<cell>_<tag>.npz`` (float64 and float32 variants).  The LSTM/GRU/Elman cotangent covers
 every state; the sLSTM cotangent reaches the loss through ``h`` only (the reference's own tests do the
 same, tests/utils.py:318-327) because the closed-form backward treats the stabiliser ``m`` as constant.
+
+``<cell>_fwbw_float32.npz`` (lstm, slstm) come from the reference's second CPU backend, ``backend="vanilla_fwbw"``: the
+same loop with the hand-written closed-form backward (flashrnn/flashrnn/vanilla_fwbw/bw.py:19-189) instead of autograd.
+That backend takes ``gradient_recurrent_clipval`` (flashrnn.py:1005-1024) but cannot run with one: its autograd
+function hands the float to ``save_for_backward`` (vanilla_fwbw/fwbw.py:52-54), which raises TypeError, and
+``backward_sequence`` never reads the value (bw.py:19-97).  So no CPU path of the reference applies the clip options;
+the vectors here are generated without them.
 """
 import argparse
 import sys
@@ -48,11 +55,25 @@ def make_inputs(function, B, T, N, D, random_init, dtype, seed):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds flashrnn/)")
+    ap.add_argument("--only-fwbw", action="store_true", help="write only the vanilla_fwbw vectors")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     sys.dont_write_bytecode = True
     from flashrnn import flashrnn  # the reference, unmodified
 
+    for function in ("lstm", "slstm"):  # closed-form backward of the reference's manual PyTorch path
+        B, T, N, D = 3, 9, 2, 16
+        Wx, R, b, s0, cot, cot_last = make_inputs(function, B, T, N, D, True, torch.float32, seed=2000)
+        Wx.requires_grad_(True), R.requires_grad_(True), b.requires_grad_(True), s0.requires_grad_(True)
+        states, last = flashrnn(Wx, R, b, s0, function=function, backend="vanilla_fwbw", dtype="float32")
+        loss = (states * cot).sum() + (last * cot_last).sum()
+        loss.backward()
+        out = dict(Wx=Wx, R=R, b=b, s0=s0, cot=cot, cot_last=cot_last, states=states, last=last,
+                   dWx=Wx.grad, dR=R.grad, db=b.grad, ds0=s0.grad)
+        np.savez_compressed(HERE / f"{function}_fwbw_float32.npz", **{k: v.detach().numpy() for k, v in out.items()})
+        print(function, "fwbw", tuple(states.shape), float(loss))
+    if args.only_fwbw:
+        return
     for function in DIMS:
         for ci, (tag, B, T, N, D, rinit) in enumerate(CASES):
             for dt, dname in ((torch.float64, "float64"), (torch.float32, "float32")):

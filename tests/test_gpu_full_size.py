@@ -1,15 +1,17 @@
 """GPU: the benchmark configurations at FULL size.
 
-C1 and C2 are compared with the oracle outright (the C oracle finishes them in seconds).  For C3-C5 the oracle runs on
-a slice of batch rows -- rows are independent, so states, dWx and ds0 of those rows must match the full run -- and
-size-independent properties cover the rest: dR/db of the full batch equal the sum over batch shards (what the
-multi-GPU path relies on), and permuting the batch permutes the outputs.  Inputs follow the distributions the
-configurations name (tests/util.py, bench.py)."""
+C1-C4 are compared with the oracle outright, every output and every gradient of the whole batch (the oracle works
+through the batch a few rows at a time; C3 and C4 take it some tens of seconds on the host cores).  C5 (1024 rows) is
+too much for the CPU: there the oracle checks (i) a few rows of the full run (rows are independent, so states, dWx
+and ds0 of those rows must match) and (ii) everything, dR and db included, of a 128-row full-length sub-batch forced
+onto the same 128-row tensor-core loops the full configuration takes.  Size-independent properties cover the rest:
+dR/db of the full batch equal the sum over batch shards (what the multi-GPU path relies on), and permuting the batch
+permutes the outputs.  Inputs follow the distributions the configurations name (tests/util.py, bench.py)."""
 import numpy as np
 import pytest
 import torch
 
-from tests.util import GRAD_REL_L2, H_MAX_ABS, assert_parity, bf16_round, max_abs, rel_l2, run_oracle
+from tests.util import GRAD_REL_L2, H_MAX_ABS, assert_parity, max_abs, rel_l2, run_oracle, run_oracle_sliced
 
 pytestmark = pytest.mark.gpu
 
@@ -42,12 +44,16 @@ def config_inputs(name, device="cuda"):
     return function, [t.to(device) for t in (Wx, R, b, s0)]
 
 
-def run_full(function, tensors):
+def run_full(function, tensors, **cfg_kw):
     """fwd + bwd (loss = sum(h)) through the public API; tensors stay on the GPU."""
-    from flashrnn_b200 import flashrnn
+    from flashrnn_b200 import FlashRNNConfig, flashrnn
 
     Wx, R, b, s0 = (t.detach().clone().requires_grad_(True) for t in tensors)
-    states, last = flashrnn(Wx, R, b, s0, function=function)
+    cfg = None
+    if cfg_kw:
+        cfg = FlashRNNConfig(function=function, head_dim=Wx.shape[4], num_heads=Wx.shape[3], batch_size=Wx.shape[0],
+                             dtype_s="float32" if s0.dtype == torch.float32 else "bfloat16", **cfg_kw)
+    states, last = flashrnn(Wx, R, b, s0, function=function, config=cfg)
     states[0].float().sum().backward()
     torch.cuda.synchronize()
     return dict(states=states.detach(), last=last.detach(), dWx=Wx.grad, dR=R.grad, db=b.grad, ds0=s0.grad)
@@ -62,15 +68,31 @@ def to_np(d, rows=None):
     return out
 
 
-@pytest.mark.parametrize("name", ["C1", "C2"])
+@pytest.mark.parametrize("name", ["C1", "C2", "C3", "C4"])
 def test_full_size_against_oracle(cuda_device, name):
+    """states, dWx, ds0 of every row and dR, db summed over the whole batch and all T steps."""
     function, tensors = config_inputs(name)
     got = to_np(run_full(function, tensors))
-    ref = run_oracle(function, *(t.to(torch.float64).cpu() for t in tensors))
-    assert_parity(function, got, ref, tag=name, zero_init=(name != "C2"))
+    ref = run_oracle_sliced(function, *tensors)
+    errs = assert_parity(function, got, ref, tag=name, zero_init=(name != "C2"))
+    print(name, {k: f"{v:.2e}" for k, v in errs.items()})
 
 
-@pytest.mark.parametrize("name,rows", [("C3", 2), ("C4", 1), ("C5", 4)])
+def test_full_length_128_row_loops_against_oracle(cuda_device):
+    """C5's 128-row tensor-core loops over all 2048 steps on a 128-row sub-batch (dR accumulated in tensor memory over
+    the whole sequence): every output and gradient against the oracle."""
+    function, tensors = config_inputs("C5")
+    Wx, R, b, s0 = tensors
+    rows = 128
+    sub = (Wx[:rows].contiguous(), R, b, s0[:, :rows].contiguous())
+    del Wx, tensors
+    got = to_np(run_full(function, sub, batch_tile=128))
+    ref = run_oracle_sliced(function, *sub, rows_per_slice=32)
+    errs = assert_parity(function, got, ref, tag="C5/128 rows")
+    print("C5 sub-batch", {k: f"{v:.2e}" for k, v in errs.items()})
+
+
+@pytest.mark.parametrize("name,rows", [("C5", 4)])
 def test_full_size_batch_slice_against_oracle(cuda_device, name, rows):
     function, tensors = config_inputs(name)
     full = run_full(function, tensors)

@@ -125,7 +125,9 @@ def test_alternative_user_layouts(cuda_device):
     from flashrnn_b200 import FlashRNNConfig, flashrnn
 
     B, T, N, D = 4, 6, 2, 64
-    Wx, R, b, s0 = (t.to("cuda", torch.bfloat16) for t in make_inputs("lstm", B, T, N, D, seed=23, random_init=True))
+    cpu_inputs = make_inputs("lstm", B, T, N, D, seed=23, random_init=True)
+    oracle = run_oracle("lstm", *cpu_inputs)
+    Wx, R, b, s0 = (t.to("cuda", torch.bfloat16) for t in cpu_inputs)
     base = [t.clone().requires_grad_(True) for t in (Wx, R, b, s0)]
     ref_states, ref_last = flashrnn(*base[:3], base[3], function="lstm")
     ref_states[0].float().sum().backward()
@@ -140,6 +142,11 @@ def test_alternative_user_layouts(cuda_device):
     assert torch.equal(alt[0].grad.permute(1, 0, 2, 3, 4), base[0].grad)
     assert torch.allclose(alt[1].grad.permute(1, 0, 2, 3).float(), base[1].grad.float(), atol=1e-2, rtol=1e-2)
     assert torch.allclose(alt[2].grad.permute(1, 0, 2).float(), base[2].grad.float(), atol=1e-2, rtol=1e-2)
+    # and against the oracle, after mapping the alternative layouts back
+    f = lambda x: x.detach().to(torch.float64).cpu().numpy()
+    got = dict(states=f(states.permute(0, 2, 1, 3, 4)), last=f(last.permute(0, 2, 1, 3, 4)), dWx=f(alt[0].grad.permute(1, 0, 2, 3, 4)),
+               dR=f(alt[1].grad.permute(1, 0, 2, 3)), db=f(alt[2].grad.permute(1, 0, 2)), ds0=f(alt[3].grad.permute(0, 2, 1, 3, 4)))
+    assert_parity("lstm", got, oracle, tag="alternative layouts", zero_init=False)
 
 
 def test_deterministic_forward(cuda_device):
@@ -165,6 +172,8 @@ def test_inference_matches_training_forward(cuda_device):
     s_tr, _ = flashrnn(*a[:3], a[3], function="gru")
     assert torch.equal(s_inf, s_tr.detach())
     assert torch.equal(last_inf, s_inf[:, :, -1:])
+    ref = run_oracle("gru", Wx, R, b, s0)  # the no-cache (inference) plan against the oracle
+    assert np.abs(s_inf.to(torch.float64).cpu().numpy()[0] - ref["states"][0]).max() <= 2e-2
 
 
 def test_chunked_sequence_equals_whole(cuda_device):

@@ -1,5 +1,5 @@
-"""GPU: step-by-step decoding through FlashRNNStepper equals the full-sequence forward of the same inputs, for every
-cell, with one-step and multi-step chunks, and when the step is replayed from a CUDA graph.  Inside one launch the
+"""GPU: step-by-step decoding through FlashRNNStepper against the oracle's states (every cell, one-step and multi-step
+chunks) and against the full-sequence forward of the same inputs, also when the step is replayed from a CUDA graph.  Inside one launch the
 cell states that do not feed the matrix product (c, n, m) are carried in fp32 registers and only their stored copy is
 rounded; across launches they pass through the state tensor.  So with float32 states the comparison is bit-exact, and
 with bfloat16 states it holds to bfloat16 rounding."""
@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from flashrnn_b200 import FlashRNNStepper, flashrnn
-from tests.util import make_inputs
+from tests.util import H_MAX_ABS, make_inputs, max_abs, run_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -16,6 +16,25 @@ def _inputs(function, B, T, N, D, dev, seed):
     Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=seed, random_init=True)
     to = lambda x: x.to(torch.bfloat16).to(dev).contiguous()
     return to(Wx), to(R), to(b), to(s0)
+
+
+def _oracle_states(function, Wx, R, b, s0):
+    """fp64 oracle forward on the very values the device tensors hold."""
+    from oracle import oracle_forward
+
+    f = lambda x: x.detach().to(torch.float64).cpu().numpy()
+    states, _ = oracle_forward(function, f(Wx), f(R), f(b), f(s0), slstm_global_rule=False)
+    return states
+
+
+def _assert_states_match_oracle(got, ref, tag):
+    """the tolerance rule of tests/util.py: h to 2e-2, unbounded states relative to their size"""
+    import numpy as np
+
+    got = got.detach().to(torch.float64).cpu().numpy()
+    assert max_abs(got[0], ref[0]) <= H_MAX_ABS, tag
+    for s in range(1, ref.shape[0]):
+        assert max_abs(got[s], ref[s]) <= H_MAX_ABS * max(1.0, float(np.abs(ref[s]).max())), (tag, s)
 
 
 @pytest.mark.parametrize("function", ["lstm", "gru", "elman", "slstm"])
@@ -30,9 +49,11 @@ def test_stepper_equals_full_sequence(cuda_device, function, chunk, dtype_s):
     with torch.no_grad():
         full, last = flashrnn(Wx, R, b, states=s0, function=function)
     assert full.dtype == s0.dtype
+    oracle = _oracle_states(function, Wx, R, b, s0)
     st = FlashRNNStepper(R, b, function=function, batch_size=B, chunk=chunk, dtype_s=dtype_s, states=s0)
     for t in range(0, T, chunk):
         out = st.step(Wx[:, t:t + chunk].contiguous())
+        _assert_states_match_oracle(out, oracle[:, :, t:t + chunk], (function, chunk, t))
         ref = full[:, :, t:t + chunk]
         if exact:
             assert torch.equal(out, ref), (function, chunk, t)

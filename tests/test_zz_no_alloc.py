@@ -1,7 +1,8 @@
 """GPU: frnn_forward_noalloc, the forward entry point for callers that cannot allocate device memory where they
 call the library (a fixed arena sized at start-up, a latency-critical loop that must not hit cudaMalloc's device
 synchronisation).  Its scratch is a fixed array inside the library, shared by all calls on a device, so the test
-makes two different calls in a row and compares each with the regular entry point on a caller-provided workspace.
+makes different calls in a row and compares each with the regular entry point on a caller-provided workspace and
+with the oracle's states.
 Collected last on purpose (file name), and self-contained so that it also passes alone in a fresh process."""
 import ctypes
 
@@ -9,7 +10,7 @@ import pytest
 import torch
 
 from flashrnn_b200 import _native as nv
-from tests.util import H_MAX_ABS, make_inputs
+from tests.util import H_MAX_ABS, make_inputs, max_abs
 
 pytestmark = pytest.mark.gpu
 
@@ -36,14 +37,22 @@ def _forward_both(function, shape, training, device):
             nv.check("frnn_forward", L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), stream))
         torch.cuda.synchronize(device)
         out.append((states, cache))
-    return out
+    from oracle import oracle_forward
+
+    f = lambda x: x.to(torch.float64).cpu().numpy()
+    ref, _ = oracle_forward(function, f(Wx), f(R), f(b), f(s0), slstm_global_rule=False)
+    return out, ref
 
 
 def test_noalloc_forward_matches_workspace_forward_twice(cuda_device):
     # two calls in a row on the shared scratch: different cell, shape and R each time
     for function, shape, training in (("lstm", (16, 12, 2, 256), True), ("gru", (5, 9, 3, 64), False),
                                       ("lstm", (16, 12, 2, 256), True)):
-        (ref_states, ref_cache), (got_states, got_cache) = _forward_both(function, shape, training, cuda_device)
+        ((ref_states, ref_cache), (got_states, got_cache)), oracle = _forward_both(function, shape, training, cuda_device)
+        got = got_states.to(torch.float64).cpu().numpy()
+        assert max_abs(got[0], oracle[0]) <= H_MAX_ABS  # h against the oracle
+        for s in range(1, oracle.shape[0]):
+            assert max_abs(got[s], oracle[s]) <= H_MAX_ABS * max(1.0, float(abs(oracle[s]).max()))
         assert float((got_states.float() - ref_states.float()).abs().max()) <= H_MAX_ABS
         assert torch.equal(got_states, ref_states)  # same kernels, same inputs: in fact bit-identical
         if training:

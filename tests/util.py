@@ -82,6 +82,23 @@ def run_oracle(function, Wx, R, b, s0, cot=None, clip=0.0, forward_clip=0.0, cut
                        slstm_global_rule=False, forward_clip=forward_clip, cut=cut)
 
 
+def run_oracle_sliced(function, Wx, R, b, s0, rows_per_slice=8):
+    """The oracle over the whole batch, ``rows_per_slice`` batch rows at a time (rows are independent: states, dWx and
+    ds0 are concatenated, dR and db summed).  Takes tensors of any dtype; each slice is widened to fp64 on its own so
+    that the full-size configurations stay within a few GB of host memory."""
+    B = Wx.shape[0]
+    R64, b64 = R.to(torch.float64).cpu(), b.to(torch.float64).cpu()
+    parts = []
+    for r0 in range(0, B, rows_per_slice):
+        sl = slice(r0, min(B, r0 + rows_per_slice))
+        parts.append(run_oracle(function, Wx[sl].to(torch.float64).cpu(), R64, b64, s0[:, sl].to(torch.float64).cpu()))
+    out = {k: np.concatenate([p[k] for p in parts], axis=1) for k in ("states", "last", "ds0")}
+    out["dWx"] = np.concatenate([p["dWx"] for p in parts], axis=0)
+    out["dR"] = sum(p["dR"] for p in parts)
+    out["db"] = sum(p["db"] for p in parts)
+    return out
+
+
 def assert_parity(function, got, ref, check_ds0=True, tag="", zero_init=True):
     S = ref["states"].shape[0]
     errs = {}
