@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 # FRNN_B200_LIB points the binding at another build of the same library (development variants)
 LIB_PATH = Path(os.environ.get("FRNN_B200_LIB") or PKG / "libfrnn_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 NOALLOC_MAX_SCRATCH_BYTES = 8 << 20  # FRNN_NOALLOC_MAX_SCRATCH_BYTES
 CELL_IDS = {"lstm": 0, "gru": 1, "elman": 2, "slstm": 3}
 DTYPE_BF16, DTYPE_F32, DTYPE_F16 = 0, 1, 2
@@ -41,18 +41,33 @@ class FrnnPlan(ctypes.Structure):
         ("abi_version", ctypes.c_int32), ("prob", FrnnProblem), ("cluster_size", ctypes.c_int32),
         ("units_per_cta", ctypes.c_int32), ("batch_tile", ctypes.c_int32), ("threads", ctypes.c_int32),
         ("wx_stages", ctypes.c_int32), ("cache_slots", ctypes.c_int32), ("test_drop_exchange", ctypes.c_int32),
-        ("keep_packed_r", ctypes.c_int32), ("reserved", ctypes.c_int32 * 4),
+        ("keep_packed_r", ctypes.c_int32), ("probe_noop_cell", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3),
         ("cache_bytes", ctypes.c_uint64), ("workspace_bytes", ctypes.c_uint64), ("grads_offset", ctypes.c_uint64),
         ("grads_count", ctypes.c_uint64),
     ]
 
 
 class FrnnFwdArgs(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_void_p) for n in ("Wx", "R", "b", "s0", "states", "cache", "workspace", "last")]
+    _fields_ = [(n, ctypes.c_void_p) for n in ("Wx", "R", "b", "s0", "states", "cache", "workspace", "last")] + \
+               [("wx_stride", ctypes.c_int64 * 4)]
 
 
 class FrnnBwdArgs(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_void_p) for n in ("R", "s0", "states", "cache", "dstates", "dWx", "ds0", "workspace")]
+    _fields_ = [(n, ctypes.c_void_p) for n in ("R", "s0", "states", "cache", "dstates", "dWx", "ds0", "workspace")] + \
+               [("dstates_stride", ctypes.c_int64 * 4)]
+
+
+def kernel_strides(t, kernel_dtype):
+    """``(tensor, strides)`` for a 5-d tensor the kernels may read through strides: the element strides of its four
+    outer dimensions when the innermost one is contiguous, the dtype is the kernels' own and every stride is a
+    non-negative multiple of 8 (16 bytes) and the first element is 16-byte aligned; otherwise a dense copy and
+    ``(0, 0, 0, 0)`` (= dense)."""
+    if (t.dtype == kernel_dtype and t.dim() == 5 and t.stride(4) == 1 and not t.is_contiguous()
+            and (t.data_ptr() - 0) % 16 == 0):
+        st = tuple(int(s) for s in t.stride()[:4])
+        if all(s >= 0 and s % 8 == 0 for s in st) and any(st):
+            return t, (ctypes.c_int64 * 4)(*st)
+    return t.to(kernel_dtype).contiguous(), (ctypes.c_int64 * 4)(0, 0, 0, 0)
 
 
 class FrnnDevStatus(ctypes.Structure):

@@ -46,6 +46,12 @@ static int kernel_cell(const frnn_problem& pr) {
   return (pr.cell == CELL_ELMAN && pr.forward_clip > 0.f) ? (int)CELL_ELMAN_CLIP : pr.cell;
 }
 
+// Activation values cached per (b,t,n,d) in training.  Elman needs its one slot (the tanh output) only when h is
+// clamped afterwards; otherwise h itself serves and no cache buffer is needed at all.
+static int cache_slots_of(const frnn_problem& pr, const CellDims& cd) {
+  return (pr.cell == CELL_ELMAN && !(pr.forward_clip > 0.f)) ? 0 : cd.GC;
+}
+
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 constexpr size_t kMaxDynSmem = 227 * 1024;
 constexpr size_t kStatusBytes = 256;
@@ -174,8 +180,7 @@ static int fill_plan(const frnn_problem* pr, int cs, int bt, int stages, frnn_pl
   pl.batch_tile = cbt;
   pl.threads = plan_threads(cd, pl.units_per_cta, cbt);
   pl.wx_stages = kStages;
-  // Elman needs its one cache slot (the tanh output) only when h is clamped afterwards; otherwise h itself serves
-  pl.cache_slots = (pr->cell == CELL_ELMAN && !(pr->forward_clip > 0.f)) ? 0 : cd.GC;
+  pl.cache_slots = cache_slots_of(*pr, cd);
   // one bf16 pair per (item, slot, step) in the time loops' own order; batch rows padded to whole tiles
   const uint64_t rows = (uint64_t)((pr->B + cbt - 1) / cbt) * cbt;
   pl.cache_bytes = rows * pr->T * pl.cache_slots * pr->N * pr->D * 2;
@@ -201,9 +206,25 @@ static int check_plan(const frnn_plan* pl, CellDims* cd) {
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Strides of a caller-produced tensor: all zero = dense (the defaults are filled in), else each a non-negative
+// multiple of 8 elements (16 bytes: what the 4/8-byte cp.async reads and the tensor maps need).
+static bool resolve_strides(const int64_t (&in)[4], const long long (&dense)[4], long long (&out)[4]) {
+  if (!in[0] && !in[1] && !in[2] && !in[3]) {
+    for (int i = 0; i < 4; ++i) out[i] = dense[i];
+    return true;
+  }
+  for (int i = 0; i < 4; ++i) {
+    if (in[i] < 0 || in[i] % 8) return false;
+    out[i] = in[i];
+  }
+  return true;
+}
+
 static cudaError_t launch_loop(const LoopKernel& k, const frnn_plan& pl, const LoopParams& lp, cudaStream_t stream) {
   const size_t smem = k.smem_bytes(pl.prob.D, pl.units_per_cta, pl.threads);
-  cudaError_t e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // always the fixed maximum, never this plan's own size: the attribute belongs to the kernel, not to the launch, and a
+  // second host thread launching the same instantiation with a larger tile must not find it lowered in between
+  cudaError_t e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxDynSmem);
   if (e != cudaSuccess) return e;
   if (pl.cluster_size > 8) {  // clusters of more than 8 CTAs are a non-portable size: opt in
     e = cudaFuncSetAttribute(k.fn, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
@@ -286,13 +307,17 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   if (rc) return rc;
   if (!a || !a->Wx || !a->R || !a->b || !a->s0 || !a->states || !a->workspace) return FRNN_ERR_NULL;
   const frnn_problem& pr = plan->prob;
-  if (pr.training && cd.GC > 0 && !a->cache) return FRNN_ERR_NULL;
+  if (pr.training && cache_slots_of(pr, cd) > 0 && !a->cache) return FRNN_ERR_NULL;
   if (!aligned16(a->Wx) || !aligned16(a->R) || !aligned16(a->b) || !aligned16(a->s0) || !aligned16(a->states) ||
       !aligned16(a->workspace) || (a->cache && !aligned16(a->cache)))
     return FRNN_ERR_ALIGN;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const WsLayout w = workspace_layout(pr, cd);
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
+  const long long nd = (long long)pr.N * pr.D;
+  const long long wx_dense[4] = {(long long)pr.T * cd.Gw * nd, cd.Gw * nd, nd, pr.D};
+  long long wxs[4];
+  if (!resolve_strides(a->wx_stride, wx_dense, wxs)) return FRNN_ERR_ALIGN;
 
   // keep_packed_r: the workspace is left as the previous call left it (R fragments kept, status block not cleared, so
   // an expired wait of an earlier step stays on record until the caller reads it)
@@ -308,8 +333,9 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
                              (size_t)pr.T * row, row, (size_t)cd.S * pr.B, cudaMemcpyDeviceToDevice, stream);
   };
   if (is_wide(*plan)) {
-    e = launch_wide_forward(a->Wx, a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N,
-                            plan->test_drop_exchange, stream);
+    if (plan->probe_noop_cell) return FRNN_ERR_PLAN;
+    e = launch_wide_forward(a->Wx, wxs[0], wxs[1], wxs[3], a->R, a->b, a->s0, a->states, reinterpret_cast<unsigned*>(ws), pr.B,
+                            pr.T, pr.N, plan->test_drop_exchange, stream);
     return (int)(e == cudaSuccess ? copy_last() : e);
   }
   if (!plan->keep_packed_r) e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);
@@ -328,7 +354,10 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
   lp.test_drop = plan->test_drop_exchange;
-  const LoopKernel k = get_fwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8);
+  lp.wx_sb = wxs[0]; lp.wx_st = wxs[1]; lp.wx_sg = wxs[2]; lp.wx_sn = wxs[3];
+  const LoopKernel k = plan->probe_noop_cell ? get_fwd_kernel_floor(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8)
+                                             : get_fwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8);
+  if (!k.fn) return FRNN_ERR_PLAN;
   e = launch_loop(k, *plan, lp, stream);
   return (int)(e == cudaSuccess ? copy_last() : e);
 }
@@ -347,7 +376,7 @@ int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* 
   const frnn_problem& pr = plan->prob;
   if (!pr.training) return FRNN_ERR_TRAINING;
   if (!a || !a->R || !a->s0 || !a->states || !a->dstates || !a->dWx || !a->ds0 || !a->workspace) return FRNN_ERR_NULL;
-  if (cd.GC > 0 && !a->cache) return FRNN_ERR_NULL;
+  if (cache_slots_of(pr, cd) > 0 && !a->cache) return FRNN_ERR_NULL;
   if (!aligned16(a->R) || !aligned16(a->s0) || !aligned16(a->states) || !aligned16(a->dstates) || !aligned16(a->dWx) ||
       !aligned16(a->ds0) || !aligned16(a->workspace) || (a->cache && !aligned16(a->cache)))
     return FRNN_ERR_ALIGN;
@@ -356,6 +385,10 @@ int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* 
   unsigned char* ws = static_cast<unsigned char*>(a->workspace);
   float* grads = reinterpret_cast<float*>(ws + w.grads);
   const size_t nR = (size_t)cd.Gr * pr.N * pr.D * pr.D, nb = (size_t)cd.Gt * pr.N * pr.D;
+  const long long nd = (long long)pr.N * pr.D;
+  const long long ds_dense[4] = {(long long)pr.B * pr.T * nd, (long long)pr.T * nd, nd, pr.D};
+  long long dss[4];
+  if (!resolve_strides(a->dstates_stride, ds_dense, dss)) return FRNN_ERR_ALIGN;
 
   cudaError_t e = cudaSuccess;
   if (parts & FRNN_PART_LOOP) {
@@ -367,8 +400,9 @@ int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* 
     if (e != cudaSuccess) return (int)e;
   }
   if (is_wide(*plan)) {  // one kernel: reverse loop with dR and db accumulated inside; the dR part has nothing left to do
+    if (plan->probe_noop_cell) return FRNN_ERR_PLAN;
     if (parts & FRNN_PART_LOOP)
-      e = launch_wide_backward(a->R, a->s0, a->states, a->dstates, a->dWx, a->ds0, grads, grads + nR,
+      e = launch_wide_backward(a->R, a->s0, a->states, a->dstates, dss[1], dss[2], dss[3], a->dWx, a->ds0, grads, grads + nR,
                                reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, plan->test_drop_exchange, stream);
     return (int)e;
   }
@@ -389,9 +423,12 @@ int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* 
   lp.state_f32 = pr.dtype_state == FRNN_DTYPE_F32;
   lp.fclip = pr.forward_clip; lp.gclip = pr.grad_clip; lp.grad_cut = pr.grad_cut;
   lp.test_drop = plan->test_drop_exchange;
+  lp.ds_ss = dss[0]; lp.ds_sb = dss[1]; lp.ds_st = dss[2]; lp.ds_sn = dss[3];
   if (parts & FRNN_PART_LOOP) {
-    const LoopKernel k = get_bwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8,
-                                        bwd_mpw(pr, cd, plan->cluster_size, plan->batch_tile));
+    const int mpw = bwd_mpw(pr, cd, plan->cluster_size, plan->batch_tile);
+    const LoopKernel k = plan->probe_noop_cell ? get_bwd_kernel_floor(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8, mpw)
+                                               : get_bwd_kernel(kernel_cell(pr), kernel_kt(pr), plan->batch_tile / 8, mpw);
+    if (!k.fn) return FRNN_ERR_PLAN;
     e = launch_loop(k, *plan, lp, stream);
     if (e != cudaSuccess) return (int)e;
   }

@@ -37,6 +37,10 @@ LoopKernel get_bwd_kernel_gru(int kt, int nt, int mpw);
 LoopKernel get_bwd_kernel_elman(int kt, int nt, int mpw);
 LoopKernel get_bwd_kernel_slstm(int kt, int nt, int mpw);
 
+// chain-floor variants (frnn_inst_floor.cu); fn == nullptr for any tile but the benchmark configurations
+LoopKernel get_fwd_kernel_floor(int cell, int kt, int nt);
+LoopKernel get_bwd_kernel_floor(int cell, int kt, int nt, int mpw);
+
 cudaError_t launch_pack_recurrent(const void* R, void* out, int Gr, int N, int D, int transpose, cudaStream_t stream);
 cudaError_t launch_recurrent_grad(int cell, int B, int T, int N, int D, int Gr, int Gw, int state_f32, const void* dWx,
                                   const void* dg0, const void* states, const void* s0, float* dR, int sm_count,
@@ -48,11 +52,13 @@ cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int G
 constexpr int kWideBatchTile = 128;
 constexpr int kWideThreads = 160;
 bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, int grad_cut);
-cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
-                                unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream);
-cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
-                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N, int test_drop,
-                                 cudaStream_t stream);
+// wx_s* / ds_s*: element strides of the batch, time and head dimensions of Wx / dstates (their head dim is contiguous)
+cudaError_t launch_wide_forward(const void* Wx, long long wx_sb, long long wx_st, long long wx_sn, const void* R,
+                                const void* bias, const void* s0, void* states, unsigned* status, int B, int T, int N,
+                                int test_drop, cudaStream_t stream);
+cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, long long ds_sb,
+                                 long long ds_st, long long ds_sn, void* dWx, void* ds0, float* dR, float* dbias,
+                                 unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream);
 // dR fed by tensor-map bulk copies (frnn_dr_tma.cu): bf16 states, head dims 64 .. 256 in steps of 64
 bool recurrent_grad_tma_supported(int D, int state_f32);
 cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int Gr, int Gw, const void* dWx, const void* dg0,

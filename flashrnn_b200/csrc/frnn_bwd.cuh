@@ -44,7 +44,18 @@ template <int CELL>
 __device__ __forceinline__ void cell_backward(float dh, const float* dext, float* car, const float* cache,
                                               const float* cur, const float* prv, float* dR_, float* dW_,
                                               float* dB_) {
-  if constexpr (CELL == CELL_LSTM) {  // vanilla_fwbw/bw.py:100-133
+  if constexpr ((CELL & kNoopCell) != 0) {  // chain-floor probe: no gate math
+    using C = Cell<CELL>;
+    const float dg = 0.25f * dh + cache[0] * 0.f;
+#pragma unroll
+    for (int g = 0; g < C::Gr; ++g) dR_[g] = dg;
+#pragma unroll
+    for (int g = 0; g < C::Gw; ++g) dW_[g] = dg;
+#pragma unroll
+    for (int g = 0; g < C::Gt; ++g) dB_[g] = dg;
+#pragma unroll
+    for (int s = 0; s < C::S; ++s) car[s] = 0.f;
+  } else if constexpr (CELL == CELL_LSTM) {  // vanilla_fwbw/bw.py:100-133
     const float ig = cache[0], fg = cache[1], zv = cache[2], og = cache[3];
     const float tc = fast_tanh(cur[0]);
     const float dc = dext[1] + car[1] + dh * og * (1.f - tc * tc);
@@ -203,7 +214,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     s0_off[i] = ((size_t)bgc) * ND + (size_t)n * D + d;  // + s*B*ND
     ch_pf[i] = reinterpret_cast<const uint32_t*>(p.cache) + cta_lin * GCA * nitems + (it_on[i] ? q : 0) + (size_t)(T - 1) * ch_step;
     st_pf[i] = static_cast<const unsigned char*>(p.states) + (st_off + (size_t)(T - 2) * ND) * st_esz;  // valid for T >= 2
-    ds_pf[i] = static_cast<const unsigned char*>(p.dstates) + (st_off + (size_t)(T - 1) * ND) * st_esz;
+    ds_pf[i] = static_cast<const unsigned char*>(p.dstates) +
+               ((size_t)bgc * p.ds_sb + (size_t)(T - 1) * p.ds_st + (size_t)n * p.ds_sn + d) * st_esz;
     s0_it[i] = static_cast<const unsigned char*>(p.s0) + s0_off[i] * st_esz;
     dwx_ptr[i] = p.dWx + ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d + (size_t)(T - 1) * Gw * ND;
     dg0_ptr[i] = p.dg0 + st_off + (size_t)(T - 1) * ND;
@@ -242,11 +254,11 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
 #pragma unroll
         for (int k = 0; k < NEXT; ++k) {  // external cotangent of state k at t
           uint2* dst = rings + ((size_t)(stage * NSS + NNEED + k) * IPT + i) * RL + tid;
-          const unsigned char* src = ds_pf[i] + (size_t)k * st_sstride;
+          const unsigned char* src = ds_pf[i] + (size_t)k * p.ds_ss * st_esz;
           if (f32) cp_async8(dst, src); else cp_async4(dst, src);
         }
         st_pf[i] -= ND * st_esz;
-        ds_pf[i] -= ND * st_esz;
+        ds_pf[i] -= (size_t)p.ds_st * st_esz;
       }
     }
     cp_async_commit();

@@ -38,6 +38,14 @@ template <> struct Cell<CELL_SLSTM> {
   __host__ __device__ static constexpr int need(int i) { return i == 0 ? 1 : 2; }
 };
 
+// CELL | kNoopCell selects the measurement variant of a cell: same gate / state counts, same data movement, exchange and
+// barriers, but the gate arithmetic is replaced by a pass-through.  Its step time is the floor the serial chain of the
+// time loops sets without any cell math (results are meaningless).  Instantiated for the benchmark tiles only.
+constexpr int kNoopCell = 8;
+template <> struct Cell<CELL_LSTM | kNoopCell> : Cell<CELL_LSTM> {};
+template <> struct Cell<CELL_GRU | kNoopCell> : Cell<CELL_GRU> {};
+template <> struct Cell<CELL_SLSTM | kNoopCell> : Cell<CELL_SLSTM> {};
+
 // Time steps of inputs kept in flight ahead of the step being computed (cp.async ring depth).
 constexpr int kStages = 4;
 
@@ -62,6 +70,9 @@ struct LoopParams {
   float fclip, gclip;        // <= 0: off
   int grad_cut;              // backward: ignore the matrix part of the recurrent cotangent (truncated BPTT)
   int test_drop;             // test hook: CTA 0 of each cluster withholds one exchange message (see frnn_plan)
+  // element strides of the caller-produced tensors (D contiguous): Wx[b][t][g][n][.], dstates[s][b][t][n][.]
+  long long wx_sb, wx_st, wx_sg, wx_sn;
+  long long ds_ss, ds_sb, ds_st, ds_sn;
 };
 
 // ------------------------------------------------------------------------------------------------ PTX

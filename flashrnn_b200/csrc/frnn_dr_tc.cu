@@ -248,7 +248,7 @@ cudaError_t launch_recurrent_grad_tc(int cell, int B, int T, int N, int D, int G
   const size_t smem = tc_smem_bytes(D, J);
   const dim3 grid((unsigned)mtiles, (unsigned)N, (unsigned)splits);
   auto launch = [&](auto kern) -> cudaError_t {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);  // fixed: see launch_loop
     if (e != cudaSuccess) return e;
     kern<<<grid, TC_THREADS, smem, stream>>>(p);
     return cudaSuccess;

@@ -251,7 +251,7 @@ cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int 
   p.chunks_per_split = (int)((chunks + splits - 1) / splits);
   splits = (chunks + p.chunks_per_split - 1) / p.chunks_per_split;
   const size_t smem = (size_t)p.stages * (2 * mt + nb) * DT_BLK + 8 * (2 * DT_STAGES + 1) + 16 + 1024;
-  cudaError_t e = cudaFuncSetAttribute(recurrent_grad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaError_t e = cudaFuncSetAttribute(recurrent_grad_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);  // fixed maximum, so that concurrent host threads never lower each other's setting
   if (e != cudaSuccess) return e;
   recurrent_grad_tma_kernel<<<dim3((unsigned)mtiles, (unsigned)N, (unsigned)splits), DT_THREADS, smem, stream>>>(tm_dwx, tm_dg0,
                                                                                                                  tm_st, p);

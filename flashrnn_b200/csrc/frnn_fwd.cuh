@@ -27,7 +27,12 @@ namespace FRNN_NS {
 template <int CELL>
 __device__ __forceinline__ void cell_forward(const float* pre, const float* wx, const float* bias, float* st,
                                              float* cache) {
-  if constexpr (CELL == CELL_LSTM) {
+  if constexpr ((CELL & kNoopCell) != 0) {  // chain-floor probe: no gate math, values stay bounded
+    using C = Cell<CELL>;
+    st[0] = 0.25f * (pre[0] + wx[0] + bias[0]);
+#pragma unroll
+    for (int k = 0; k < C::GC; ++k) cache[k] = st[0];
+  } else if constexpr (CELL == CELL_LSTM) {
     const float ig = fast_sigmoid(pre[0] + wx[0] + bias[0]);
     const float fg = fast_sigmoid(pre[1] + wx[1] + bias[1]);
     const float zv = fast_tanh(pre[2] + wx[2] + bias[2]);
@@ -138,7 +143,7 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     const int bgc = bg < B ? bg : B - 1;
     pre_it[i] = pre + (size_t)bl * PS + 2 * up;
     hloc_it[i] = (uint32_t)(bl * US + 2 * up);
-    wx_pf[i] = p.Wx + ((size_t)bgc * T * Gw) * ND + (size_t)n * D + d;
+    wx_pf[i] = p.Wx + (size_t)bgc * p.wx_sb + (size_t)n * p.wx_sn + d;
     st_ptr[i] = static_cast<unsigned char*>(p.states) + (((size_t)bgc * T) * ND + (size_t)n * D + d) * st_esz;
     ch_ptr[i] = reinterpret_cast<uint32_t*>(p.cache) + cta_lin * GCA * nitems + (it_on[i] ? q : 0);
 #pragma unroll
@@ -171,8 +176,8 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
         if (it_ok[i]) {
 #pragma unroll
           for (int g = 0; g < Gw; ++g)
-            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * RL + tid, wx_pf[i] + (size_t)g * ND);
-          wx_pf[i] += (size_t)Gw * ND;
+            cp_async4(ring + ((size_t)(stage * Gw + g) * IPT + i) * RL + tid, wx_pf[i] + (size_t)g * p.wx_sg);
+          wx_pf[i] += p.wx_st;
         }
       }
     }

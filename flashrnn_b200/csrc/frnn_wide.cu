@@ -706,36 +706,32 @@ bool encode_tiles(CUtensorMap* tm, const void* base, const uint64_t (&dims)[5], 
   return encode_tiles16(tm, base, dims, strides, box);
 }
 
+// Element strides of the batch, time and head dimensions of a tensor whose head dim (64 elements) is contiguous.
+struct RowStrides { long long sb, st, sn; };
+static RowStrides dense_strides(int T, int N) { return RowStrides{(long long)T * N * WD, (long long)N * WD, WD}; }
+
 // [B,T,1,N,64] (Wx, dWx): coordinates (0, n, 0, t, b)
-bool map_btgnd(CUtensorMap* tm, const void* base, int B, int T, int N) {
-  const uint64_t row = WD * 2;
+bool map_btgnd(CUtensorMap* tm, const void* base, int B, int T, int N, RowStrides s) {
   const uint64_t dims[5] = {WD, (uint64_t)N, 1, (uint64_t)T, (uint64_t)B};
-  const uint64_t strides[4] = {row, row * N, row * N, row * N * T};
+  const uint64_t strides[4] = {(uint64_t)s.sn * 2, (uint64_t)s.st * 2, (uint64_t)s.st * 2, (uint64_t)s.sb * 2};
   return encode_tiles(tm, base, dims, strides, 4);
 }
 // [1,B,T,N,64] (states, dstates): coordinates (0, n, t, b, 0);  T = 1 gives the initial-state layout [1,B,1,N,64]
-bool map_sbtnd(CUtensorMap* tm, const void* base, int B, int T, int N) {
-  const uint64_t row = WD * 2;
+bool map_sbtnd(CUtensorMap* tm, const void* base, int B, int T, int N, RowStrides s) {
   const uint64_t dims[5] = {WD, (uint64_t)N, (uint64_t)T, (uint64_t)B, 1};
-  const uint64_t strides[4] = {row, row * N, row * N * T, row * N * T * B};
+  const uint64_t strides[4] = {(uint64_t)s.sn * 2, (uint64_t)s.st * 2, (uint64_t)s.sb * 2, (uint64_t)s.sb * 2};
   return encode_tiles(tm, base, dims, strides, 3);
 }
 
 // Both layouts ([B,T,1,N,64] and [1,B,T,N,64]) with B a multiple of 8, two time steps per box: coordinates
 // (0, 0, t, b / 8, n); a box is [16 groups of 8 rows][2 steps][8 rows][64], so each group's pages are touched twice in a row
-bool map_pairs(CUtensorMap* tm, const void* base, int B, int T, int N) {
-  const uint64_t row = WD * 2, st = row * N, sb = st * T;
+bool map_pairs(CUtensorMap* tm, const void* base, int B, int T, int N, RowStrides s) {
   const uint64_t dims[5] = {WD, 8, (uint64_t)T, (uint64_t)B / 8, (uint64_t)N};
-  const uint64_t strides[4] = {sb, st, sb * 8, row};
+  const uint64_t strides[4] = {(uint64_t)s.sb * 2, (uint64_t)s.st * 2, (uint64_t)s.sb * 16, (uint64_t)s.sn * 2};
   const uint32_t box[5] = {WD, 8, 2, WM / 8, 1};
   return encode_tiles16(tm, base, dims, strides, box);
 }
-#ifdef FRNN_WIDE_NOPAIR  // development aid: one time step per copy everywhere
-bool pairs_ok(int, int) { return false; }
-#else
 bool pairs_ok(int B, int T) { return B % 8 == 0 && T >= 2; }
-#endif
-
 
 }  // namespace
 
@@ -743,12 +739,14 @@ bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, in
   return cell == CELL_ELMAN && D == WD && !state_f32 && !(fclip > 0.f) && !(gclip > 0.f) && !grad_cut;
 }
 
-cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias, const void* s0, void* states,
-                                unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream) {
+cudaError_t launch_wide_forward(const void* Wx, long long wx_sb, long long wx_st, long long wx_sn, const void* R,
+                                const void* bias, const void* s0, void* states, unsigned* status, int B, int T, int N,
+                                int test_drop, cudaStream_t stream) {
   CUtensorMap tm_wx, tm_st;
   const bool pair = pairs_ok(B, T);
-  if (pair ? (!map_pairs(&tm_wx, Wx, B, T, N) || !map_pairs(&tm_st, states, B, T, N))
-           : (!map_btgnd(&tm_wx, Wx, B, T, N) || !map_sbtnd(&tm_st, states, B, T, N)))
+  const RowStrides dense = dense_strides(T, N), wxs = RowStrides{wx_sb, wx_st, wx_sn};
+  if (pair ? (!map_pairs(&tm_wx, Wx, B, T, N, wxs) || !map_pairs(&tm_st, states, B, T, N, dense))
+           : (!map_btgnd(&tm_wx, Wx, B, T, N, wxs) || !map_sbtnd(&tm_st, states, B, T, N, dense)))
     return cudaErrorNotSupported;
   WideFwdParams p;
   p.R = static_cast<const elem_t*>(R);
@@ -764,14 +762,16 @@ cudaError_t launch_wide_forward(const void* Wx, const void* R, const void* bias,
   return cudaGetLastError();
 }
 
-cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, void* dWx,
-                                 void* ds0, float* dR, float* dbias, unsigned* status, int B, int T, int N, int test_drop,
-                                 cudaStream_t stream) {
+cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, long long ds_sb,
+                                 long long ds_st, long long ds_sn, void* dWx, void* ds0, float* dR, float* dbias,
+                                 unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream) {
   CUtensorMap tm_st, tm_s0, tm_dst, tm_dwx;
   const bool pair = pairs_ok(B, T);
-  if (!(pair ? map_pairs(&tm_st, states, B, T, N) : map_sbtnd(&tm_st, states, B, T, N)) || !map_sbtnd(&tm_s0, s0, B, 1, N) ||
-      !(pair ? map_pairs(&tm_dst, dstates, B, T, N) : map_sbtnd(&tm_dst, dstates, B, T, N)) ||
-      !(pair ? map_pairs(&tm_dwx, dWx, B, T, N) : map_btgnd(&tm_dwx, dWx, B, T, N)))
+  const RowStrides dense = dense_strides(T, N), dss = RowStrides{ds_sb, ds_st, ds_sn};
+  if (!(pair ? map_pairs(&tm_st, states, B, T, N, dense) : map_sbtnd(&tm_st, states, B, T, N, dense)) ||
+      !map_sbtnd(&tm_s0, s0, B, 1, N, dense_strides(1, N)) ||
+      !(pair ? map_pairs(&tm_dst, dstates, B, T, N, dss) : map_sbtnd(&tm_dst, dstates, B, T, N, dss)) ||
+      !(pair ? map_pairs(&tm_dwx, dWx, B, T, N, dense) : map_btgnd(&tm_dwx, dWx, B, T, N, dense)))
     return cudaErrorNotSupported;
   WideBwdParams p;
   p.R = static_cast<const elem_t*>(R);

@@ -6,7 +6,12 @@ reference (flashrnn/flashrnn/flashrnn.py:124-207, 1093-1135).  What changed on p
 * one native backend (``"cuda_fused"``, alias ``"b200"``); Triton, the alternating cuBLAS backend and the
   PyTorch loops are gone and there is no CPU fallback -- other backend names raise;
 * tensors are consumed and produced in the user layouts directly (no permute + ``.contiguous()`` copies,
-  reference flashrnn.py:1049-1057, 1130-1135);
+  reference flashrnn.py:1049-1057, 1130-1135); the other layout strings (``input_shape="TBGHD"`` ...) reach the
+  kernels as strided views of Wx and of the incoming cotangent, and leave as permuted views of the outputs;
+* under ``torch.autocast`` the call behaves like the reference's ``custom_fwd(cast_inputs=dtype)`` / ``custom_bwd``
+  pair (flashrnn.py:690-695, 735-738): inputs of any floating dtype are cast to the kernel dtype by hand, gradients
+  come back in the inputs' dtypes, and since forward and backward consist of library calls only (no torch op that
+  autocast could re-type), there is nothing for the decorators to switch off;
 * GRU runs fused (the reference silently switches it to the alternating backend, flashrnn.py:280-284);
 * states may be kept in float32 while Wx/R/b are bfloat16 / float16 (``dtype_s="float32"`` or by passing float32
   ``states``), which the reference's fused kernel cannot express;
@@ -176,7 +181,7 @@ class _FrnnFunction(torch.autograd.Function):
         state_dtype = cfg.torch_dtype_s
         kdt = cfg.torch_dtype  # element type the kernels compute in: bfloat16 or float16
         in_dtypes = (Wx.dtype, R.dtype, b.dtype, s0.dtype)
-        Wx_k = Wx.to(kdt).contiguous()
+        Wx_k, wx_strides = _native.kernel_strides(Wx, kdt)  # a strided view (other input_shape) is read in place
         R_k = R.to(kdt).contiguous()
         b_k = b.to(kdt).contiguous()
         s0_k = s0.to(state_dtype).contiguous()
@@ -189,7 +194,8 @@ class _FrnnFunction(torch.autograd.Function):
         states = torch.empty((cfg.num_states, B, T, N, D), dtype=state_dtype, device=dev)
         cache = torch.empty(max(int(plan.cache_bytes), 16), dtype=torch.uint8, device=dev) if training else None
         ws = torch.empty(int(plan.workspace_bytes), dtype=torch.uint8, device=dev)
-        args = _native.FrnnFwdArgs(_ptr(Wx_k), _ptr(R_k), _ptr(b_k), _ptr(s0_k), _ptr(states), _ptr(cache), _ptr(ws))
+        args = _native.FrnnFwdArgs(_ptr(Wx_k), _ptr(R_k), _ptr(b_k), _ptr(s0_k), _ptr(states), _ptr(cache), _ptr(ws), None,
+                                   wx_strides)
         with torch.cuda.device(dev):
             _native.check("frnn_forward", _native.lib().frnn_forward(ctypes.byref(plan), ctypes.byref(args), _stream_ptr(dev)))
             if cfg.check_device_status:
@@ -209,10 +215,11 @@ class _FrnnFunction(torch.autograd.Function):
         R_k, s0_k, states, cache = ctx.saved_tensors
         plan, ws = ctx.plan, ctx.ws
         dev = states.device
-        dstates = dstates.to(states.dtype).contiguous()
+        dstates, ds_strides = _native.kernel_strides(dstates, states.dtype)  # e.g. the cotangent of a permuted output view
         dWx = torch.empty(ctx.wx_shape, dtype=R_k.dtype, device=dev)
         ds0 = torch.empty_like(s0_k)
-        args = _native.FrnnBwdArgs(_ptr(R_k), _ptr(s0_k), _ptr(states), _ptr(cache), _ptr(dstates), _ptr(dWx), _ptr(ds0), _ptr(ws))
+        args = _native.FrnnBwdArgs(_ptr(R_k), _ptr(s0_k), _ptr(states), _ptr(cache), _ptr(dstates), _ptr(dWx), _ptr(ds0), _ptr(ws),
+                                   ds_strides)
         L = _native.lib()
         with torch.cuda.device(dev):
             _native.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(args), _stream_ptr(dev)))
@@ -268,8 +275,9 @@ def flashrnn(
         raise RuntimeError("flashrnn_b200 runs on CUDA tensors only; there is no CPU fallback")
     if Wx.dim() != 5 or R.dim() != 4 or b.dim() != 3:
         raise ValueError("expected Wx[B,T,G,N,D], R[G,N,D,D], b[G,N,D]")
-    # other user layouts (reference flashrnn.py:165-173) are views of the native one; the kernels consume
-    # BTGHD / GHDP / GHD / SBTHD, so a non-default layout costs one copy of that tensor
+    # other user layouts (reference flashrnn.py:165-173) are views of the native one: Wx and the cotangent of the states
+    # reach the kernels through their strides, the outputs leave as permuted views; only R, b and the initial states
+    # (small) are copied into GHDP / GHD / SBTHD order
     Wx = _to_layout(Wx, config.input_shape, "BTGHD")
     R = _to_layout(R, config.recurrent_shape, "GHDP")
     b = _to_layout(b, config.bias_shape, "GHD")

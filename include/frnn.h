@@ -9,6 +9,10 @@
  *     user-facing layouts (reference flashrnn/flashrnn/flashrnn.py:165-173):
  *         Wx[B,T,Gw,N,D]  R[Gr,N,D,D] (R[g,n,d_out,d_in])  b[Gt,N,D]
  *         s0[S,B,1,N,D]   states[S,B,T,N,D]   dstates like states   dWx like Wx   ds0 like s0
+ *     The two large tensors the CALLER produces, Wx and dstates, may instead be strided views (element strides in
+ *     frnn_fwd_args.wx_stride / frnn_bwd_args.dstates_stride): that covers the reference's other layout strings
+ *     (input_shape "TBGHD", output_shape "STBHD", flashrnn.py:165-173, 291-321) without a permute + copy.  The tensors the
+ *     library produces (states, dWx, ds0) are always dense; a caller that wants another order returns a permuted view.
  *   - The library never allocates or frees device memory and never synchronises the host with the
  *     device (except frnn_read_device_status, which copies one small struct back).  The caller provides
  *     the activation cache and a workspace whose sizes frnn_query reports.
@@ -27,7 +31,7 @@
 extern "C" {
 #endif
 
-#define FRNN_ABI_VERSION 2
+#define FRNN_ABI_VERSION 3
 
 /* cells: gate/state counts follow the reference registry flashrnn/flashrnn/flashrnn.py:49-71 */
 enum { FRNN_CELL_LSTM = 0, FRNN_CELL_GRU = 1, FRNN_CELL_ELMAN = 2, FRNN_CELL_SLSTM = 3 };
@@ -84,7 +88,12 @@ typedef struct frnn_plan {
                                  1: the workspace is as an earlier frnn_forward with this plan left it and R has not
                                  changed since: skip both launches (step-by-step decoding calls frnn_forward once per
                                  token); a device status recorded by an earlier step stays until the caller reads it */
-  int32_t reserved[4];
+  int32_t probe_noop_cell;    /* MEASUREMENT HOOK, leave 0.  1: the time loops run with the gate arithmetic replaced by a
+                                 pass-through (same exchange, matrix products, barriers and copies): their duration is
+                                 the floor the serial chain of T dependent steps sets, which no cell math can undercut.
+                                 Results are meaningless.  Exists for the tiles of the benchmark configurations only
+                                 (lstm D=256, gru D=128, slstm D=192, 8-row batch tiles); elsewhere FRNN_ERR_PLAN.   */
+  int32_t reserved[3];
   uint64_t cache_bytes;     /* size of the activation cache (opaque layout, tied to this plan) */
   uint64_t workspace_bytes; /* size of the scratch workspace                                  */
   uint64_t grads_offset;    /* byte offset, inside the workspace, of the fp32 gradients dR || db */
@@ -100,11 +109,14 @@ typedef struct frnn_fwd_args {
   const void* b;       /* [Gt,N,D]     dtype_io                      */
   const void* s0;      /* [S,B,1,N,D]  dtype_state                   */
   void* states;        /* [S,B,T,N,D]  dtype_state (output)          */
-  void* cache;         /* cache_bytes, output; may be NULL when training == 0 */
+  void* cache;         /* cache_bytes, output; may be NULL when training == 0 or plan.cache_bytes == 0 */
   void* workspace;     /* workspace_bytes                            */
   void* last;          /* optional (NULL: off) [S,B,1,N,D] dtype_state (output): the states after step T-1 (one strided
                           device copy behind the time loop).  May be the very buffer `s0` points to: chunked or
                           token-by-token calls then carry their states in place                              */
+  int64_t wx_stride[4]; /* element strides of the B, T, G, N dimensions of Wx (the D dimension is contiguous).  All
+                           four 0: dense [B,T,Gw,N,D].  Each must be a non-negative multiple of 8 (16 bytes), else
+                           FRNN_ERR_ALIGN                                                                          */
 } frnn_fwd_args;
 
 /* Backward arguments.  Replaces FlashRNNFuncFused::backward(R_t, b, s, g_r, g_i, ds_new) ->
@@ -115,11 +127,13 @@ typedef struct frnn_bwd_args {
   const void* R;        /* [Gr,N,D,D]  dtype_io                                      */
   const void* s0;       /* [S,B,1,N,D] dtype_state                                   */
   const void* states;   /* [S,B,T,N,D] dtype_state, as written by frnn_forward       */
-  const void* cache;    /* as written by frnn_forward (training == 1)                */
+  const void* cache;    /* as written by frnn_forward (training == 1); may be NULL when plan.cache_bytes == 0 */
   const void* dstates;  /* [S,B,T,N,D] dtype_state: cotangent of `states`            */
   void* dWx;            /* [B,T,Gw,N,D] dtype_io (output)                            */
   void* ds0;            /* [S,B,1,N,D] dtype_state (output)                          */
   void* workspace;      /* workspace_bytes; holds fp32 dR || db on return            */
+  int64_t dstates_stride[4]; /* element strides of the S, B, T, N dimensions of dstates (D contiguous); all four 0:
+                                dense [S,B,T,N,D]; multiples of 8 as for wx_stride                                 */
 } frnn_bwd_args;
 
 /* One word of device-side status per workspace: 0 = clean. */
@@ -162,13 +176,19 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* args, void* 
  * library (a fixed arena handed out at start-up, a hot path on which cudaMalloc's device synchronisation is not
  * acceptable): the forward's scratch -- status block + R repacked into tensor-core fragments -- lives in a
  * file-scope device array of FRNN_NOALLOC_MAX_SCRATCH_BYTES inside the library, which every GPU that loads the
- * library holds until the process exits.  Nothing is allocated or freed, by the CUDA runtime or any other library.
+ * library holds until the process exits.  The entry point itself allocates and frees nothing, through the CUDA
+ * runtime or any other library; what happens once per device is the driver loading this library's device code, see
+ * "first call" below.
  *   - The plan is chosen as by frnn_query(problem).  Inputs, `states` and (training == 1) the activation `cache`
  *     of plan.cache_bytes (use frnn_query to size it) are still the caller's buffers.
  *   - Limit: 256 + Gr*N*D*D*2 bytes (rounded up to 256) must fit FRNN_NOALLOC_MAX_SCRATCH_BYTES, else
  *     FRNN_ERR_TOO_LARGE is returned and nothing is launched.
- *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
- *     current); make that first call before starting any stream capture.
+ *   - First call on a device: it looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current).  If nothing of the library has run on that device yet, this lookup makes the driver load the
+ *     library's device code, which is when the 8 MiB are set aside and which may synchronise the device.  Make that
+ *     first call at start-up, before any stream capture and before the latency-critical phase.  To prime a device
+ *     without launching work, call with a valid `problem` and an `args` whose tensor pointers are NULL: the address
+ *     is looked up, then the call returns FRNN_ERR_NULL and nothing is enqueued.
  *   - All calls on one device share the array.  It keeps the previous call's contents; each call clears the status
  *     block and rewrites the fragments before use.  Two calls whose GPU work overlaps (different streams, or
  *     different host threads without ordering) race on it: order them on one stream or with events.

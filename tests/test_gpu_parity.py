@@ -149,6 +149,63 @@ def test_alternative_user_layouts(cuda_device):
     assert_parity("lstm", got, oracle, tag="alternative layouts", zero_init=False)
 
 
+def test_strided_inputs_through_the_c_abi(cuda_device):
+    """Wx stored time-major and the cotangent stored state-time-batch-major reach the kernels through
+    frnn_fwd_args.wx_stride / frnn_bwd_args.dstates_stride (no dense copy) and give the oracle's numbers: the
+    cluster kernels (lstm) and the 128-row tensor-core loops (elman, with and without two-step copies)."""
+    import ctypes
+    from flashrnn_b200 import _native as nv
+
+    for function, (B, T, N, D), tile in (("lstm", (10, 7, 2, 128), 0), ("elman", (136, 6, 2, 64), 128), ("elman", (131, 5, 2, 64), 128)):
+        cpu = make_inputs(function, B, T, N, D, seed=31, random_init=True)
+        S = cpu[3].shape[0]
+        g = torch.Generator().manual_seed(5)
+        cot = torch.randn(S, B, T, N, D, generator=g, dtype=torch.float64).to(torch.bfloat16).to(torch.float64)
+        ref = run_oracle(function, *cpu, cot=cot)
+        Wx, R, b, s0 = (t.to("cuda", torch.bfloat16).contiguous() for t in cpu)
+        Wx_tm = Wx.permute(1, 0, 2, 3, 4).contiguous()                        # memory order [T,B,G,N,D]
+        cot_tm = cot.to("cuda", torch.bfloat16).permute(0, 2, 1, 3, 4).contiguous()  # memory order [S,T,B,N,D]
+        wx_view, ds_view = Wx_tm.permute(1, 0, 2, 3, 4), cot_tm.permute(0, 2, 1, 3, 4)
+        plan = nv.query(nv.make_problem(function, B, T, N, D, False, True), 0, tile)
+        states = torch.empty(S, B, T, N, D, device="cuda", dtype=torch.bfloat16)
+        cache = torch.empty(max(16, int(plan.cache_bytes)), device="cuda", dtype=torch.uint8)
+        ws = torch.empty(int(plan.workspace_bytes), device="cuda", dtype=torch.uint8)
+        dWx, ds0, dR, db = torch.empty_like(Wx), torch.empty_like(s0), torch.empty_like(R), torch.empty_like(b)
+        P = lambda t: ctypes.c_void_p(t.data_ptr())
+        strides = lambda t: (ctypes.c_int64 * 4)(*t.stride()[:4])
+        sp = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        L = nv.lib()
+        fa = nv.FrnnFwdArgs(P(wx_view), P(R), P(b), P(s0), P(states), P(cache), P(ws), None, strides(wx_view))
+        ba = nv.FrnnBwdArgs(P(R), P(s0), P(states), P(cache), P(ds_view), P(dWx), P(ds0), P(ws), strides(ds_view))
+        nv.check("fwd", L.frnn_forward(ctypes.byref(plan), ctypes.byref(fa), sp))
+        nv.check("bwd", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), sp))
+        off, cnt = int(plan.grads_offset), int(plan.grads_count)
+        nv.check("cast", L.frnn_finalize_grads(ctypes.byref(plan), P(ws[off:off + 4 * cnt]), P(dR), P(db), sp))
+        torch.cuda.synchronize()
+        f = lambda x: x.to(torch.float64).cpu().numpy()
+        got = dict(states=f(states), last=f(states[:, :, -1:]), dWx=f(dWx), dR=f(dR), db=f(db), ds0=f(ds0))
+        assert_parity(function, got, ref, tag=f"strided {function} B{B}", zero_init=False)
+
+
+def test_autocast_behaves_like_the_reference_decorators(cuda_device):
+    """Under torch.autocast float32 inputs are computed in the kernel dtype (what the reference's
+    custom_fwd(cast_inputs=...) does, flashrnn.py:690-695) and the gradients come back as float32."""
+    from flashrnn_b200 import flashrnn
+
+    cpu = make_inputs("lstm", 4, 6, 2, 64, seed=37)
+    a32 = [t.to("cuda", torch.float32).requires_grad_(True) for t in cpu[:3]]
+    a16 = [t.to("cuda", torch.bfloat16).requires_grad_(True) for t in cpu[:3]]
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        s32, _ = flashrnn(*a32, function="lstm")
+        s32[0].float().sum().backward()
+    # float32 Wx makes the states float32 (dtype_s follows dtype_w, as in the reference's config); same thing spelled out:
+    s16, _ = flashrnn(*a16, states=torch.zeros(2, 4, 1, 2, 64, device="cuda"), function="lstm")
+    s16[0].float().sum().backward()
+    assert s32.dtype == torch.float32 and torch.equal(s32, s16)
+    for x32, x16 in zip(a32, a16):
+        assert x32.grad.dtype == torch.float32 and torch.equal(x32.grad, x16.grad.float())
+
+
 def test_deterministic_forward(cuda_device):
     """Two runs give bit-identical states (no race in the h exchange)."""
     from flashrnn_b200 import flashrnn

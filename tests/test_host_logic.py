@@ -27,7 +27,8 @@ def test_struct_sizes_match_header():
     # int32 x 8 + float x 2; plan = 4 + 40 + 6*4 + 6*4 (reserved) padded to 8 + 4 * 8
     assert ctypes.sizeof(_native.FrnnProblem) == 44
     assert ctypes.sizeof(_native.FrnnPlan) == 128
-    assert ctypes.sizeof(_native.FrnnFwdArgs) == 8 * 8 and ctypes.sizeof(_native.FrnnBwdArgs) == 8 * 8
+    # 8 pointers + 4 int64 strides each
+    assert ctypes.sizeof(_native.FrnnFwdArgs) == 12 * 8 and ctypes.sizeof(_native.FrnnBwdArgs) == 12 * 8
 
 
 @pytest.mark.parametrize("function,B,T,N,D,f32", [
@@ -156,3 +157,107 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _native.lib()
+
+
+def _c_layout():
+    """sizeof / offsetof of the structs in include/frnn.h as the C compiler sees them."""
+    import subprocess
+    import tempfile
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    src = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "frnn.h"
+#define S(t) printf(#t " %zu\n", sizeof(t))
+#define O(t, f) printf(#t "." #f " %zu\n", offsetof(t, f))
+int main(void) {
+  S(frnn_problem); O(frnn_problem, grad_cut);
+  S(frnn_plan); O(frnn_plan, prob); O(frnn_plan, probe_noop_cell); O(frnn_plan, cache_bytes); O(frnn_plan, grads_count);
+  S(frnn_fwd_args); O(frnn_fwd_args, last); O(frnn_fwd_args, wx_stride);
+  S(frnn_bwd_args); O(frnn_bwd_args, workspace); O(frnn_bwd_args, dstates_stride);
+  S(frnn_dev_status);
+  printf("abi %d\n", FRNN_ABI_VERSION);
+  return 0;
+}'''
+    with tempfile.TemporaryDirectory() as d:
+        (Path(d) / "layout.c").write_text(src)
+        subprocess.run(["gcc", "-I", str(root / "include"), str(Path(d) / "layout.c"), "-o", str(Path(d) / "layout")], check=True)
+        out = subprocess.run([str(Path(d) / "layout")], check=True, capture_output=True, text=True).stdout
+    return {k: int(v) for k, v in (line.rsplit(" ", 1) for line in out.strip().splitlines())}
+
+
+def test_ctypes_structs_mirror_the_c_header():
+    c = _c_layout()
+    n = _native
+    assert c["abi"] == n.ABI_VERSION == n.lib().frnn_abi_version()
+    for cname, cls in (("frnn_problem", n.FrnnProblem), ("frnn_plan", n.FrnnPlan), ("frnn_fwd_args", n.FrnnFwdArgs),
+                       ("frnn_bwd_args", n.FrnnBwdArgs), ("frnn_dev_status", n.FrnnDevStatus)):
+        assert ctypes.sizeof(cls) == c[cname], cname
+    assert n.FrnnProblem.grad_cut.offset == c["frnn_problem.grad_cut"]
+    assert n.FrnnPlan.prob.offset == c["frnn_plan.prob"]
+    assert n.FrnnPlan.probe_noop_cell.offset == c["frnn_plan.probe_noop_cell"]
+    assert n.FrnnPlan.cache_bytes.offset == c["frnn_plan.cache_bytes"]
+    assert n.FrnnPlan.grads_count.offset == c["frnn_plan.grads_count"]
+    assert n.FrnnFwdArgs.last.offset == c["frnn_fwd_args.last"]
+    assert n.FrnnFwdArgs.wx_stride.offset == c["frnn_fwd_args.wx_stride"]
+    assert n.FrnnBwdArgs.dstates_stride.offset == c["frnn_bwd_args.dstates_stride"]
+
+
+def test_integration_stub_structs_have_the_header_sizes():
+    """The binding INTEGRATION.md shows a maintainer (its ``class Problem`` ... lines) must describe the same bytes."""
+    import re
+    from pathlib import Path
+
+    text = (Path(__file__).resolve().parent.parent / "INTEGRATION.md").read_text()
+    block = re.search(r"    import ctypes, torch\n(.*?)\n\n", text, re.S)
+    assert block, "stub not found in INTEGRATION.md"
+    code = "import ctypes\n" + "\n".join(l[4:] for l in block.group(1).splitlines() if not l.strip().startswith("L ="))
+    ns = {}
+    exec(code, ns)
+    c = _c_layout()
+    assert ctypes.sizeof(ns["Problem"]) == c["frnn_problem"] == ctypes.sizeof(_native.FrnnProblem)
+    assert ctypes.sizeof(ns["Plan"]) == c["frnn_plan"]
+    assert ctypes.sizeof(ns["FwdArgs"]) == c["frnn_fwd_args"]
+    assert ctypes.sizeof(ns["BwdArgs"]) == c["frnn_bwd_args"]
+
+
+def test_strided_views_are_passed_through_and_everything_else_is_densified():
+    ks = _native.kernel_strides
+    x = torch.zeros(6, 4, 3, 2, 64, dtype=torch.bfloat16)          # stored as [T,B,G,N,D]
+    v = x.permute(1, 0, 2, 3, 4)                                    # seen as [B,T,G,N,D]
+    t, st = ks(v, torch.bfloat16)
+    assert t.data_ptr() == x.data_ptr() and tuple(st) == (3 * 2 * 64, 4 * 3 * 2 * 64, 2 * 64, 64)
+    t, st = ks(v.contiguous(), torch.bfloat16)
+    assert tuple(st) == (0, 0, 0, 0)
+    t, st = ks(v.float(), torch.bfloat16)                           # wrong dtype: cast + dense
+    assert t.dtype == torch.bfloat16 and t.is_contiguous() and tuple(st) == (0, 0, 0, 0)
+    odd = torch.zeros(4, 6, 3, 2, 36, dtype=torch.bfloat16)[..., :32]  # strides not multiples of 8 elements
+    t, st = ks(odd, torch.bfloat16)
+    assert t.is_contiguous() and tuple(st) == (0, 0, 0, 0)
+    t, st = ks(torch.zeros(1).to(torch.bfloat16).expand(4, 6, 3, 2, 64), torch.bfloat16)  # broadcast: last stride 0
+    assert t.is_contiguous() and tuple(st) == (0, 0, 0, 0)
+
+
+def test_stride_validation_happens_before_any_launch():
+    L = _native.lib()
+    plan = _native.query(_native.make_problem("elman", 2, 3, 1, 32, False, True))
+    args = _native.FrnnFwdArgs()
+    for name in ("Wx", "R", "b", "s0", "states", "cache", "workspace"):
+        setattr(args, name, 4096)
+    args.wx_stride[0] = 100  # not a multiple of 8 elements
+    assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) == -5
+    args.wx_stride[0] = -64
+    assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) == -5
+
+
+def test_floor_probe_exists_for_the_benchmark_tiles_only():
+    """probe_noop_cell is a measurement hook of three tiles; any other plan refuses it before launching."""
+    L = _native.lib()
+    plan = _native.query(_native.make_problem("elman", 2, 3, 1, 32, False, True))
+    plan.probe_noop_cell = 1
+    args = _native.FrnnFwdArgs()
+    for name in ("Wx", "R", "b", "s0", "states", "cache", "workspace"):
+        setattr(args, name, 4096)
+    assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) != 0
