@@ -52,7 +52,12 @@ NCU_TRAFFIC = {"C2": {"bytes": 237_129_984 + 105_455_360, "source": "ncu --set f
                       "2026-11-25 (the loop's data movement has not changed since)"}}
 # fwd+bwd of the reference's own CUDA backend on a B200 of this pool, measured by `bench.py --impl reference_gpu`
 # (tokens/s; None: not measured).  The live arm is the source of truth; this record lets the default line carry the ratio.
-REFERENCE_GPU_RECORD = {}
+REFERENCE_GPU_RECORD = {
+    "C2": {"value": 1549168.3, "unit": "tokens/s", "ms_per_step": 10.576,
+           "source": "`bench.py --impl reference_gpu --steps 10` on a B200 of this pool, 2026-11-25: the reference's cuda_fused backend "
+                     "(unmodified, baseline/_ref, its own JIT build and tiling search), bf16, same seeded inputs, median of 5 blocks of "
+                     "10 steps, CUDA events, SM clock 1965 MHz, no throttle reason"},
+}
 
 
 def measured_peaks():
@@ -402,7 +407,8 @@ def measure(job: Job, function, B, T, N, D, f32, *, allreduce, group=True, clust
     if floor and not wide:
         probe = nv.FrnnPlan.from_buffer_copy(plan)
         probe.probe_noop_cell = 1
-        if L.frnn_forward(ctypes.byref(probe), ctypes.byref(fa), sp) == 0:
+        if (L.frnn_forward(ctypes.byref(probe), ctypes.byref(fa), sp) == 0 and
+                L.frnn_backward_parts(ctypes.byref(probe), ctypes.byref(ba), sp, 1) == 0):  # else: no probe for this tile
             k = max(5, args.steps)
             ef = [ev() for _ in range(3)]
             for _ in range(2):

@@ -96,7 +96,8 @@ static bool tile_ok(const frnn_problem& pr, const CellDims& cd, int cs, int bt) 
   const int D = pr.D;
   if (bt == kWideBatchTile) return cs == 1 && wide_problem(pr);  // 128-row tensor-core loops: one CTA per head and tile
   if (cs < 1 || D % cs) return false;
-  if (streamed(pr) ? (cs > 16 || D / cs != kStreamU) : cs > 8) return false;
+  // clusters above 8 CTAs (a non-portable size): the streamed kernels, and 16 CTAs of 16 units for head dim 256
+  if (streamed(pr) ? (cs > 16 || D / cs != kStreamU) : (cs > 8 && !(cs == 16 && D == 256))) return false;
   const int U = D / cs;
   if (U % 16 || ((U / 16) & (U / 16 - 1))) return false;  // 16 * power of two
   if (bt != 8 && bt != 16 && bt != 32) return false;

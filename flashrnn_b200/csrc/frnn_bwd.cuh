@@ -104,7 +104,7 @@ template <int CELL, int KT, int MPW> struct RsGeom {
   static constexpr int U = NUT * 16;
   static constexpr int CS = MPW * Cell<CELL>::Gr;
   static constexpr bool valid = MPW > 0 && KT % MPW == 0 && KPW % Cell<CELL>::Gr == 0 && NUT >= 1 &&
-                                (NUT & (NUT - 1)) == 0 && CS <= 8 && CS * U == KT * 16;
+                                (NUT & (NUT - 1)) == 0 && CS <= 16 && CS * U == KT * 16;
 };
 
 template <int CELL, int NT, int MPW>

@@ -44,6 +44,17 @@ def test_parity_every_cluster_size(cuda_device, function, cs, bt):
 
 
 @pytest.mark.parametrize("function", CELLS)
+def test_parity_16_cta_cluster(cuda_device, function):
+    """Head dim 256 spread over 16 CTAs of 16 units (a non-portable cluster size; reduce-scatter backward for the
+    four-gate cells)."""
+    B, T, N, D = 12, 10, 2, 256
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=43, random_init=True)
+    got = run_native(function, Wx, R, b, s0, cluster_size=16, batch_tile=8)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=f"{function} cs16", zero_init=False)
+
+
+@pytest.mark.parametrize("function", CELLS)
 def test_parity_random_cotangent_and_initial_state(cuda_device, function):
     """Random cotangent on the states (h only for sLSTM, as the reference's tests do) + random initial states."""
     B, T, N, D = 6, 9, 2, 64
