@@ -43,6 +43,19 @@ def test_parity_every_cluster_size(cuda_device, function, cs, bt):
     assert_parity(function, got, ref, tag=f"{function} cs{cs} bt{bt}", zero_init=False)
 
 
+@pytest.mark.parametrize("function", ["lstm", "gru", "slstm"])
+@pytest.mark.parametrize("D,T,state_f32", [(128, 1, False), (128, 2, True), (192, 3, False), (192, 9, True), (256, 8, False),
+                                           (256, 11, True)])
+def test_parity_32_unit_tiles(cuda_device, function, D, T, state_f32):
+    """The tile of the benchmark configurations (32 units per CTA, 8-row batch tiles, clusters of 4 / 6 / 8) with odd and
+    even sequence lengths, a ragged batch, two batch tiles per head and 16-bit or fp32 states."""
+    B, N, cs = 11, 2, D // 32
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=47 + T, random_init=(function != "slstm"), state_f32=state_f32)
+    got = run_native(function, Wx, R, b, s0, state_f32=state_f32, cluster_size=cs, batch_tile=8)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=f"{function} D{D} T{T}", zero_init=(function == "slstm"))
+
+
 @pytest.mark.parametrize("function", CELLS)
 def test_parity_16_cta_cluster(cuda_device, function):
     """Head dim 256 spread over 16 CTAs of 16 units (a non-portable cluster size; reduce-scatter backward for the
