@@ -136,9 +136,17 @@ static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs,
     // clusters of 8 = 256 CTAs on 148 SMs 3.64 ms, clusters of 4 = 128 CTAs 3.05 ms, clusters of 2 3.53 ms); the
     // second pass takes whatever exists.
     const int sms = sm_count_cached();
+    // ... but never below 32 units per CTA while that tile exists: 16-unit CTAs (3-4 warps each) lose more in the
+    // exchange than they gain in the matrix phase (GRU head dim 128, 16 pairs: clusters of 8 x 16 units 3.54 ms, clusters
+    // of 4 x 32 units 3.03 ms; LSTM head dim 256: 16 x 16 units 1.07 ms per forward loop against 0.78 ms for 8 x 32)
+    // Head dims up to 64 do best with the whole head in one CTA, no exchange at all (LSTM D=64, 2 pairs: fwd + bwd loops
+    // 0.33 ms against 0.35 / 0.36 ms for clusters of 2 / 4; Elman D=64: 0.46 against 0.65 / 0.81 ms).
+    const int cs32 = pr.D <= 64 ? 1 : ((pr.D % 32 == 0 && pr.D / 32 <= 8) ? pr.D / 32 : 0);
     for (int pass = 0; pass < 2; ++pass)
-      for (int ci = 0; ci < 8; ++ci) {
-        int cs = want_cs ? want_cs : (fill ? order_large[ci] : order_small[ci]);
+      for (int ci = -1; ci < 8; ++ci) {
+        if (ci < 0 && (fill || want_cs || streamed(pr) || !cs32)) continue;
+        int cs = ci < 0 ? cs32 : (want_cs ? want_cs : (fill ? order_large[ci] : order_small[ci]));
+        if (ci >= 0 && !fill && !want_cs && cs32 && cs > cs32) continue;  // fewer than 32 units per CTA
         if (streamed(pr) && !want_cs) cs = pr.D / kStreamU;  // the streamed kernels have one geometry
         const bool crowded = !fill && !want_cs && !streamed(pr) && pairs * cs > sms;
         if (!(pass == 0 && crowded) && tile_ok(pr, cd, cs, bt)) { *cs_out = cs; *bt_out = bt; return true; }

@@ -41,8 +41,10 @@ def main():
         st_l[0].float().sum().backward()
         hi = lo + Wx_l.shape[0]
         assert torch.equal(st_l, st_full[:, lo:hi]), (function, "states rows")
-        assert torch.equal(loc[0].grad, full[0].grad[lo:hi]), (function, "dWx rows")
-        assert torch.equal(loc[3].grad, full[3].grad[:, lo:hi]), (function, "ds0 rows")
+        # a shard may run with another cluster size than the whole batch (the tile table looks at the number of batch
+        # tiles), which changes the order of the fp32 sums behind dh: equal to rounding, not to the bit
+        assert rel_l2(f(loc[0].grad), f(full[0].grad[lo:hi])) <= 0.5 * GRAD_REL_L2, (function, "dWx rows")
+        assert rel_l2(f(loc[3].grad), f(full[3].grad[:, lo:hi])) <= 0.5 * GRAD_REL_L2, (function, "ds0 rows")
         ref = run_oracle(function, *cpu)
         for name, got, one in (("dR", loc[1].grad, full[1].grad), ("db", loc[2].grad, full[2].grad)):
             assert rel_l2(f(got), f(one)) <= GRAD_REL_L2, (function, name, "vs single GPU", rel_l2(f(got), f(one)))
