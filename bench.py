@@ -48,8 +48,8 @@ DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm
 METRIC = "fwd+bwd tokens/sec (B*T/s)"
 # DRAM bytes (read + write) of ONE launch of the reverse time loop, from an `ncu --set full` capture of
 # `python bench.py --steps 2 --warmup 1 --no-cpu` on a B200; reported with its provenance, for the kernel build named.
-NCU_TRAFFIC = {"C2": {"bytes": 237_129_984 + 105_455_360, "source": "ncu --set full capture of frnn_bwd_kernel<lstm,KT16,NT1,MPW2>, "
-                      "2026-11-25 (the loop's data movement has not changed since)"}}
+NCU_TRAFFIC = {"C2": {"bytes": 237_750_016 + 105_541_632, "source": "ncu --set full capture of frnn_bwd_kernel<lstm,KT16,NT1,MPW2> on this "
+                      "command line with --steps 1 --min-seconds 0, 2026-11-25 (the kernel has not changed since)"}}
 # fwd+bwd of the reference's own CUDA backend on a B200 of this pool, measured by `bench.py --impl reference_gpu`
 # (tokens/s; None: not measured).  The live arm is the source of truth; this record lets the default line carry the ratio.
 REFERENCE_GPU_RECORD = {
@@ -328,11 +328,12 @@ class Job:
 
 
 def measure(job: Job, function, B, T, N, D, f32, *, allreduce, group=True, cluster_size=0, batch_tile=0, floor=True,
-            min_seconds=0.5, keep=None):
+            min_seconds=None, keep=None):
     """The C-ABI step (forward, reverse loop, dR, [all-reduce,] cast) of one workload on resident buffers.
     ``group``: the ranks run it together (barriers, max over ranks); False: this rank alone.  Returns a dict of timings;
     ``keep`` (a dict) receives the tensors for a caller that goes on to use them."""
     nv, L, dev, stream, sp, args = job.nv, job.L, job.dev, job.stream, job.sp, job.args
+    min_seconds = args.min_seconds if min_seconds is None else min_seconds
     Gr, Gw, Gt, S = DIMS[function]
     Wx, R, b, s0 = make_inputs(function, B, T, N, D, f32, dev, seed=job.rank, edt=job.edt)
     sdt = torch.float32 if f32 else job.edt
@@ -664,6 +665,9 @@ def main():
                     help="N > 1 GPUs: batch shards (weak scaling, default) or head shards of one workload (strong scaling)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--headline-only", action="store_true", help="skip the `workloads` object (the other configurations)")
+    ap.add_argument("--min-seconds", dest="min_seconds", type=float, default=0.5,
+                    help="length of the timed region per workload (blocks of --steps steps are repeated until it is reached; "
+                         "0 = three blocks, for runs under a profiler)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16"],
                     help="16-bit element type of Wx/R/b/gradients (the baseline metric is quoted in bfloat16)")
     args = ap.parse_args()
