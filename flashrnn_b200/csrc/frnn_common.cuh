@@ -250,7 +250,10 @@ __device__ __forceinline__ void store_state2(void* base, size_t elem_off, int f3
 template <int KT, int NT>
 __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const elem_t* opnd, int stride, int kofs,
                                               int ushift, int slice_elems, int lane, float (&out)[NT][4]) {
-  constexpr int NACC = (NT >= 4) ? 1 : (4 / NT);
+  // independent accumulator sets: 4 chains, 8 for the longest rows (16 k-steps: C2 forward loop 0.780 -> 0.764 ms; with
+  // 8 or 12 k-steps the extra additions cost more than the shorter chains save)
+  constexpr int NSETS = (KT >= 16) ? 8 : 4;
+  constexpr int NACC = (NT >= NSETS) ? 1 : (NSETS / NT);
   float acc[NACC][NT][4];
 #pragma unroll
   for (int a = 0; a < NACC; ++a)
@@ -398,7 +401,7 @@ __host__ __device__ constexpr int ring_row_len(int U, int BT, int threads) {
   return (U / 2) * BT < threads ? (U / 2) * BT : threads;
 }
 
-template <int KT> struct MaxThreads { static constexpr int v = (KT >= 12) ? 384 : 512; };
+template <int KT> struct MaxThreads { static constexpr int v = (KT >= 16) ? 256 : (KT >= 12) ? 384 : 512; };
 // Launch bounds per (cell, KT): a CTA never has more than 2*Gr*D threads (U <= D).  No minimum-blocks hint: capping
 // the registers of the small-head kernels to raise occupancy (6 instead of 4 CTAs per SM) made the Elman D=64
 // backward 70 % slower on B200 (measured), so the compiler is left free.
