@@ -43,6 +43,7 @@ WORKLOADS = {
     "C4": ("slstm", 8, 4096, 4, 192, True),
     "C5": ("elman", 1024, 2048, 16, 64, False),
     "C5s": ("elman", 1024, 256, 16, 64, False),  # C5 with T cut to 256 (2.1 GB resident): the size ncu captures use
+    "LB": ("lstm", 1024, 512, 16, 64, False),    # large-batch LSTM (the reference's batch-size sweeps): 16-row tiles, HBM-side regime
 }
 DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm": (4, 4, 4, 4)}
 METRIC = "fwd+bwd tokens/sec (B*T/s)"
@@ -563,7 +564,7 @@ def run_ours(args):
             return {"value": tokens_per_s(Bw, Tw, ranks, m["ms_per_step"]), "unit": "tokens/s", **more, **m}
 
         if world == 1:
-            for name in ("C3", "C4", "C5"):
+            for name in ("C3", "C4", "C5", "LB"):
                 if name == args.workload:
                     continue
                 fn, Bw, Tw, Nw, Dw, f32w = WORKLOADS[name]

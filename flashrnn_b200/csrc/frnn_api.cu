@@ -123,8 +123,13 @@ static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs,
     *bt_out = kWideBatchTile;
     return true;
   }
-  // measured on B200: otherwise 8-row batch tiles win for every benchmark configuration (more CTAs, shorter steps)
-  const int bt_pref[3] = {8, 16, 32};
+  // Measured on B200.  Small batches (fewer than 128 (head, batch tile) pairs; every benchmark configuration but the large
+  // Elman one): 8-row batch tiles -- more CTAs, shorter steps; 16-row tiles double the step time of the serial chain.
+  // Large batches of the cells with three or four gates: 16-row tiles, whose CTAs reuse every fragment of R for two
+  // 8-row MMA columns (LSTM B1024 N16 D64: 55 -> 72 M tokens/s through the two loops; GRU 64 -> 75; sLSTM 82 -> 96; LSTM
+  // B512 N8 D128 37 -> 48; 32-row tiles spill in the reverse loop and lose).  Elman keeps 8 rows (D=128: 100 against 72).
+  const bool rows16 = cd.Gr >= 3 && (long long)((pr.B + 15) / 16) * pr.N >= 128;
+  const int bt_pref[3] = {rows16 ? 16 : 8, rows16 ? 8 : 16, 32};
   for (int bi = 0; bi < 3; ++bi) {
     const int bt = want_bt ? want_bt : bt_pref[bi];
     const long long pairs = (long long)((pr.B + bt - 1) / bt) * pr.N;
@@ -132,19 +137,23 @@ static bool choose_tile(const frnn_problem& pr, const CellDims& cd, int want_cs,
     // power-of-two cluster sizes first, then the others
     const int order_small[8] = {8, 4, 2, 1, 6, 3, 7, 5};
     const int order_large[8] = {1, 2, 4, 8, 3, 6, 5, 7};
-    // Small batches: the largest cluster whose CTAs all get an SM of their own (measured on C3, 32 (head, tile) pairs:
-    // clusters of 8 = 256 CTAs on 148 SMs 3.64 ms, clusters of 4 = 128 CTAs 3.05 ms, clusters of 2 3.53 ms); the
-    // second pass takes whatever exists.
     const int sms = sm_count_cached();
-    // ... but never below 32 units per CTA while that tile exists: 16-unit CTAs (3-4 warps each) lose more in the
-    // exchange than they gain in the matrix phase (GRU head dim 128, 16 pairs: clusters of 8 x 16 units 3.54 ms, clusters
-    // of 4 x 32 units 3.03 ms; LSTM head dim 256: 16 x 16 units 1.07 ms per forward loop against 0.78 ms for 8 x 32)
-    // Head dims up to 64 do best with the whole head in one CTA, no exchange at all (LSTM D=64, 2 pairs: fwd + bwd loops
-    // 0.33 ms against 0.35 / 0.36 ms for clusters of 2 / 4; Elman D=64: 0.46 against 0.65 / 0.81 ms).
+    // The preferred cluster, small batch or large: 32 units per CTA from head dim 128 (clusters of D/32), the whole head in
+    // one CTA up to head dim 64.  16-unit CTAs (3-4 warps each) lose more in the exchange than they gain in the matrix
+    // phase (GRU head dim 128, 16 pairs: clusters of 8 x 16 units 3.54 ms, 4 x 32 units 3.03 ms, 2 x 64 3.37 ms; LSTM head dim
+    // 256: 16 x 16 units 1.07 ms per forward loop against 0.78 ms for 8 x 32; large batch LSTM D=128: 4 x 32 units 48, 2 x 64
+    // units 41 M tokens/s); up to head dim 64 one CTA per head, no exchange at all, wins (LSTM D=64, 2 pairs: fwd + bwd
+    // loops 0.33 ms against 0.35 / 0.36 ms for clusters of 2 / 4; Elman D=64: 0.46 against 0.65 / 0.81 ms; large batch LSTM
+    // D=64: 72 against 66 M tokens/s).
+    // Small batches fall back to smaller clusters when the preferred one would not give every CTA an SM of its own
+    // (C3 with clusters of 8: 256 CTAs on 148 SMs 3.64 ms, clusters of 4: 128 CTAs 3.05 ms); the second pass takes
+    // whatever exists.
     const int cs32 = pr.D <= 64 ? 1 : ((pr.D % 32 == 0 && pr.D / 32 <= 8) ? pr.D / 32 : 0);
     for (int pass = 0; pass < 2; ++pass)
       for (int ci = -1; ci < 8; ++ci) {
-        if (ci < 0 && (fill || want_cs || streamed(pr) || !cs32)) continue;
+        // (large batches of the single-gate cell do best without any cluster: Elman B1024 D=128, one CTA per head 100 M
+        // tokens/s, clusters of 2 x 64 units 70)
+        if (ci < 0 && (want_cs || streamed(pr) || !cs32 || (fill && cd.Gr < 3))) continue;
         int cs = ci < 0 ? cs32 : (want_cs ? want_cs : (fill ? order_large[ci] : order_small[ci]));
         if (ci >= 0 && !fill && !want_cs && cs32 && cs > cs32) continue;  // fewer than 32 units per CTA
         if (streamed(pr) && !want_cs) cs = pr.D / kStreamU;  // the streamed kernels have one geometry

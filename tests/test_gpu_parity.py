@@ -56,6 +56,21 @@ def test_parity_32_unit_tiles(cuda_device, function, D, T, state_f32):
     assert_parity(function, got, ref, tag=f"{function} D{D} T{T}", zero_init=(function == "slstm"))
 
 
+@pytest.mark.parametrize("function,D", [("lstm", 64), ("gru", 64), ("slstm", 64), ("lstm", 128)])
+def test_parity_large_batch_16_row_tiles(cuda_device, function, D):
+    """Enough (head, batch tile) pairs to fill the GPU: the table switches the cells with three or four gates to 16-row
+    batch tiles (one CTA per head up to head dim 64, clusters of 32-unit CTAs above)."""
+    from flashrnn_b200 import _native
+
+    B, T, N = 168, 5, 13  # ragged: 10.5 tiles of 16 rows
+    plan = _native.query(_native.make_problem(function, B, T, N, D, False, True))
+    assert plan.batch_tile == 16 and plan.units_per_cta == (64 if D == 64 else 32)
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=53, random_init=(function != "slstm"))
+    got = run_native(function, Wx, R, b, s0)
+    ref = run_oracle(function, Wx, R, b, s0)
+    assert_parity(function, got, ref, tag=f"{function} D{D} large batch", zero_init=(function == "slstm"))
+
+
 @pytest.mark.parametrize("function", CELLS)
 def test_parity_16_cta_cluster(cuda_device, function):
     """Head dim 256 spread over 16 CTAs of 16 units (a non-portable cluster size; reduce-scatter backward for the

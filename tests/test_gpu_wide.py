@@ -41,6 +41,6 @@ def test_wide_is_the_default_for_large_batches():
     assert (big.batch_tile, big.cluster_size, big.threads) == (128, 1, 160)
     small = nv.query(nv.make_problem("elman", 64, 16, 16, 64, False, True))
     assert small.batch_tile == 8
-    # cells / options the 128-row loops do not cover keep the small tiles
-    assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True)).batch_tile == 8
+    # cells / options the 128-row loops do not cover keep the warp-MMA loops (16-row tiles for large multi-gate batches)
+    assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True)).batch_tile == 16
     assert nv.query(nv.make_problem("elman", 1024, 16, 16, 64, True, True)).batch_tile == 8
