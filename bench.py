@@ -241,8 +241,8 @@ def run_reference_gpu(args):
     if not (ref_root / "flashrnn").exists():
         print(json.dumps({**base, "unavailable": "baseline/_ref holds no reference install"}), flush=True)
         return 0
-    os.environ.setdefault("TORCH_EXTENSIONS_DIR", str(ROOT / "gpurun_out" / "ref_ext"))
-    os.environ.setdefault("CONSTRINT_CACHE_DIR", str(ROOT / "gpurun_out" / "ref_ext" / "constrint"))
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", str(ROOT / "baseline" / "_ref_ext"))  # the reference's JIT builds land here
+    os.environ.setdefault("CONSTRINT_CACHE_DIR", str(ROOT / "baseline" / "_ref_ext" / "constrint"))
     Path(os.environ["TORCH_EXTENSIONS_DIR"]).mkdir(parents=True, exist_ok=True)
     t_start = time.time()
     try:
