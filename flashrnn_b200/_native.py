@@ -129,11 +129,13 @@ def check(what: str, code: int) -> None:
 
 def make_problem(function: str, B: int, T: int, N: int, D: int, state_f32: bool, training: bool,
                  forward_clip: float | None = None, grad_clip: float | None = None, grad_cut: bool = False,
-                 f16: bool = False) -> FrnnProblem:
-    """``f16``: Wx, R, b, the gradients and (unless ``state_f32``) the states are float16 instead of bfloat16."""
+                 f16: bool = False, f32: bool = False) -> FrnnProblem:
+    """``f16``: Wx, R, b, the gradients and (unless ``state_f32``) the states are float16 instead of bfloat16.
+    ``f32``: everything, states included, is float32 (the float32 loops)."""
     if function not in CELL_IDS:
         raise AssertionError(f"RNN function {function} not in registry")
-    io = DTYPE_F16 if f16 else DTYPE_BF16
+    io = DTYPE_F32 if f32 else (DTYPE_F16 if f16 else DTYPE_BF16)
+    state_f32 = state_f32 or f32
     return FrnnProblem(CELL_IDS[function], B, T, N, D, io, DTYPE_F32 if state_f32 else io,
                        1 if training else 0, float(forward_clip or 0.0), float(grad_clip or 0.0), 1 if grad_cut else 0)
 

@@ -299,6 +299,21 @@ int frnn_backward_parts_f16(const frnn_plan*, const frnn_bwd_args*, void*, int);
 int frnn_finalize_grads_f16(const frnn_plan*, const void*, void*, void*, void*);
 }
 #endif
+// float32 problems (Wx, R, b, states and gradients all fp32) go to the float32 loops of frnn_f32.cu
+#ifdef FRNN_F16
+#define FRNN_FORWARD_F32(is_f32, call)
+#else
+#define FRNN_FORWARD_F32(is_f32, call) \
+  if (is_f32) return call
+extern "C" {
+int frnn_query_f32(const frnn_problem*, int, int, int, frnn_plan*);
+int frnn_forward_f32(const frnn_plan*, const frnn_fwd_args*, void*);
+int frnn_backward_parts_f32(const frnn_plan*, const frnn_bwd_args*, void*, int);
+int frnn_finalize_grads_f32(const frnn_plan*, const void*, void*, void*, void*);
+}
+#endif
+static inline bool wants_f32(const frnn_problem* pr) { return pr && pr->dtype_io == FRNN_DTYPE_F32; }
+static inline bool wants_f32(const frnn_plan* pl) { return pl && pl->prob.dtype_io == FRNN_DTYPE_F32; }
 static inline bool wants_f16(const frnn_problem* pr) { return pr && pr->dtype_io == FRNN_DTYPE_F16; }
 static inline bool wants_f16(const frnn_plan* pl) { return pl && pl->prob.dtype_io == FRNN_DTYPE_F16; }
 
@@ -309,16 +324,19 @@ int frnn_abi_version(void) { return FRNN_ABI_VERSION; }
 #endif
 
 int FRNN_ENTRY(frnn_query)(const frnn_problem* problem, frnn_plan* out) {
+  FRNN_FORWARD_F32(wants_f32(problem), frnn_query_f32(problem, 0, 0, 0, out));
   FRNN_FORWARD_F16(wants_f16(problem), frnn_query_f16(problem, out));
   return fill_plan(problem, 0, 0, 0, out);
 }
 
 int FRNN_ENTRY(frnn_query_tile)(const frnn_problem* problem, int cluster_size, int batch_tile, int wx_stages, frnn_plan* out) {
+  FRNN_FORWARD_F32(wants_f32(problem), frnn_query_f32(problem, cluster_size, batch_tile, wx_stages, out));
   FRNN_FORWARD_F16(wants_f16(problem), frnn_query_tile_f16(problem, cluster_size, batch_tile, wx_stages, out));
   return fill_plan(problem, cluster_size, batch_tile, wx_stages, out);
 }
 
 int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
+  FRNN_FORWARD_F32(wants_f32(plan), frnn_forward_f32(plan, a, stream_));
   FRNN_FORWARD_F16(wants_f16(plan), frnn_forward_f16(plan, a, stream_));
   CellDims cd;
   int rc = check_plan(plan, &cd);
@@ -387,6 +405,7 @@ int frnn_backward(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_) 
 #endif
 
 int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_, int parts) {
+  FRNN_FORWARD_F32(wants_f32(plan), frnn_backward_parts_f32(plan, a, stream_, parts));
   FRNN_FORWARD_F16(wants_f16(plan), frnn_backward_parts_f16(plan, a, stream_, parts));
   CellDims cd;
   int rc = check_plan(plan, &cd);
@@ -468,6 +487,7 @@ int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* 
 }
 
 int FRNN_ENTRY(frnn_finalize_grads)(const frnn_plan* plan, const void* grads_f32, void* dR, void* db, void* stream_) {
+  FRNN_FORWARD_F32(wants_f32(plan), frnn_finalize_grads_f32(plan, grads_f32, dR, db, stream_));
   FRNN_FORWARD_F16(wants_f16(plan), frnn_finalize_grads_f16(plan, grads_f32, dR, db, stream_));
   CellDims cd;
   int rc = check_plan(plan, &cd);
@@ -492,8 +512,8 @@ const char* frnn_status_string(int code) {
     case FRNN_OK: return "ok";
     case FRNN_ERR_NULL: return "frnn: a required pointer is NULL";
     case FRNN_ERR_CELL: return "frnn: unknown cell (expected lstm, gru, elman or slstm)";
-    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256} or a multiple of 64 up to 1024)";
-    case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b bfloat16 or float16; states of the same type or float32)";
+    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256} or a multiple of 64 up to 1024; float32: a multiple of 4 up to 1024)";
+    case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b bfloat16 or float16 with states of the same type or float32; or everything float32)";
     case FRNN_ERR_ALIGN: return "frnn: tensor pointers must be 16-byte aligned";
     case FRNN_ERR_PLAN: return "frnn: invalid plan or tile for this problem";
     case FRNN_ERR_TRAINING: return "frnn: backward needs a plan made with training = 1";

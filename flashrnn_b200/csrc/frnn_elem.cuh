@@ -8,7 +8,9 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
-#ifdef FRNN_F16
+#if defined(FRNN_NS_OVERRIDE)
+#define FRNN_NS FRNN_NS_OVERRIDE  // a translation unit that instantiates the shared templates with other compile options
+#elif defined(FRNN_F16)
 #define FRNN_NS frnn_f16
 #else
 #define FRNN_NS frnn

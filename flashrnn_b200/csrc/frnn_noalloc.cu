@@ -49,10 +49,10 @@ extern "C" int frnn_forward_noalloc(const frnn_problem* problem, const frnn_fwd_
   frnn_plan plan;
   const int rc = frnn_query(problem, &plan);
   if (rc != FRNN_OK) return rc;
-  // what the forward touches of a workspace: the 256-byte status block followed by R as fragments (16-bit elements, same
-  // size as R).  Gate count of R: 4 (lstm, slstm), 3 (gru), 1 (elman).
+  // what the forward touches of a workspace: the 256-byte status block followed by R repacked (same size as R).  Gate count of R: 4 (lstm, slstm), 3 (gru), 1 (elman).
   const size_t gr = problem->cell == FRNN_CELL_GRU ? 3 : (problem->cell == FRNN_CELL_ELMAN ? 1 : 4);
-  const size_t need = 256 + align_up(gr * (size_t)problem->N * problem->D * problem->D * 2, 256);
+  const size_t esz = problem->dtype_io == FRNN_DTYPE_F32 ? 4 : 2;  // float32 problems keep a transposed fp32 copy of R there
+  const size_t need = 256 + align_up(gr * (size_t)problem->N * problem->D * problem->D * esz, 256);
   if (need > (size_t)FRNN_NOALLOC_MAX_SCRATCH_BYTES) return FRNN_ERR_TOO_LARGE;
   unsigned char* scratch = nullptr;
   const int sc = scratch_for_current_device(&scratch);

@@ -15,8 +15,10 @@ reference (flashrnn/flashrnn/flashrnn.py:124-207, 1093-1135).  What changed on p
 * GRU runs fused (the reference silently switches it to the alternating backend, flashrnn.py:280-284);
 * states may be kept in float32 while Wx/R/b are bfloat16 / float16 (``dtype_s="float32"`` or by passing float32
   ``states``), which the reference's fused kernel cannot express;
-* ``dtype`` is ``"bfloat16"`` or ``"float16"`` (the MMA operand type); accumulation and gate math are fp32 for both
-  (the reference accumulates float16 in float16, fused/flashrnn_fused_forward.cu), ``"float32"`` raises.
+* ``dtype`` is ``"bfloat16"`` or ``"float16"`` (the MMA operand type; accumulation and gate math are fp32 for both,
+  where the reference accumulates float16 in float16, fused/flashrnn_fused_forward.cu), or ``"float32"``: everything in
+  fp32 on the CUDA cores -- accurate to ~1e-5 against the fp32 ``vanilla`` loop (the reference multiplies in tf32
+  there, fused/flashrnn_fused_forward.cu:108-112), an order of magnitude slower than the 16-bit tensor-core loops.
 """
 from __future__ import annotations
 
@@ -187,7 +189,7 @@ class _FrnnFunction(torch.autograd.Function):
         s0_k = s0.to(state_dtype).contiguous()
         prob = _native.make_problem(cfg.function, B, T, N, D, state_dtype == torch.float32, training,
                                     cfg.forward_clipval, cfg.gradient_recurrent_clipval, cfg.gradient_recurrent_cut,
-                                    f16=kdt == torch.float16)
+                                    f16=kdt == torch.float16, f32=kdt == torch.float32)
         plan = _native.query(prob, cfg.cluster_size, cfg.batch_tile)
         plan.test_drop_exchange = 1 if cfg._test_drop_exchange else 0
         dev = Wx.device
@@ -265,9 +267,11 @@ def flashrnn(
             f"{_NATIVE_BACKENDS} is provided (no Triton, no alternating cuBLAS backend, no CPU/PyTorch path)")
     if config.backend not in _NATIVE_BACKENDS:
         raise ValueError(f"Unknown backend {config.backend}")
-    if config.dtype not in ("bfloat16", "float16"):
-        raise NotImplementedError(f"dtype '{config.dtype}': the sm_100a kernels compute in bfloat16 or float16 with fp32 accumulation")
-    if config.dtype_s in ("bfloat16", "float16"):
+    if config.dtype not in ("bfloat16", "float16", "float32"):
+        raise NotImplementedError(f"dtype '{config.dtype}': the sm_100a kernels compute in bfloat16, float16 or float32")
+    if config.dtype == "float32":
+        config.dtype_s = "float32"  # the float32 loops keep everything in fp32
+    elif config.dtype_s in ("bfloat16", "float16"):
         config.dtype_s = config.dtype  # 16-bit states live in the kernel dtype (inputs of the other 16-bit type are cast)
     elif config.dtype_s != "float32":
         raise NotImplementedError(f"states in '{config.dtype_s}': states are kept in the kernel dtype or in float32")

@@ -37,15 +37,16 @@ class FlashRNNStepper:
             raise ValueError(f"shape mismatch for function '{function}': R{tuple(R.shape)} b{tuple(b.shape)}")
         self.function, self.B, self.chunk, self.N, self.D, self.S, self.Gw = function, batch_size, chunk, N, D, S, Gw
         dev = R.device
-        if dtype not in ("bfloat16", "float16"):
-            raise NotImplementedError(f"dtype '{dtype}': the sm_100a kernels compute in bfloat16 or float16")
+        if dtype not in ("bfloat16", "float16", "float32"):
+            raise NotImplementedError(f"dtype '{dtype}': the sm_100a kernels compute in bfloat16, float16 or float32")
         self._kdt = DTYPE_DICT[dtype]
-        sdt = DTYPE_DICT[dtype_s or dtype]
+        sdt = DTYPE_DICT["float32" if dtype == "float32" else (dtype_s or dtype)]
         if sdt not in (self._kdt, torch.float32):
             raise NotImplementedError("states are kept in the kernel dtype or in float32")
         self._R = R.detach().to(self._kdt).contiguous()
         self._b = b.detach().to(self._kdt).contiguous()
-        prob = _native.make_problem(function, batch_size, chunk, N, D, sdt == torch.float32, False, f16=self._kdt == torch.float16)
+        prob = _native.make_problem(function, batch_size, chunk, N, D, sdt == torch.float32, False, f16=self._kdt == torch.float16,
+                                    f32=self._kdt == torch.float32)
         self._plan = _native.query(prob)
         self._s0 = torch.zeros((S, batch_size, 1, N, D), dtype=sdt, device=dev)
         self._out = torch.empty((S, batch_size, chunk, N, D), dtype=sdt, device=dev)

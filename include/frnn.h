@@ -58,8 +58,10 @@ typedef struct frnn_problem {
   int32_t cell;          /* FRNN_CELL_*                                             */
   int32_t B, T, N, D;    /* batch, time steps, heads, head dim                     */
   int32_t dtype_io;      /* dtype of Wx, R, b, dWx, dR, db : FRNN_DTYPE_BF16 or _F16 (MMA operand type; accumulation and
-                            gate math are fp32 either way)                           */
-  int32_t dtype_state;   /* dtype of s0, states, dstates, ds0 : same as dtype_io, or F32 */
+                            gate math are fp32 either way), or FRNN_DTYPE_F32: the float32 loops (fp32 products on the
+                            CUDA cores, exp-based nonlinearities; accurate to ~1e-5 against an fp32 reference, an order
+                            of magnitude slower than the 16-bit tensor-core loops; any head_dim % 4 == 0 up to 1024)  */
+  int32_t dtype_state;   /* dtype of s0, states, dstates, ds0 : same as dtype_io, or F32 (F32 io needs F32 states) */
   int32_t training;      /* 1: forward writes the activation cache for backward     */
   float forward_clip;    /* > 0: clamp the new h to [-v, v]   (forward_clipval)     */
   float grad_clip;       /* > 0: clamp the recurrent dh to [-v, v] (gradient_recurrent_clipval) */
@@ -181,7 +183,7 @@ int frnn_backward_parts(const frnn_plan* plan, const frnn_bwd_args* args, void* 
  * "first call" below.
  *   - The plan is chosen as by frnn_query(problem).  Inputs, `states` and (training == 1) the activation `cache`
  *     of plan.cache_bytes (use frnn_query to size it) are still the caller's buffers.
- *   - Limit: 256 + Gr*N*D*D*2 bytes (rounded up to 256) must fit FRNN_NOALLOC_MAX_SCRATCH_BYTES, else
+ *   - Limit: 256 + Gr*N*D*D*2 bytes (float32 problems: *4; rounded up to 256) must fit FRNN_NOALLOC_MAX_SCRATCH_BYTES, else
  *     FRNN_ERR_TOO_LARGE is returned and nothing is launched.
  *   - First call on a device: it looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current).  If nothing of the library has run on that device yet, this lookup makes the driver load the

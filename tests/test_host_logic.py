@@ -117,6 +117,8 @@ def test_no_cpu_fallback_and_removed_backends():
     with pytest.raises(ValueError):
         flashrnn(Wx, R, b, function="lstm", backend="tpu")
     with pytest.raises(NotImplementedError):
+        flashrnn(Wx, R, b, function="lstm", dtype="float64")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):  # float32 is a kernel dtype; still no CPU path
         flashrnn(Wx, R, b, function="lstm", dtype="float32")
     with pytest.raises(RuntimeError, match="no CPU fallback"):  # float16 is a kernel dtype; still no CPU path
         flashrnn(Wx.half(), R.half(), b.half(), function="lstm", dtype="float16")
@@ -261,3 +263,25 @@ def test_floor_probe_exists_for_the_benchmark_tiles_only():
     for name in ("Wx", "R", "b", "s0", "states", "cache", "workspace"):
         setattr(args, name, 4096)
     assert L.frnn_forward(ctypes.byref(plan), ctypes.byref(args), None) != 0
+
+
+def test_float32_problems_take_the_float32_loops():
+    """dtype_io = float32: one geometry (a CTA per head and 8 batch rows), fp32 cache and workspace, any head_dim % 4."""
+    Gr, Gt, GC = 4, 4, 4
+    B, T, N, D = 5, 7, 3, 20
+    plan = _native.query(_native.make_problem("lstm", B, T, N, D, True, True, f32=True))
+    assert (plan.cluster_size, plan.units_per_cta, plan.batch_tile, plan.threads) == (1, D, 8, 256)
+    assert plan.prob.dtype_io == _native.DTYPE_F32 and plan.prob.dtype_state == _native.DTYPE_F32
+    assert plan.cache_bytes == B * T * GC * N * D * 4
+    assert plan.grads_count == Gr * N * D * D + Gt * N * D and plan.workspace_bytes >= plan.grads_offset + 4 * plan.grads_count
+    with pytest.raises(_native.FrnnError) as e:  # no other tile exists
+        _native.query(_native.make_problem("lstm", B, T, N, D, True, True, f32=True), 2, 8)
+    assert e.value.code == -6
+    with pytest.raises(_native.FrnnError) as e:
+        _native.query(_native.make_problem("lstm", B, T, N, 1030, True, True, f32=True))
+    assert e.value.code == -3
+    bad = _native.make_problem("lstm", B, T, N, D, True, True, f32=True)
+    bad.dtype_state = _native.DTYPE_BF16  # fp32 inputs need fp32 states
+    with pytest.raises(_native.FrnnError) as e:
+        _native.query(bad)
+    assert e.value.code == -4

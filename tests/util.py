@@ -56,7 +56,8 @@ def run_native(function, Wx, R, b, s0, cot=None, state_f32=False, device="cuda",
     """Runs the CUDA path through the public API; returns numpy float64 dict like oracle_fwbw."""
     from flashrnn_b200 import FlashRNNConfig, flashrnn
 
-    name = {torch.bfloat16: "bfloat16", torch.float16: "float16"}[dtype]
+    name = {torch.bfloat16: "bfloat16", torch.float16: "float16", torch.float32: "float32"}[dtype]
+    state_f32 = state_f32 or dtype == torch.float32
     sdt = torch.float32 if state_f32 else dtype
     Wx_d = Wx.to(device=device, dtype=dtype).requires_grad_(True)
     R_d = R.to(device=device, dtype=dtype).requires_grad_(True)
