@@ -4,12 +4,16 @@
 // tf32, fused/flashrnn_fused_forward.cu:108-112).  Here the fp32 path is the ACCURATE one: products and sums in fp32 on
 // the CUDA cores, gate nonlinearities from exp (error ~1e-6), so that it agrees with the fp32 `vanilla` loop to ~1e-5 --
 // the 16-bit tensor-core loops are the fast path, this one is for callers that need float32 results (reference checks,
-// gradient checks, small models).  Same structure as the other loops, kept simple:
-//   * forward: one CTA per (head, 8 batch rows) runs all T steps.  Per step: pre = R h_{t-1} (thread = gate row, R read
-//     transposed so that a warp reads consecutive addresses, from shared memory when the head's R fits there, else from
-//     L2; h broadcast from shared memory), then the pointwise cell on (row, unit) items, new h into the shared tile.
-//   * backward: the reverse loop with the closed-form cell backward; dh_{t-1} = R^T delta (thread = input unit p);
-//     the carried cotangents live in the ds0 output itself, db is summed in shared memory and flushed once.
+// gradient checks, small models).
+//   * cluster loops (x32c_*): a cluster of CS CTAs owns one head and 8 batch rows for all T steps; CTA c owns U = D / CS
+//     units, keeps its slice of R in shared memory as fp32 (Gr*U*D*4 bytes) and exchanges per step only what the others
+//     need -- its slice of h_t (forward, all-gather) or its partial sums of dh_{t-1} (reverse, reduce-scatter) -- with
+//     one bulk copy per peer that completes on the peer's mbarrier, the protocol of the 16-bit loops.  A thread's items
+//     (batch row, unit) are fixed, so states, carried cotangents and bias stay in registers and the next step's global
+//     inputs are loaded one step ahead.  The matrix phase is FFMA from shared memory: a thread keeps 16 (forward: two
+//     gate rows x 8 batch rows) or 8 (reverse: one column x 8 batch rows) sums over its share of k.
+//   * streamed loops (x32_*): one CTA per (head, 8 batch rows), R read from L2 in every step; for head dims whose slices
+//     do not fit the shared memory of a portable cluster (e.g. four-gate cells above 256) or are no multiple of 4 units.
 //   * dR: a tiled fp32 GEMM over all (b, t) with split-K and fp32 atomics.
 // Replaces, for float32, FLASHRNNCellFusedForward / FLASHRNNCellFusedBackward / the cuBLAS dR GEMM of the reference
 // (fused/flashrnn_fused_forward.cu:146-659, fused/flashrnn_fused_backward.cu:129-624, 1049-1058).
@@ -33,7 +37,10 @@ struct XParams {
   const float* Wx; const float* R; const float* RT; const float* bias; const float* s0;
   float* states; float* cache;
   const float* dstates; float* dWx; float* dg0; float* ds0; float* dbias;
+  unsigned* status;
   int B, T, N, D;
+  int U, CS, KS;  // cluster loops: units per CTA, CTAs per cluster, k-splits of the matrix phase
+  int test_drop;  // test hook: CTA 0 of every cluster withholds its message of step 1
   int r_in_smem;
   float fclip, gclip;
   int grad_cut;
@@ -198,6 +205,432 @@ __global__ void __launch_bounds__(XTHREADS) x32_bwd_kernel(const XParams p) {
   }
 }
 
+// ================================================================================================ cluster loops
+// Shared memory of the forward loop (floats): Rs[D][Gr*U] | h[2][D][8] | part[KS][8][Gr*U] | 2 mbarriers + flag
+// Rs[k][g*U + u] = R[g][n][unit0 + u][k];  h[x][k][b] = h of unit k, batch row b (CTA c's slice = rows c*U .. c*U+U-1)
+template <int CELL, int IPT>
+__global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) {
+  using C = Cell<CELL>;
+  constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, GCA = GC > 0 ? GC : 1;
+  extern __shared__ __align__(16) float sm[];
+  const int D = p.D, U = p.U, CS = p.CS, KS = p.KS, GU = Gr * U, T = p.T, B = p.B, N = p.N;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, b0 = blockIdx.y * XBT;
+  const uint32_t crank = CS > 1 ? cluster_ctarank() : 0u;
+  const int unit0 = (int)crank * U;
+  const size_t ND = (size_t)N * D;
+  float* Rs = sm;
+  float* hbuf = Rs + (size_t)D * GU;
+  float* part = hbuf + 2 * XBT * D;
+  uint64_t* full = reinterpret_cast<uint64_t*>(part + (size_t)KS * XBT * GU);
+  volatile int* gave_up = reinterpret_cast<volatile int*>(full + 2);
+
+  {  // this CTA's slice of R, from the transposed copy RT[n][k][g*D + d]
+    const float* RT = p.RT + (size_t)n * D * Gr * D;
+    for (int i = tid; i < D * GU; i += XTHREADS) {
+      const int k = i / GU, j = i - k * GU, g = j / U, u = j - g * U;
+      Rs[i] = RT[(size_t)k * Gr * D + g * D + unit0 + u];
+    }
+  }
+  // ---- this thread's items (batch row, unit): fixed for all steps
+  bool it_on[IPT], it_ok[IPT];
+  int bl_[IPT], u_[IPT];
+  const float* wx_p[IPT];
+  float* st_p[IPT];
+  float* ch_p[IPT];
+  float bias[IPT][Gt], st[IPT][S], wxn[IPT][Gw];
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int q = tid + i * XTHREADS;
+    it_on[i] = q < XBT * U;
+    bl_[i] = it_on[i] ? q / U : 0;
+    u_[i] = it_on[i] ? q - bl_[i] * U : 0;
+    const int bg = b0 + bl_[i], d = unit0 + u_[i];
+    it_ok[i] = it_on[i] && bg < B;
+    const int bgc = bg < B ? bg : B - 1;
+    const size_t nd = (size_t)n * D + d;
+    wx_p[i] = p.Wx + (size_t)bgc * p.wx_sb + (size_t)n * p.wx_sn + d;
+    st_p[i] = p.states + ((size_t)bgc * T) * ND + nd;
+    ch_p[i] = p.cache + ((size_t)bgc * T) * GCA * ND + nd;
+#pragma unroll
+    for (int g = 0; g < Gt; ++g) bias[i][g] = p.bias[(size_t)g * ND + nd];
+#pragma unroll
+    for (int s = 0; s < S; ++s) st[i][s] = it_ok[i] ? p.s0[((size_t)s * B + bg) * ND + nd] : 0.f;
+#pragma unroll
+    for (int g = 0; g < Gw; ++g) wxn[i][g] = it_ok[i] ? wx_p[i][(size_t)g * p.wx_sg] : 0.f;  // Wx of step 0
+    wx_p[i] += p.wx_st;
+  }
+  // ---- h_{-1} of the whole head -> h[0] (read straight from global by every CTA)
+  for (int i = tid; i < XBT * D; i += XTHREADS) {
+    const int bl = i / D, k = i - bl * D, b = b0 + bl;
+    hbuf[k * XBT + bl] = b < B ? p.s0[(size_t)b * ND + (size_t)n * D + k] : 0.f;
+  }
+  const uint32_t slice_bytes = (uint32_t)(U * XBT * 4);
+  const uint32_t expect_bytes = (uint32_t)(CS - 1) * slice_bytes;
+  bool poisoned = false;
+  if (CS > 1) {
+    if (tid == 0) {
+      *gave_up = 0;
+      mbar_init(&full[0], 1);
+      mbar_init(&full[1], 1);
+      fence_mbar_init();
+      if (T > 1) mbar_arrive_expect_tx(&full[1], expect_bytes);  // h_0, consumed at step 1
+      if (T > 2) mbar_arrive_expect_tx(&full[0], expect_bytes);  // h_1, consumed at step 2
+    }
+    cluster_arrive();
+    cluster_wait();  // every CTA of the cluster is resident and its barriers are initialised
+  } else {
+    __syncthreads();
+  }
+  const uint32_t my_slice0 = smem_u32(hbuf + (size_t)unit0 * XBT);
+  const uint32_t buf_bytes = (uint32_t)(XBT * D * 4);
+  const uint32_t full_u32 = smem_u32(&full[0]);
+  const int nrp = GU >> 1, nwork = nrp * KS, KQ = (D + KS - 1) / KS;
+
+  for (int t = 0; t < T; ++t) {
+    const int cur = t & 1, nxt = cur ^ 1;
+    float wxc[IPT][Gw];
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+#pragma unroll
+      for (int g = 0; g < Gw; ++g) wxc[i][g] = wxn[i][g];
+      if (it_ok[i] && t + 1 < T) {  // the next step's inputs, a whole step ahead of their use
+#pragma unroll
+        for (int g = 0; g < Gw; ++g) wxn[i][g] = wx_p[i][(size_t)g * p.wx_sg];
+        wx_p[i] += p.wx_st;
+      }
+    }
+    if (CS > 1 && t > 0) {
+      if (!mbar_wait_bounded(&full[cur], ((t - 1) >> 1) & 1)) {
+        poisoned = true;
+        *gave_up = 1;
+        report_timeout(p.status, t);
+      }
+      // re-arm for h_{t+1}; never after an expired wait: that phase is still open and has no arrival left to give
+      if (tid == 0 && !poisoned && t + 2 < T) mbar_arrive_expect_tx(&full[cur], expect_bytes);
+    }
+    // ---------------- matrix phase: part[kc][b][row] = sum over this thread's k of R[row][k] * h_{t-1}[b][k]
+    {
+      const float* hcur = hbuf + (size_t)cur * XBT * D;
+      for (int w = tid; w < nwork; w += XTHREADS) {
+        const int kc = w / nrp, rp = w - kc * nrp;
+        const int k0 = kc * KQ, k1 = (k0 + KQ < D) ? k0 + KQ : D;
+        float acc[2][XBT];
+#pragma unroll
+        for (int b = 0; b < XBT; ++b) acc[0][b] = acc[1][b] = 0.f;
+        const float* rr = Rs + 2 * rp;
+#pragma unroll 4
+        for (int k = k0; k < k1; ++k) {
+          const float2 r = *reinterpret_cast<const float2*>(rr + (size_t)k * GU);
+          const float4 ha = *reinterpret_cast<const float4*>(hcur + k * XBT);
+          const float4 hb = *reinterpret_cast<const float4*>(hcur + k * XBT + 4);
+          const float hv[XBT] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+#pragma unroll
+          for (int b = 0; b < XBT; ++b) {
+            acc[0][b] = fmaf(r.x, hv[b], acc[0][b]);
+            acc[1][b] = fmaf(r.y, hv[b], acc[1][b]);
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < XBT; ++b)
+          *reinterpret_cast<float2*>(part + ((size_t)kc * XBT + b) * GU + 2 * rp) = make_float2(acc[0][b], acc[1][b]);
+      }
+    }
+    __syncthreads();
+    // set when a wait of this step expired in some thread of the CTA (written before the barrier above)
+    const int quit = (CS > 1) ? *gave_up : 0;
+    // ---------------- cell phase: this thread's items; new h into this CTA's slice of h[nxt]
+    float cch[IPT][GCA];
+    float* hdst = hbuf + (size_t)nxt * XBT * D + (size_t)unit0 * XBT;
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_on[i]) continue;
+      float prv[Gr];
+#pragma unroll
+      for (int g = 0; g < Gr; ++g) prv[g] = 0.f;
+      for (int kc = 0; kc < KS; ++kc) {
+        const float* pp = part + ((size_t)kc * XBT + bl_[i]) * GU + u_[i];
+#pragma unroll
+        for (int g = 0; g < Gr; ++g) prv[g] += pp[g * U];
+      }
+      cell_forward<CELL>(prv, wxc[i], bias[i], st[i], cch[i]);
+      if (p.fclip > 0.f) st[i][0] = clampf(st[i][0], p.fclip);
+      if (!it_ok[i]) {  // rows beyond B: keep everything zero
+#pragma unroll
+        for (int s = 0; s < S; ++s) st[i][s] = 0.f;
+      }
+      hdst[u_[i] * XBT + bl_[i]] = st[i][0];
+    }
+    if (CS > 1) fence_proxy_async_smem();  // make the slice visible to the bulk-copy engine
+    __syncthreads();
+    // ---------------- push: this CTA's slice of h_t -> h[nxt] of every other CTA of the cluster
+    if (CS > 1 && t + 1 < T && !(p.test_drop && crank == 0 && t == 1))  // uniform branch; one elected lane per warp copies
+      push_slice_to_peers(my_slice0 + nxt * buf_bytes, slice_bytes, full_u32 + nxt * 8, crank, (uint32_t)CS, (uint32_t)warp,
+                          (uint32_t)(XTHREADS >> 5));
+    // ---------------- behind the exchange: results to global memory
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_ok[i]) continue;
+#pragma unroll
+      for (int s = 0; s < S; ++s) st_p[i][(size_t)s * B * T * ND] = st[i][s];
+      st_p[i] += ND;
+      if (GC > 0 && p.cache != nullptr) {
+#pragma unroll
+        for (int k = 0; k < GC; ++k) ch_p[i][(size_t)k * ND] = cch[i][k];
+        ch_p[i] += (size_t)GCA * ND;
+      }
+    }
+    // After an expired wait the whole CTA leaves the loop and sends nothing further, so every other CTA of the cluster
+    // runs into its own bounded wait and leaves the same way.
+    if (quit) break;
+  }
+  if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight
+}
+
+// Shared memory of the reverse loop (floats): Rb[Gr*U][D] | delta[Gr*U][8] | send[2][CS][MSG] | recv[2][CS][MSG] |
+// dbs[Gt][U] | 2 mbarriers + flag, MSG = KS*8*U.  Rb[g*U + u][p] = R[g][n][unit0 + u][p].
+// Reduce-scatter: CTA c multiplies ITS deltas with its rows of R for all D columns p and sends the owner of p the
+// partial sums; message for CTA x: [kc][b][u] with p = x*U + u (the CTA's own part goes straight into its recv slot).
+template <int CELL, int IPT>
+__global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) {
+  using C = Cell<CELL>;
+  constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, GCA = GC > 0 ? GC : 1, NNEED = C::NNEED, NEXT = C::NEXT;
+  extern __shared__ __align__(16) float sm[];
+  const int D = p.D, U = p.U, CS = p.CS, KS = p.KS, GU = Gr * U, T = p.T, B = p.B, N = p.N;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n = blockIdx.z, b0 = blockIdx.y * XBT;
+  const uint32_t crank = CS > 1 ? cluster_ctarank() : 0u;
+  const int unit0 = (int)crank * U;
+  const size_t ND = (size_t)N * D;
+  const int MSG = KS * XBT * U;
+  float* Rb = sm;
+  float* delta = Rb + (size_t)GU * D;
+  float* send = delta + GU * XBT;
+  float* recv = send + 2 * CS * MSG;
+  float* dbs = recv + 2 * CS * MSG;
+  uint64_t* full = reinterpret_cast<uint64_t*>(dbs + Gt * U);
+  volatile int* gave_up = reinterpret_cast<volatile int*>(full + 2);
+  const bool exch = !p.grad_cut;  // with the recurrent gradient cut no dh crosses a step: no matrix phase, no exchange
+
+  for (int i = tid; i < GU * D; i += XTHREADS) {
+    const int j = i / D, pc = i - j * D, g = j / U, u = j - g * U;
+    Rb[i] = p.R[(((size_t)g * N + n) * D + unit0 + u) * D + pc];
+  }
+  for (int i = tid; i < Gt * U; i += XTHREADS) dbs[i] = 0.f;
+
+  bool it_on[IPT], it_ok[IPT];
+  int bl_[IPT], u_[IPT];
+  const float* st_p[IPT];   // states[0][b][t][n][d] of the step whose values are loaded NEXT
+  const float* ch_p[IPT];
+  const float* ex_p[IPT];
+  float* dw_p[IPT];
+  float* dg_p[IPT];
+  float car[IPT][S], cur[IPT][NNEED], prv[IPT][NNEED], cv[IPT][GCA], ext[IPT][NEXT], dbacc[IPT][Gt];
+  const size_t sstride = (size_t)B * T * ND;
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    const int q = tid + i * XTHREADS;
+    it_on[i] = q < XBT * U;
+    bl_[i] = it_on[i] ? q / U : 0;
+    u_[i] = it_on[i] ? q - bl_[i] * U : 0;
+    const int bg = b0 + bl_[i], d = unit0 + u_[i];
+    it_ok[i] = it_on[i] && bg < B;
+    const int bgc = bg < B ? bg : B - 1;
+    const size_t nd = (size_t)n * D + d;
+    // everything of time T-1
+    st_p[i] = p.states + ((size_t)bgc * T + (T - 1)) * ND + nd;
+    ch_p[i] = p.cache + (((size_t)bgc * T + (T - 1)) * GCA) * ND + nd;
+    ex_p[i] = p.dstates + (size_t)bgc * p.ds_sb + (size_t)(T - 1) * p.ds_st + (size_t)n * p.ds_sn + d;
+    dw_p[i] = p.dWx + (((size_t)bgc * T + (T - 1)) * Gw) * ND + nd;
+    dg_p[i] = p.dg0 + ((size_t)bgc * T + (T - 1)) * ND + nd;
+#pragma unroll
+    for (int s = 0; s < S; ++s) car[i][s] = 0.f;
+#pragma unroll
+    for (int g = 0; g < Gt; ++g) dbacc[i][g] = 0.f;
+#pragma unroll
+    for (int k = 0; k < NNEED; ++k) {
+      const size_t so = (size_t)C::need(k) * sstride;
+      cur[i][k] = it_ok[i] ? st_p[i][so] : 1.f;
+      prv[i][k] = !it_ok[i] ? 1.f : (T > 1 ? st_p[i][so - ND] : p.s0[((size_t)C::need(k) * B + bgc) * ND + nd]);
+    }
+#pragma unroll
+    for (int k = 0; k < GCA; ++k) cv[i][k] = (GC > 0 && it_ok[i] && k < GC) ? ch_p[i][(size_t)k * ND] : 0.f;
+#pragma unroll
+    for (int k = 0; k < NEXT; ++k) ext[i][k] = it_ok[i] ? ex_p[i][(size_t)k * p.ds_ss] : 0.f;
+    st_p[i] -= 2 * ND;  // the next load of a previous state is the one of time T-3 (prv of step T-2)
+    ch_p[i] -= (size_t)GCA * ND;
+    ex_p[i] -= p.ds_st;
+  }
+  const uint32_t msg_bytes = (uint32_t)(MSG * 4);
+  const uint32_t expect_bytes = (uint32_t)(CS - 1) * msg_bytes;
+  const bool xc = exch && CS > 1;
+  bool poisoned = false;
+  if (CS > 1) {
+    if (tid == 0) {
+      *gave_up = 0;
+      mbar_init(&full[0], 1);
+      mbar_init(&full[1], 1);
+      fence_mbar_init();
+      if (exch) {
+        mbar_arrive_expect_tx(&full[0], expect_bytes);             // partial sums of step 0
+        if (T > 1) mbar_arrive_expect_tx(&full[1], expect_bytes);  // ... of step 1
+      }
+    }
+    cluster_arrive();
+    cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  const uint32_t full_u32 = smem_u32(&full[0]);
+  const int KQ = (GU + KS - 1) / KS, nwork = D * KS;
+
+  // sum of the partial sums that arrived for item i in buffer x
+  auto gather = [&](int i, int x) {
+    float r = 0.f;
+    for (int c = 0; c < CS; ++c) {
+      const float* q = recv + ((size_t)x * CS + c) * MSG + bl_[i] * U + u_[i];
+      for (int kc = 0; kc < KS; ++kc) r += q[(size_t)kc * XBT * U];
+    }
+    return r;
+  };
+  bool quit_all = false;
+  for (int j = 0; j < T; ++j) {  // j-th step of the reverse loop, time t = T-1-j
+    const int t = T - 1 - j, buf = j & 1, pb = buf ^ 1;
+    // ---- the next step's inputs (time t-1), a whole step ahead of their use
+    float prv_n[IPT][NNEED], cv_n[IPT][GCA], ext_n[IPT][NEXT];
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+#pragma unroll
+      for (int k = 0; k < NNEED; ++k) prv_n[i][k] = 1.f;
+#pragma unroll
+      for (int k = 0; k < GCA; ++k) cv_n[i][k] = 0.f;
+#pragma unroll
+      for (int k = 0; k < NEXT; ++k) ext_n[i][k] = 0.f;
+      if (it_ok[i] && t > 0) {
+        const int bg = b0 + bl_[i];
+        const size_t nd = (size_t)n * D + unit0 + u_[i];
+#pragma unroll
+        for (int k = 0; k < NNEED; ++k)
+          prv_n[i][k] = t > 1 ? st_p[i][(size_t)C::need(k) * sstride] : p.s0[((size_t)C::need(k) * B + bg) * ND + nd];
+        if (GC > 0) {
+#pragma unroll
+          for (int k = 0; k < GC; ++k) cv_n[i][k] = ch_p[i][(size_t)k * ND];
+        }
+#pragma unroll
+        for (int k = 0; k < NEXT; ++k) ext_n[i][k] = ex_p[i][(size_t)k * p.ds_ss];
+        st_p[i] -= ND;
+        ch_p[i] -= (size_t)GCA * ND;
+        ex_p[i] -= p.ds_st;
+      }
+    }
+    if (xc && j > 0) {  // the partial sums of step j-1
+      if (!mbar_wait_bounded(&full[pb], ((j - 1) >> 1) & 1)) {
+        poisoned = true;
+        *gave_up = 1;
+        report_timeout(p.status, t);
+      }
+      if (tid == 0 && !poisoned && j + 1 < T) mbar_arrive_expect_tx(&full[pb], expect_bytes);  // re-arm for step j+1
+    }
+    // ---------------- cell phase
+#pragma unroll
+    for (int i = 0; i < IPT; ++i) {
+      if (!it_on[i]) continue;
+      float r = car[i][0];
+      if (exch && j > 0) r += gather(i, pb);
+      if (p.gclip > 0.f) r = clampf(r, p.gclip);
+      float dR_[Gr], dW_[Gw], dB_[Gt];
+      cell_backward<CELL>(ext[i][0] + r, ext[i], car[i], cv[i], cur[i], prv[i], dR_, dW_, dB_);
+      if (!it_ok[i]) {
+#pragma unroll
+        for (int s = 0; s < S; ++s) car[i][s] = 0.f;
+#pragma unroll
+        for (int g = 0; g < Gr; ++g) dR_[g] = 0.f;
+      } else {
+#pragma unroll
+        for (int g = 0; g < Gw; ++g) dw_p[i][(size_t)g * ND] = dW_[g];
+        dw_p[i] -= (size_t)Gw * ND;
+        if (CELL == CELL_GRU) { *dg_p[i] = dR_[0]; dg_p[i] -= ND; }
+#pragma unroll
+        for (int g = 0; g < Gt; ++g) dbacc[i][g] += dB_[g];
+      }
+#pragma unroll
+      for (int g = 0; g < Gr; ++g) delta[(g * U + u_[i]) * XBT + bl_[i]] = dR_[g];
+#pragma unroll
+      for (int k = 0; k < NNEED; ++k) { cur[i][k] = prv[i][k]; prv[i][k] = prv_n[i][k]; }
+#pragma unroll
+      for (int k = 0; k < GCA; ++k) cv[i][k] = cv_n[i][k];
+#pragma unroll
+      for (int k = 0; k < NEXT; ++k) ext[i][k] = ext_n[i][k];
+    }
+    __syncthreads();
+    const int quit = (CS > 1) ? *gave_up : 0;
+    if (exch) {
+      // ---------------- matrix phase: partial dh_{t-1}[b][p] = sum over this thread's (g, u) of delta[b][g,u] * R[g][u][p]
+      for (int w = tid; w < nwork; w += XTHREADS) {
+        const int kc = w / D, pc = w - kc * D;
+        const int j0 = kc * KQ, j1 = (j0 + KQ < GU) ? j0 + KQ : GU;
+        float acc[XBT];
+#pragma unroll
+        for (int b = 0; b < XBT; ++b) acc[b] = 0.f;
+        const float* rr = Rb + pc;
+#pragma unroll 4
+        for (int jj = j0; jj < j1; ++jj) {
+          const float r = rr[(size_t)jj * D];
+          const float4 da = *reinterpret_cast<const float4*>(delta + jj * XBT);
+          const float4 db4 = *reinterpret_cast<const float4*>(delta + jj * XBT + 4);
+          acc[0] = fmaf(r, da.x, acc[0]); acc[1] = fmaf(r, da.y, acc[1]); acc[2] = fmaf(r, da.z, acc[2]); acc[3] = fmaf(r, da.w, acc[3]);
+          acc[4] = fmaf(r, db4.x, acc[4]); acc[5] = fmaf(r, db4.y, acc[5]); acc[6] = fmaf(r, db4.z, acc[6]); acc[7] = fmaf(r, db4.w, acc[7]);
+        }
+        const int c = pc / U, u = pc - c * U;
+        // the owner's slot: recv[buf][crank] over there; the message leaves from send[buf][c], the own part stays here
+        float* dst = ((uint32_t)c == crank ? recv + ((size_t)buf * CS + crank) * MSG : send + ((size_t)buf * CS + c) * MSG) +
+                     (size_t)kc * XBT * U + u;
+#pragma unroll
+        for (int b = 0; b < XBT; ++b) dst[b * U] = acc[b];
+      }
+      if (CS > 1) fence_proxy_async_smem();
+      __syncthreads();
+      if (CS > 1 && !(p.test_drop && crank == 0 && j == 1)) {  // uniform branch; warp w serves the peers w, w + 8, ...
+        __syncwarp();
+        for (uint32_t c = (uint32_t)warp; c < (uint32_t)CS; c += XTHREADS >> 5) {
+          if (c == crank) continue;
+          const uint32_t src = smem_u32(send + ((size_t)buf * CS + c) * MSG);
+          const uint32_t dst = map_to_cta(smem_u32(recv + ((size_t)buf * CS + crank) * MSG), c);
+          const uint32_t bar = map_to_cta(full_u32 + buf * 8, c);
+          if (elect_one_sync()) bulk_copy_to_cta(dst, src, msg_bytes, bar);
+        }
+      }
+    }
+    if (quit) { quit_all = true; break; }
+  }
+  // ---- cotangents of the initial states: the carried ones; h also gets the matrix part of the last step
+  if (xc && !quit_all) {
+    if (!mbar_wait_bounded(&full[(T - 1) & 1], ((T - 1) >> 1) & 1)) {
+      report_timeout(p.status, -1);
+      quit_all = true;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < IPT; ++i) {
+    if (!it_ok[i]) continue;
+    const int bg = b0 + bl_[i];
+    const size_t nd = (size_t)n * D + unit0 + u_[i];
+    float r = car[i][0];
+    if (exch && !quit_all) r += gather(i, (T - 1) & 1);
+    p.ds0[(size_t)bg * ND + nd] = r;
+#pragma unroll
+    for (int s = 1; s < S; ++s) p.ds0[((size_t)s * B + bg) * ND + nd] = car[i][s];
+#pragma unroll
+    for (int g = 0; g < Gt; ++g) atomicAdd(&dbs[g * U + u_[i]], dbacc[i][g]);
+  }
+  __syncthreads();
+  for (int i = tid; i < Gt * U; i += XTHREADS) {
+    const int g = i / U, u = i - g * U;
+    atomicAdd(p.dbias + (size_t)g * ND + (size_t)n * D + unit0 + u, dbs[i]);
+  }
+  if (CS > 1) { cluster_arrive(); cluster_wait(); }
+}
+
 // dR[g][n][d][p] += sum over this CTA's rows k = (b, t) of delta_g[k][d] * h_{t-1}[k][p]: 64 x 64 tile of ((g, d), p)
 struct XDrParams {
   const float* dWx; const float* dg0; const float* states; const float* s0; float* dR;
@@ -294,24 +727,77 @@ size_t fwd_smem(const frnn_problem& pr, const Dims& d, bool r_in) {
 size_t bwd_smem(const frnn_problem& pr, const Dims& d) {
   return ((size_t)XBT * d.Gr * pr.D + (size_t)XBT * pr.D + (size_t)d.Gt * pr.D) * 4;
 }
+// Geometry of the loops for a cluster size: U units per CTA, k-splits of the two matrix phases, items per thread.
+// `cluster` false = the streamed loops (one CTA per head, R from L2).
+struct Tile { int cs, u, ksf, ksb, ipt; bool cluster; size_t smem_f, smem_b; };
+int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+bool cluster_tile(const frnn_problem& pr, const Dims& d, int cs, Tile* t) {
+  if (cs < 1 || cs > 8 || pr.D % cs) return false;
+  const int u = pr.D / cs;
+  if (u % 4 || u > 64) return false;
+  const size_t gu = (size_t)d.Gr * u, D = (size_t)pr.D;
+  t->cs = cs; t->u = u; t->cluster = true;
+  t->ksf = clampi((int)(512 / gu), 1, 8);
+  t->ksb = clampi(256 / pr.D, 1, 8);
+  t->ipt = XBT * u > XTHREADS ? 2 : 1;
+  t->smem_f = (D * gu + 2 * XBT * D + (size_t)t->ksf * XBT * gu) * 4 + 64;
+  t->smem_b = (gu * D + gu * XBT + (size_t)4 * t->ksb * XBT * D + (size_t)d.Gt * u) * 4 + 64;
+  return t->smem_f <= kSmemMax && t->smem_b <= kSmemMax;
+}
+// cs == 0: the preferred tile -- the whole head in one CTA up to head dim 64, else the smallest cluster with at most 32
+// units per CTA, else the smallest cluster that fits, else the streamed loops.  cs > 0: that cluster size or nothing
+// (cs == 1 falls back to the streamed loops when the head does not fit one CTA).
+bool pick_tile(const frnn_problem& pr, const Dims& d, int cs, Tile* t) {
+  if (cs > 0) {
+    if (cluster_tile(pr, d, cs, t)) return true;
+    if (cs != 1) return false;
+  } else {
+    if (pr.D <= 64 && cluster_tile(pr, d, 1, t)) return true;
+    for (int c = 1; c <= 8; ++c)
+      if (cluster_tile(pr, d, c, t) && t->u <= 32) return true;
+    for (int c = 1; c <= 8; ++c)
+      if (cluster_tile(pr, d, c, t)) return true;
+  }
+  *t = Tile{1, pr.D, 0, 0, 0, false, fwd_smem(pr, d, false), bwd_smem(pr, d)};
+  return t->smem_f <= kSmemMax && t->smem_b <= kSmemMax;
+}
 int validate(const frnn_problem* pr, Dims* d) {
   if (!pr) return FRNN_ERR_NULL;
   if (!dims_of(pr->cell, pr->forward_clip, d)) return FRNN_ERR_CELL;
   if (pr->dtype_io != FRNN_DTYPE_F32 || pr->dtype_state != FRNN_DTYPE_F32) return FRNN_ERR_DTYPE;
   if (pr->B < 1 || pr->T < 1 || pr->N < 1 || pr->N > 65535 || pr->D < 4 || pr->D > 1024 || pr->D % 4) return FRNN_ERR_SHAPE;
   if ((pr->B + XBT - 1) / XBT > 65535) return FRNN_ERR_SHAPE;
-  if (fwd_smem(*pr, *d, false) > kSmemMax || bwd_smem(*pr, *d) > kSmemMax) return FRNN_ERR_SHAPE;
+  Tile t;
+  if (!pick_tile(*pr, *d, 0, &t)) return FRNN_ERR_SHAPE;
   return FRNN_OK;
 }
-int check(const frnn_plan* pl, Dims* d) {
+int check(const frnn_plan* pl, Dims* d, Tile* t) {
   if (!pl) return FRNN_ERR_NULL;
   if (pl->abi_version != FRNN_ABI_VERSION) return FRNN_ERR_PLAN;
   const int rc = validate(&pl->prob, d);
   if (rc) return rc;
-  if (pl->cluster_size != 1 || pl->batch_tile != XBT || pl->threads != XTHREADS || pl->units_per_cta != pl->prob.D ||
-      pl->workspace_bytes != ws_layout(pl->prob, *d).total || pl->probe_noop_cell)
+  if (!pick_tile(pl->prob, *d, pl->cluster_size, t) || pl->batch_tile != XBT || pl->threads != XTHREADS ||
+      pl->units_per_cta != t->u || pl->workspace_bytes != ws_layout(pl->prob, *d).total || pl->probe_noop_cell)
     return FRNN_ERR_PLAN;
   return FRNN_OK;
+}
+template <typename K>
+cudaError_t launch_cluster(K kern, const frnn_problem& pr, const Tile& t, size_t smem, const XParams& p, cudaStream_t stream) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);  // fixed maximum
+  if (e != cudaSuccess) return e;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)t.cs, (unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
+  cfg.blockDim = dim3(XTHREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)t.cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = t.cs > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, p);
 }
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 bool strides_ok(const int64_t (&in)[4], const long long (&dense)[4], long long (&out)[4]) {
@@ -338,12 +824,14 @@ __attribute__((visibility("hidden"))) int frnn_query_f32(const frnn_problem* pr,
   const int rc = validate(pr, &d);
   if (rc) return rc;
   if (!out) return FRNN_ERR_NULL;
-  if ((cs && cs != 1) || (bt && bt != XBT) || stages) return FRNN_ERR_PLAN;  // the float32 loops have one geometry
+  if ((bt && bt != XBT) || stages) return FRNN_ERR_PLAN;  // 8 batch rows per CTA, no input ring
+  Tile tl;
+  if (!pick_tile(*pr, d, cs, &tl)) return FRNN_ERR_PLAN;
   frnn_plan pl = {};
   pl.abi_version = FRNN_ABI_VERSION;
   pl.prob = *pr;
-  pl.cluster_size = 1;
-  pl.units_per_cta = pr->D;
+  pl.cluster_size = tl.cs;
+  pl.units_per_cta = tl.u;
   pl.batch_tile = XBT;
   pl.threads = XTHREADS;
   pl.wx_stages = 0;
@@ -359,7 +847,8 @@ __attribute__((visibility("hidden"))) int frnn_query_f32(const frnn_problem* pr,
 
 __attribute__((visibility("hidden"))) int frnn_forward_f32(const frnn_plan* plan, const frnn_fwd_args* a, void* stream_) {
   Dims d;
-  int rc = check(plan, &d);
+  Tile tl;
+  int rc = check(plan, &d, &tl);
   if (rc) return rc;
   const frnn_problem& pr = plan->prob;
   if (!a || !a->Wx || !a->R || !a->b || !a->s0 || !a->states || !a->workspace) return FRNN_ERR_NULL;
@@ -389,22 +878,37 @@ __attribute__((visibility("hidden"))) int frnn_forward_f32(const frnn_plan* plan
   p.bias = static_cast<const float*>(a->b); p.s0 = static_cast<const float*>(a->s0);
   p.states = static_cast<float*>(a->states); p.cache = pr.training ? static_cast<float*>(a->cache) : nullptr;
   p.B = pr.B; p.T = pr.T; p.N = pr.N; p.D = pr.D;
-  p.r_in_smem = fwd_smem(pr, d, true) <= kSmemMax;
+  p.status = reinterpret_cast<unsigned*>(ws);
   p.fclip = pr.forward_clip; p.gclip = pr.grad_clip; p.grad_cut = pr.grad_cut;
   p.wx_sb = wxs[0]; p.wx_st = wxs[1]; p.wx_sg = wxs[2]; p.wx_sn = wxs[3];
-  const dim3 grid((unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
-  const size_t smem = fwd_smem(pr, d, p.r_in_smem != 0);
-  auto launch = [&](auto kern) -> cudaError_t {
-    cudaError_t s = set_smem(kern);
-    if (s != cudaSuccess) return s;
-    kern<<<grid, XTHREADS, smem, stream>>>(p);
-    return cudaGetLastError();
-  };
-  switch (pr.cell) {
-    case CELL_LSTM: e = launch(x32_fwd_kernel<CELL_LSTM>); break;
-    case CELL_GRU: e = launch(x32_fwd_kernel<CELL_GRU>); break;
-    case CELL_SLSTM: e = launch(x32_fwd_kernel<CELL_SLSTM>); break;
-    default: e = pr.forward_clip > 0.f ? launch(x32_fwd_kernel<CELL_ELMAN_CLIP>) : launch(x32_fwd_kernel<CELL_ELMAN>); break;
+  if (tl.cluster) {
+    p.U = tl.u; p.CS = tl.cs; p.KS = tl.ksf; p.test_drop = plan->test_drop_exchange;
+    auto launch = [&](auto k1, auto k2) { return tl.ipt == 1 ? launch_cluster(k1, pr, tl, tl.smem_f, p, stream) : launch_cluster(k2, pr, tl, tl.smem_f, p, stream); };
+    switch (pr.cell) {
+      case CELL_LSTM: e = launch(x32c_fwd_kernel<CELL_LSTM, 1>, x32c_fwd_kernel<CELL_LSTM, 2>); break;
+      case CELL_GRU: e = launch(x32c_fwd_kernel<CELL_GRU, 1>, x32c_fwd_kernel<CELL_GRU, 2>); break;
+      case CELL_SLSTM: e = launch(x32c_fwd_kernel<CELL_SLSTM, 1>, x32c_fwd_kernel<CELL_SLSTM, 2>); break;
+      default:
+        e = pr.forward_clip > 0.f ? launch(x32c_fwd_kernel<CELL_ELMAN_CLIP, 1>, x32c_fwd_kernel<CELL_ELMAN_CLIP, 2>)
+                                  : launch(x32c_fwd_kernel<CELL_ELMAN, 1>, x32c_fwd_kernel<CELL_ELMAN, 2>);
+        break;
+    }
+  } else {
+    p.r_in_smem = fwd_smem(pr, d, true) <= kSmemMax;
+    const dim3 grid((unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
+    const size_t smem = fwd_smem(pr, d, p.r_in_smem != 0);
+    auto launch = [&](auto kern) -> cudaError_t {
+      cudaError_t s = set_smem(kern);
+      if (s != cudaSuccess) return s;
+      kern<<<grid, XTHREADS, smem, stream>>>(p);
+      return cudaGetLastError();
+    };
+    switch (pr.cell) {
+      case CELL_LSTM: e = launch(x32_fwd_kernel<CELL_LSTM>); break;
+      case CELL_GRU: e = launch(x32_fwd_kernel<CELL_GRU>); break;
+      case CELL_SLSTM: e = launch(x32_fwd_kernel<CELL_SLSTM>); break;
+      default: e = pr.forward_clip > 0.f ? launch(x32_fwd_kernel<CELL_ELMAN_CLIP>) : launch(x32_fwd_kernel<CELL_ELMAN>); break;
+    }
   }
   if (e != cudaSuccess) return (int)e;
   if (a->last) {  // states[:, :, T-1] -> last (may be the s0 buffer itself)
@@ -417,7 +921,8 @@ __attribute__((visibility("hidden"))) int frnn_forward_f32(const frnn_plan* plan
 
 __attribute__((visibility("hidden"))) int frnn_backward_parts_f32(const frnn_plan* plan, const frnn_bwd_args* a, void* stream_, int parts) {
   Dims d;
-  int rc = check(plan, &d);
+  Tile tl;
+  int rc = check(plan, &d, &tl);
   if (rc) return rc;
   const frnn_problem& pr = plan->prob;
   if (!pr.training) return FRNN_ERR_TRAINING;
@@ -449,19 +954,34 @@ __attribute__((visibility("hidden"))) int frnn_backward_parts_f32(const frnn_pla
     p.B = pr.B; p.T = pr.T; p.N = pr.N; p.D = pr.D;
     p.fclip = pr.forward_clip; p.gclip = pr.grad_clip; p.grad_cut = pr.grad_cut;
     p.ds_ss = dss[0]; p.ds_sb = dss[1]; p.ds_st = dss[2]; p.ds_sn = dss[3];
-    const dim3 grid((unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
-    const size_t smem = bwd_smem(pr, d);
-    auto launch = [&](auto kern) -> cudaError_t {
-      cudaError_t s = set_smem(kern);
-      if (s != cudaSuccess) return s;
-      kern<<<grid, XTHREADS, smem, stream>>>(p);
-      return cudaGetLastError();
-    };
-    switch (pr.cell) {
-      case CELL_LSTM: e = launch(x32_bwd_kernel<CELL_LSTM>); break;
-      case CELL_GRU: e = launch(x32_bwd_kernel<CELL_GRU>); break;
-      case CELL_SLSTM: e = launch(x32_bwd_kernel<CELL_SLSTM>); break;
-      default: e = pr.forward_clip > 0.f ? launch(x32_bwd_kernel<CELL_ELMAN_CLIP>) : launch(x32_bwd_kernel<CELL_ELMAN>); break;
+    p.status = reinterpret_cast<unsigned*>(ws);
+    if (tl.cluster) {
+      p.U = tl.u; p.CS = tl.cs; p.KS = tl.ksb; p.test_drop = plan->test_drop_exchange;
+      auto launch = [&](auto k1, auto k2) { return tl.ipt == 1 ? launch_cluster(k1, pr, tl, tl.smem_b, p, stream) : launch_cluster(k2, pr, tl, tl.smem_b, p, stream); };
+      switch (pr.cell) {
+        case CELL_LSTM: e = launch(x32c_bwd_kernel<CELL_LSTM, 1>, x32c_bwd_kernel<CELL_LSTM, 2>); break;
+        case CELL_GRU: e = launch(x32c_bwd_kernel<CELL_GRU, 1>, x32c_bwd_kernel<CELL_GRU, 2>); break;
+        case CELL_SLSTM: e = launch(x32c_bwd_kernel<CELL_SLSTM, 1>, x32c_bwd_kernel<CELL_SLSTM, 2>); break;
+        default:
+          e = pr.forward_clip > 0.f ? launch(x32c_bwd_kernel<CELL_ELMAN_CLIP, 1>, x32c_bwd_kernel<CELL_ELMAN_CLIP, 2>)
+                                    : launch(x32c_bwd_kernel<CELL_ELMAN, 1>, x32c_bwd_kernel<CELL_ELMAN, 2>);
+          break;
+      }
+    } else {
+      const dim3 grid((unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
+      const size_t smem = bwd_smem(pr, d);
+      auto launch = [&](auto kern) -> cudaError_t {
+        cudaError_t s = set_smem(kern);
+        if (s != cudaSuccess) return s;
+        kern<<<grid, XTHREADS, smem, stream>>>(p);
+        return cudaGetLastError();
+      };
+      switch (pr.cell) {
+        case CELL_LSTM: e = launch(x32_bwd_kernel<CELL_LSTM>); break;
+        case CELL_GRU: e = launch(x32_bwd_kernel<CELL_GRU>); break;
+        case CELL_SLSTM: e = launch(x32_bwd_kernel<CELL_SLSTM>); break;
+        default: e = pr.forward_clip > 0.f ? launch(x32_bwd_kernel<CELL_ELMAN_CLIP>) : launch(x32_bwd_kernel<CELL_ELMAN>); break;
+      }
     }
     if (e != cudaSuccess) return (int)e;
   }
@@ -486,7 +1006,8 @@ __attribute__((visibility("hidden"))) int frnn_backward_parts_f32(const frnn_pla
 
 __attribute__((visibility("hidden"))) int frnn_finalize_grads_f32(const frnn_plan* plan, const void* grads_f32, void* dR, void* db, void* stream_) {
   Dims d;
-  int rc = check(plan, &d);
+  Tile tl;
+  int rc = check(plan, &d, &tl);
   if (rc) return rc;
   if (!grads_f32 || !dR || !db) return FRNN_ERR_NULL;
   const frnn_problem& pr = plan->prob;

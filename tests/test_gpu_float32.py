@@ -86,3 +86,38 @@ def test_float32_options_layouts_and_stepper(cuda_device):
     for t in range(T):
         out = st.step(dev[0][:, t:t + 1].contiguous())
         assert max_abs(out.double().cpu().numpy(), ref["states"][:, :, t:t + 1]) <= 4 * TOL
+
+
+def test_float32_first_benchmark_configuration(cuda_device):
+    """LSTM float32 B4 T256 N2 D64, zero initial states, seed 0, loss = sum(h): the configuration the reference runs on
+    its CPU backend in float32, here in float32 on the GPU over all 256 steps."""
+    B, T, N, D = 4, 256, 2, 64
+    g = torch.Generator().manual_seed(0)
+    Wx = torch.randn(B, T, 4, N, D, generator=g).double()
+    R = (torch.randn(4, N, D, D, generator=g) / D ** 0.5).double()
+    b = (0.1 * torch.randn(4, N, D, generator=g)).double()
+    s0 = torch.zeros(2, B, 1, N, D, dtype=torch.float64)
+    got = run_native("lstm", Wx, R, b, s0, dtype=torch.float32)
+    ref = run_oracle("lstm", Wx, R, b, s0)
+    _check("lstm", got, ref, "C1")
+
+
+@pytest.mark.parametrize("function,D,cs", [("lstm", 64, 1), ("lstm", 64, 2), ("lstm", 64, 4), ("lstm", 64, 8), ("gru", 96, 3),
+                                           ("gru", 128, 0), ("slstm", 192, 0), ("elman", 128, 0), ("elman", 512, 0),
+                                           ("lstm", 128, 2), ("slstm", 128, 4), ("gru", 256, 0), ("lstm", 48, 1)])
+def test_float32_cluster_sizes(cuda_device, function, D, cs):
+    """The cluster loops at every cluster size (0 = the preferred one): exchange of h slices forward, of partial sums of
+    dh in the reverse loop; ragged batch (11 rows = one full and one partial tile)."""
+    from flashrnn_b200 import _native
+
+    B, T, N = 11, 10, 2
+    plan = _native.query(_native.make_problem(function, B, T, N, D, True, True, f32=True), cs, 0)
+    assert plan.cluster_size * plan.units_per_cta == D and (cs == 0 or plan.cluster_size == cs)
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=5 + D + cs, random_init=(function != "slstm"), dtype=torch.float32)
+    g = torch.Generator().manual_seed(9)
+    cot = torch.randn(s0.shape[0], B, T, N, D, generator=g, dtype=torch.float64).float().double()
+    if function == "slstm":
+        cot[1:] = 0
+    got = run_native(function, Wx, R, b, s0, cot=cot, dtype=torch.float32, cluster_size=cs)
+    ref = run_oracle(function, Wx, R, b, s0, cot=cot)
+    _check(function, got, ref, f"{function} D{D} cs{cs}", n_ds0=1 if function == "slstm" else None)
