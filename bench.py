@@ -312,7 +312,8 @@ class Job:
         self.stream = torch.cuda.current_stream(self.dev)
         self.sp = ctypes.c_void_p(self.stream.cuda_stream)
         self.f16 = args.dtype == "float16"
-        self.edt = torch.float16 if self.f16 else torch.bfloat16
+        self.f32io = args.dtype == "float32"  # the float32 loops (CUDA cores): everything, states included, fp32
+        self.edt = torch.float32 if self.f32io else (torch.float16 if self.f16 else torch.bfloat16)
         self.hbm_peak, self.tc_peak, self.peak_source = measured_peaks()
 
     def barrier(self, group=True):
@@ -336,11 +337,12 @@ def measure(job: Job, function, B, T, N, D, f32, *, allreduce, group=True, clust
     nv, L, dev, stream, sp, args = job.nv, job.L, job.dev, job.stream, job.sp, job.args
     min_seconds = args.min_seconds if min_seconds is None else min_seconds
     Gr, Gw, Gt, S = DIMS[function]
+    f32 = f32 or job.f32io
     Wx, R, b, s0 = make_inputs(function, B, T, N, D, f32, dev, seed=job.rank, edt=job.edt)
     sdt = torch.float32 if f32 else job.edt
-    esz, ssz = 2, (4 if f32 else 2)
+    esz, ssz = (4 if job.f32io else 2), (4 if f32 else 2)
     E = B * T * N * D
-    prob = nv.make_problem(function, B, T, N, D, f32, True, f16=job.f16)
+    prob = nv.make_problem(function, B, T, N, D, f32, True, f16=job.f16, f32=job.f32io)
     plan = nv.query(prob, cluster_size, batch_tile)
     states = torch.empty(S, B, T, N, D, device=dev, dtype=sdt)
     cache = torch.empty(max(16, int(plan.cache_bytes)), device=dev, dtype=torch.uint8)
@@ -447,7 +449,9 @@ def measure(job: Job, function, B, T, N, D, f32, *, allreduce, group=True, clust
             "forward_loop": {"achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9, "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / job.hbm_peak,
                              "algorithmic_bytes_per_launch": fwd_bytes},
             "whole_step": {"hbm_frac": (fwd_bytes + bwd_bytes) / (ms * 1e-3) / 1e9 / job.hbm_peak,
-                           "tensor_frac": (6.0 * E * Gr * D / (ms * 1e-3) / 1e12) / job.tc_peak},
+                           "tensor_frac": None if job.f32io else (6.0 * E * Gr * D / (ms * 1e-3) / 1e12) / job.tc_peak,
+                           # float32 loops: FFMA on the CUDA cores; nominal 148 SMs x 128 lanes x 2 flop x max SM clock
+                           "fp32_cuda_core_frac": (6.0 * E * Gr * D / (ms * 1e-3) / 1e12) / (148 * 128 * 2 * 1.965e-3) if job.f32io else None},
             "chain_floor": chain,
             "note": "streams one 16 KB tile per operand, step and CTA; HBM-bound" if wide else
                     "the serial chain of 2T dependent steps (chain_floor), not HBM or the tensor pipe, bounds this workload"},
@@ -519,7 +523,7 @@ def measure_e2e(job: Job, function, tensors, gcnt, allreduce):
         blocks.append(e2.elapsed_time(e3) / k2)
     e2e_ms = statistics.median(job.max_over_ranks(blocks))
     h2d = sum(t.numel() * t.element_size() for t in hostW)
-    d2h = host_out.numel() * 2 + 4
+    d2h = host_out.numel() * host_out.element_size() + 4
     # what the host side of this box delivers when all ranks copy at once: the same bytes, copies only
     job.barrier()
     c0, c1 = ev(), ev()
@@ -616,7 +620,7 @@ def run_ours(args):
     ms = head["ms_per_step"]
     value = tokens_per_s(B, T, tok_ranks, ms)
     roof = head["roofline"]
-    tr = NCU_TRAFFIC.get(args.workload) if (world == 1 and not args.cluster_size and not args.batch_tile and not job.f16) else None
+    tr = NCU_TRAFFIC.get(args.workload) if (world == 1 and not args.cluster_size and not args.batch_tile and not job.f16 and not job.f32io) else None
     if tr:
         roof["traffic"], roof["traffic_source"] = tr["bytes"], tr["source"]
     nsteps = args.steps * head["blocks"]
@@ -624,9 +628,9 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if by_heads else "weak",
         "vs_baseline": None,
-        "dtype": "f16" if job.f16 else "bf16", "data": "synthetic",
+        "dtype": "f32" if job.f32io else ("f16" if job.f16 else "bf16"), "data": "synthetic",
         "config": {"workload": f"{args.workload}: {function} fwd+bwd B={B} T={T} N={N} D={D} per GPU, loss=sum(h), "
-                               f"states {'f32' if f32 else ('f16' if job.f16 else 'bf16')}", "global_batch": tok_ranks * B,
+                               f"states {'f32' if (f32 or job.f32io) else ('f16' if job.f16 else 'bf16')}", "global_batch": tok_ranks * B,
                    "parallelism": (f"head-sharded x{world} ({N} of {N * world} heads per GPU), no collective" if by_heads else
                                    f"batch-sharded x{world}, NCCL all-reduce of fp32 dR||db") if world > 1 else "single GPU",
                    "tile": head["tile"],
@@ -669,8 +673,9 @@ def main():
     ap.add_argument("--min-seconds", dest="min_seconds", type=float, default=0.5,
                     help="length of the timed region per workload (blocks of --steps steps are repeated until it is reached; "
                          "0 = three blocks, for runs under a profiler)")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16"],
-                    help="16-bit element type of Wx/R/b/gradients (the baseline metric is quoted in bfloat16)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float16", "float32"],
+                    help="element type of Wx/R/b/gradients (the baseline metric is quoted in bfloat16; float32 = the "
+                         "accurate CUDA-core loops)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)

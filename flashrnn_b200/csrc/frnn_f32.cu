@@ -20,6 +20,8 @@
 #ifndef FRNN_F16  // compiled once, into the bfloat16 build, which owns the public entry points
 #define FRNN_NS_OVERRIDE frnn_x32
 #define FRNN_EXACT_ACT 1
+#include <type_traits>
+
 #include "../../include/frnn.h"
 #include "frnn_bwd.cuh"
 #include "frnn_fwd.cuh"
@@ -208,21 +210,36 @@ __global__ void __launch_bounds__(XTHREADS) x32_bwd_kernel(const XParams p) {
 // ================================================================================================ cluster loops
 // Shared memory of the forward loop (floats): Rs[D][Gr*U] | h[2][D][8] | part[KS][8][Gr*U] | 2 mbarriers + flag
 // Rs[k][g*U + u] = R[g][n][unit0 + u][k];  h[x][k][b] = h of unit k, batch row b (CTA c's slice = rows c*U .. c*U+U-1)
-template <int CELL, int IPT>
+// BT consecutive floats (one k, all batch rows of the tile)
+template <int BT> __device__ __forceinline__ void load_row(const float* q, float (&v)[BT]) {
+  if constexpr (BT == 8) {
+    const float4 a = *reinterpret_cast<const float4*>(q), b = *reinterpret_cast<const float4*>(q + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else if constexpr (BT == 4) {
+    const float4 a = *reinterpret_cast<const float4*>(q);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+  } else {
+    const float2 a = *reinterpret_cast<const float2*>(q);
+    v[0] = a.x; v[1] = a.y;
+  }
+}
+
+// BT = batch rows per cluster (8, 4 or 2: small batches are cut into more tiles so that more SMs take part)
+template <int CELL, int IPT, int BT>
 __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, GCA = GC > 0 ? GC : 1;
   extern __shared__ __align__(16) float sm[];
   const int D = p.D, U = p.U, CS = p.CS, KS = p.KS, GU = Gr * U, T = p.T, B = p.B, N = p.N;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int n = blockIdx.z, b0 = blockIdx.y * XBT;
+  const int n = blockIdx.z, b0 = blockIdx.y * BT;
   const uint32_t crank = CS > 1 ? cluster_ctarank() : 0u;
   const int unit0 = (int)crank * U;
   const size_t ND = (size_t)N * D;
   float* Rs = sm;
   float* hbuf = Rs + (size_t)D * GU;
-  float* part = hbuf + 2 * XBT * D;
-  uint64_t* full = reinterpret_cast<uint64_t*>(part + (size_t)KS * XBT * GU);
+  float* part = hbuf + 2 * BT * D;
+  uint64_t* full = reinterpret_cast<uint64_t*>(part + (size_t)KS * BT * GU);
   volatile int* gave_up = reinterpret_cast<volatile int*>(full + 2);
 
   {  // this CTA's slice of R, from the transposed copy RT[n][k][g*D + d]
@@ -242,7 +259,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int q = tid + i * XTHREADS;
-    it_on[i] = q < XBT * U;
+    it_on[i] = q < BT * U;
     bl_[i] = it_on[i] ? q / U : 0;
     u_[i] = it_on[i] ? q - bl_[i] * U : 0;
     const int bg = b0 + bl_[i], d = unit0 + u_[i];
@@ -261,11 +278,11 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
     wx_p[i] += p.wx_st;
   }
   // ---- h_{-1} of the whole head -> h[0] (read straight from global by every CTA)
-  for (int i = tid; i < XBT * D; i += XTHREADS) {
+  for (int i = tid; i < BT * D; i += XTHREADS) {
     const int bl = i / D, k = i - bl * D, b = b0 + bl;
-    hbuf[k * XBT + bl] = b < B ? p.s0[(size_t)b * ND + (size_t)n * D + k] : 0.f;
+    hbuf[k * BT + bl] = b < B ? p.s0[(size_t)b * ND + (size_t)n * D + k] : 0.f;
   }
-  const uint32_t slice_bytes = (uint32_t)(U * XBT * 4);
+  const uint32_t slice_bytes = (uint32_t)(U * BT * 4);
   const uint32_t expect_bytes = (uint32_t)(CS - 1) * slice_bytes;
   bool poisoned = false;
   if (CS > 1) {
@@ -282,8 +299,8 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
   } else {
     __syncthreads();
   }
-  const uint32_t my_slice0 = smem_u32(hbuf + (size_t)unit0 * XBT);
-  const uint32_t buf_bytes = (uint32_t)(XBT * D * 4);
+  const uint32_t my_slice0 = smem_u32(hbuf + (size_t)unit0 * BT);
+  const uint32_t buf_bytes = (uint32_t)(BT * D * 4);
   const uint32_t full_u32 = smem_u32(&full[0]);
   const int nrp = GU >> 1, nwork = nrp * KS, KQ = (D + KS - 1) / KS;
 
@@ -311,29 +328,28 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
     }
     // ---------------- matrix phase: part[kc][b][row] = sum over this thread's k of R[row][k] * h_{t-1}[b][k]
     {
-      const float* hcur = hbuf + (size_t)cur * XBT * D;
+      const float* hcur = hbuf + (size_t)cur * BT * D;
       for (int w = tid; w < nwork; w += XTHREADS) {
         const int kc = w / nrp, rp = w - kc * nrp;
         const int k0 = kc * KQ, k1 = (k0 + KQ < D) ? k0 + KQ : D;
-        float acc[2][XBT];
+        float acc[2][BT];
 #pragma unroll
-        for (int b = 0; b < XBT; ++b) acc[0][b] = acc[1][b] = 0.f;
+        for (int b = 0; b < BT; ++b) acc[0][b] = acc[1][b] = 0.f;
         const float* rr = Rs + 2 * rp;
 #pragma unroll 4
         for (int k = k0; k < k1; ++k) {
           const float2 r = *reinterpret_cast<const float2*>(rr + (size_t)k * GU);
-          const float4 ha = *reinterpret_cast<const float4*>(hcur + k * XBT);
-          const float4 hb = *reinterpret_cast<const float4*>(hcur + k * XBT + 4);
-          const float hv[XBT] = {ha.x, ha.y, ha.z, ha.w, hb.x, hb.y, hb.z, hb.w};
+          float hv[BT];
+          load_row<BT>(hcur + k * BT, hv);
 #pragma unroll
-          for (int b = 0; b < XBT; ++b) {
+          for (int b = 0; b < BT; ++b) {
             acc[0][b] = fmaf(r.x, hv[b], acc[0][b]);
             acc[1][b] = fmaf(r.y, hv[b], acc[1][b]);
           }
         }
 #pragma unroll
-        for (int b = 0; b < XBT; ++b)
-          *reinterpret_cast<float2*>(part + ((size_t)kc * XBT + b) * GU + 2 * rp) = make_float2(acc[0][b], acc[1][b]);
+        for (int b = 0; b < BT; ++b)
+          *reinterpret_cast<float2*>(part + ((size_t)kc * BT + b) * GU + 2 * rp) = make_float2(acc[0][b], acc[1][b]);
       }
     }
     __syncthreads();
@@ -341,7 +357,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
     const int quit = (CS > 1) ? *gave_up : 0;
     // ---------------- cell phase: this thread's items; new h into this CTA's slice of h[nxt]
     float cch[IPT][GCA];
-    float* hdst = hbuf + (size_t)nxt * XBT * D + (size_t)unit0 * XBT;
+    float* hdst = hbuf + (size_t)nxt * BT * D + (size_t)unit0 * BT;
 #pragma unroll
     for (int i = 0; i < IPT; ++i) {
       if (!it_on[i]) continue;
@@ -349,7 +365,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
 #pragma unroll
       for (int g = 0; g < Gr; ++g) prv[g] = 0.f;
       for (int kc = 0; kc < KS; ++kc) {
-        const float* pp = part + ((size_t)kc * XBT + bl_[i]) * GU + u_[i];
+        const float* pp = part + ((size_t)kc * BT + bl_[i]) * GU + u_[i];
 #pragma unroll
         for (int g = 0; g < Gr; ++g) prv[g] += pp[g * U];
       }
@@ -359,7 +375,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
 #pragma unroll
         for (int s = 0; s < S; ++s) st[i][s] = 0.f;
       }
-      hdst[u_[i] * XBT + bl_[i]] = st[i][0];
+      hdst[u_[i] * BT + bl_[i]] = st[i][0];
     }
     if (CS > 1) fence_proxy_async_smem();  // make the slice visible to the bulk-copy engine
     __syncthreads();
@@ -391,21 +407,21 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
 // dbs[Gt][U] | 2 mbarriers + flag, MSG = KS*8*U.  Rb[g*U + u][p] = R[g][n][unit0 + u][p].
 // Reduce-scatter: CTA c multiplies ITS deltas with its rows of R for all D columns p and sends the owner of p the
 // partial sums; message for CTA x: [kc][b][u] with p = x*U + u (the CTA's own part goes straight into its recv slot).
-template <int CELL, int IPT>
+template <int CELL, int IPT, int BT>
 __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) {
   using C = Cell<CELL>;
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, GCA = GC > 0 ? GC : 1, NNEED = C::NNEED, NEXT = C::NEXT;
   extern __shared__ __align__(16) float sm[];
   const int D = p.D, U = p.U, CS = p.CS, KS = p.KS, GU = Gr * U, T = p.T, B = p.B, N = p.N;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int n = blockIdx.z, b0 = blockIdx.y * XBT;
+  const int n = blockIdx.z, b0 = blockIdx.y * BT;
   const uint32_t crank = CS > 1 ? cluster_ctarank() : 0u;
   const int unit0 = (int)crank * U;
   const size_t ND = (size_t)N * D;
-  const int MSG = KS * XBT * U;
+  const int MSG = KS * BT * U;
   float* Rb = sm;
   float* delta = Rb + (size_t)GU * D;
-  float* send = delta + GU * XBT;
+  float* send = delta + GU * BT;
   float* recv = send + 2 * CS * MSG;
   float* dbs = recv + 2 * CS * MSG;
   uint64_t* full = reinterpret_cast<uint64_t*>(dbs + Gt * U);
@@ -430,7 +446,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
 #pragma unroll
   for (int i = 0; i < IPT; ++i) {
     const int q = tid + i * XTHREADS;
-    it_on[i] = q < XBT * U;
+    it_on[i] = q < BT * U;
     bl_[i] = it_on[i] ? q / U : 0;
     u_[i] = it_on[i] ? q - bl_[i] * U : 0;
     const int bg = b0 + bl_[i], d = unit0 + u_[i];
@@ -482,14 +498,14 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
     __syncthreads();
   }
   const uint32_t full_u32 = smem_u32(&full[0]);
-  const int KQ = (GU + KS - 1) / KS, nwork = D * KS;
+  const int KQ = (GU + KS - 1) / KS, hD = D >> 1, nwork = hD * KS;
 
   // sum of the partial sums that arrived for item i in buffer x
   auto gather = [&](int i, int x) {
     float r = 0.f;
     for (int c = 0; c < CS; ++c) {
       const float* q = recv + ((size_t)x * CS + c) * MSG + bl_[i] * U + u_[i];
-      for (int kc = 0; kc < KS; ++kc) r += q[(size_t)kc * XBT * U];
+      for (int kc = 0; kc < KS; ++kc) r += q[(size_t)kc * BT * U];
     }
     return r;
   };
@@ -554,7 +570,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
         for (int g = 0; g < Gt; ++g) dbacc[i][g] += dB_[g];
       }
 #pragma unroll
-      for (int g = 0; g < Gr; ++g) delta[(g * U + u_[i]) * XBT + bl_[i]] = dR_[g];
+      for (int g = 0; g < Gr; ++g) delta[(g * U + u_[i]) * BT + bl_[i]] = dR_[g];
 #pragma unroll
       for (int k = 0; k < NNEED; ++k) { cur[i][k] = prv[i][k]; prv[i][k] = prv_n[i][k]; }
 #pragma unroll
@@ -567,26 +583,29 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
     if (exch) {
       // ---------------- matrix phase: partial dh_{t-1}[b][p] = sum over this thread's (g, u) of delta[b][g,u] * R[g][u][p]
       for (int w = tid; w < nwork; w += XTHREADS) {
-        const int kc = w / D, pc = w - kc * D;
+        const int kc = w / hD, pc = 2 * (w - kc * hD);  // columns pc, pc + 1 (same owner: U is even)
         const int j0 = kc * KQ, j1 = (j0 + KQ < GU) ? j0 + KQ : GU;
-        float acc[XBT];
+        float acc[2][BT];
 #pragma unroll
-        for (int b = 0; b < XBT; ++b) acc[b] = 0.f;
+        for (int b = 0; b < BT; ++b) acc[0][b] = acc[1][b] = 0.f;
         const float* rr = Rb + pc;
 #pragma unroll 4
         for (int jj = j0; jj < j1; ++jj) {
-          const float r = rr[(size_t)jj * D];
-          const float4 da = *reinterpret_cast<const float4*>(delta + jj * XBT);
-          const float4 db4 = *reinterpret_cast<const float4*>(delta + jj * XBT + 4);
-          acc[0] = fmaf(r, da.x, acc[0]); acc[1] = fmaf(r, da.y, acc[1]); acc[2] = fmaf(r, da.z, acc[2]); acc[3] = fmaf(r, da.w, acc[3]);
-          acc[4] = fmaf(r, db4.x, acc[4]); acc[5] = fmaf(r, db4.y, acc[5]); acc[6] = fmaf(r, db4.z, acc[6]); acc[7] = fmaf(r, db4.w, acc[7]);
+          const float2 r = *reinterpret_cast<const float2*>(rr + (size_t)jj * D);
+          float dv[BT];
+          load_row<BT>(delta + jj * BT, dv);
+#pragma unroll
+          for (int b = 0; b < BT; ++b) {
+            acc[0][b] = fmaf(r.x, dv[b], acc[0][b]);
+            acc[1][b] = fmaf(r.y, dv[b], acc[1][b]);
+          }
         }
         const int c = pc / U, u = pc - c * U;
         // the owner's slot: recv[buf][crank] over there; the message leaves from send[buf][c], the own part stays here
         float* dst = ((uint32_t)c == crank ? recv + ((size_t)buf * CS + crank) * MSG : send + ((size_t)buf * CS + c) * MSG) +
-                     (size_t)kc * XBT * U + u;
+                     (size_t)kc * BT * U + u;
 #pragma unroll
-        for (int b = 0; b < XBT; ++b) dst[b * U] = acc[b];
+        for (int b = 0; b < BT; ++b) *reinterpret_cast<float2*>(dst + b * U) = make_float2(acc[0][b], acc[1][b]);
       }
       if (CS > 1) fence_proxy_async_smem();
       __syncthreads();
@@ -631,64 +650,97 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
   if (CS > 1) { cluster_arrive(); cluster_wait(); }
 }
 
-// dR[g][n][d][p] += sum over this CTA's rows k = (b, t) of delta_g[k][d] * h_{t-1}[k][p]: 64 x 64 tile of ((g, d), p)
+// dR[g][n][d][p] += sum over this CTA's rows k = (b, t) of delta_g[k][d] * h_{t-1}[k][p]: a 128 x 64 tile of ((g, d), p),
+// 8 x 4 sums per thread, 16 rows of k per stage (the next stage's global loads are in flight while this one is multiplied),
+// split-K over the grid's z, fp32 atomics at the end.
 struct XDrParams {
   const float* dWx; const float* dg0; const float* states; const float* s0; float* dR;
   int cell, B, T, N, D, Gr, Gw;
   long long K;
   int rows_per_split;
 };
+constexpr int DR_M = 128, DR_P = 64, DR_K = 16;
 __global__ void __launch_bounds__(XTHREADS) x32_dr_kernel(const XDrParams p) {
-  __shared__ float As[32][65], Hs[32][65];
+  __shared__ __align__(16) float As[2][DR_K][DR_M];
+  __shared__ __align__(16) float Hs[2][DR_K][DR_P];
   const int D = p.D, N = p.N, T = p.T, GD = p.Gr * D;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const int m0 = blockIdx.x * 64, p0 = blockIdx.y * 64;
+  const int m0 = blockIdx.x * DR_M, p0 = blockIdx.y * DR_P;
   const int n = blockIdx.z % N, split = blockIdx.z / N;
   const size_t ND = (size_t)N * D;
   const long long k0 = (long long)split * p.rows_per_split;
   long long k1 = k0 + p.rows_per_split;
   if (k1 > p.K) k1 = p.K;
-  float acc[4][4];
+  // global -> register staging: thread loads A chunks (kk = tid / 32 + {0, 8}, 4 columns at (tid % 32) * 4) and one H chunk
+  const int a_kk = tid >> 5, a_c = (tid & 31) * 4;
+  const int h_kk = tid >> 4, h_c = (tid & 15) * 4;
+  const float* a_src[2];  // per A chunk: address of (k = 0) or null when the column is outside the matrix
+  {
+    const int m = m0 + a_c;
+    const float* base = nullptr;
+    if (m < GD) {
+      const int g = m / D, d = m - g * D;
+      if (p.cell == CELL_GRU && g == 0) base = p.dg0 + (size_t)n * D + d;
+      else base = p.dWx + (size_t)(p.cell == CELL_GRU ? g - 1 : g) * ND + (size_t)n * D + d;
+    }
+    a_src[0] = a_src[1] = base;
+  }
+  const bool a_dg0 = p.cell == CELL_GRU && (m0 + a_c) < D;
+  const size_t a_row = a_dg0 ? ND : (size_t)p.Gw * ND;  // floats between rows k and k+1
+  const bool h_on = p0 + h_c < D;
+  float4 ra[2], rh;
+  auto fetch = [&](long long kc) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 2; ++i) {
+      const long long k = kc + a_kk + 8 * i;
+      ra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < k1 && a_src[i] != nullptr) ra[i] = *reinterpret_cast<const float4*>(a_src[i] + (size_t)k * a_row);
+    }
+    const long long k = kc + h_kk;
+    rh = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (k < k1 && h_on) {
+      const long long b = k / T;
+      const int tt = (int)(k - b * T);
+      const float* src = tt > 0 ? p.states + (size_t)(k - 1) * ND : p.s0 + (size_t)b * ND;
+      rh = *reinterpret_cast<const float4*>(src + (size_t)n * D + p0 + h_c);
+    }
+  };
+  auto stash = [&](int s) {
+    *reinterpret_cast<float4*>(&As[s][a_kk][a_c]) = ra[0];
+    *reinterpret_cast<float4*>(&As[s][a_kk + 8][a_c]) = ra[1];
+    *reinterpret_cast<float4*>(&Hs[s][h_kk][h_c]) = rh;
+  };
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-  for (long long kc = k0; kc < k1; kc += 32) {
-    for (int i = tid; i < 32 * 64; i += XTHREADS) {
-      const int kk = i >> 6, c = i & 63;
-      const long long k = kc + kk;
-      float a = 0.f, hv = 0.f;
-      if (k < k1) {
-        const long long b = k / T;
-        const int t = (int)(k - b * T);
-        const int m = m0 + c;
-        if (m < GD) {
-          const int g = m / D, d = m - g * D;
-          if (p.cell == CELL_GRU && g == 0) a = p.dg0[(size_t)k * ND + (size_t)n * D + d];
-          else a = p.dWx[((size_t)k * p.Gw + (p.cell == CELL_GRU ? g - 1 : g)) * ND + (size_t)n * D + d];
-        }
-        const int pc = p0 + c;
-        if (pc < D) hv = t > 0 ? p.states[(size_t)(k - 1) * ND + (size_t)n * D + pc] : p.s0[(size_t)b * ND + (size_t)n * D + pc];
-      }
-      As[kk][c] = a;
-      Hs[kk][c] = hv;
-    }
-    __syncthreads();
-#pragma unroll 8
-    for (int kk = 0; kk < 32; ++kk) {
-      float a[4], hh[4];
+  fetch(k0);
+  stash(0);
+  __syncthreads();
+  int s = 0;
+  for (long long kc = k0; kc < k1; kc += DR_K) {
+    const bool more = kc + DR_K < k1;
+    if (more) fetch(kc + DR_K);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; hh[i] = Hs[kk][tx * 4 + i]; }
+    for (int kk = 0; kk < DR_K; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[s][kk][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[s][kk][64 + ty * 4]);
+      const float4 h4 = *reinterpret_cast<const float4*>(&Hs[s][kk][tx * 4]);
+      const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float hh[4] = {h4.x, h4.y, h4.z, h4.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], hh[j], acc[i][j]);
     }
+    if (more) stash(s ^ 1);
     __syncthreads();
+    s ^= 1;
   }
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int m = m0 + ty * 4 + i;
+  for (int i = 0; i < 8; ++i) {
+    const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
     if (m >= GD) continue;
     const int g = m / D, d = m - g * D;
 #pragma unroll
@@ -729,36 +781,48 @@ size_t bwd_smem(const frnn_problem& pr, const Dims& d) {
 }
 // Geometry of the loops for a cluster size: U units per CTA, k-splits of the two matrix phases, items per thread.
 // `cluster` false = the streamed loops (one CTA per head, R from L2).
-struct Tile { int cs, u, ksf, ksb, ipt; bool cluster; size_t smem_f, smem_b; };
+struct Tile { int cs, u, bt, ksf, ksb, ipt; bool cluster; size_t smem_f, smem_b; };
 int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
-bool cluster_tile(const frnn_problem& pr, const Dims& d, int cs, Tile* t) {
+// Clusters of one CTA per SM that a B200 (148 SMs in GPCs of unequal size) keeps resident at once, by cluster size, as
+// cudaOccupancyMaxActiveClusters reports it for these kernels' footprint (sizes 5 and 7: not measured, rounded down).
+constexpr int kResidentClusters[9] = {0, 148, 74, 45, 33, 26, 22, 17, 15};
+// bt == 0: the smallest batch tile (8, 4, 2 rows) whose clusters are still all resident at once -- within one wave the
+// step time falls with the rows per CTA, beyond it the tiles queue up (LSTM B16 N4 D256: 16 clusters of 8 ran 25 % slower
+// than 8 clusters of twice the rows)
+bool cluster_tile(const frnn_problem& pr, const Dims& d, int cs, int bt, Tile* t) {
   if (cs < 1 || cs > 8 || pr.D % cs) return false;
+  if (bt != 0 && bt != 8 && bt != 4 && bt != 2) return false;
+  if (bt == 0) {
+    bt = 8;
+    while (bt > 2 && (long long)((pr.B + bt / 2 - 1) / (bt / 2)) * pr.N <= kResidentClusters[cs]) bt /= 2;
+  }
   const int u = pr.D / cs;
   if (u % 4 || u > 64) return false;
   const size_t gu = (size_t)d.Gr * u, D = (size_t)pr.D;
-  t->cs = cs; t->u = u; t->cluster = true;
+  t->cs = cs; t->u = u; t->bt = bt; t->cluster = true;
   t->ksf = clampi((int)(512 / gu), 1, 8);
-  t->ksb = clampi(256 / pr.D, 1, 8);
-  t->ipt = XBT * u > XTHREADS ? 2 : 1;
-  t->smem_f = (D * gu + 2 * XBT * D + (size_t)t->ksf * XBT * gu) * 4 + 64;
-  t->smem_b = (gu * D + gu * XBT + (size_t)4 * t->ksb * XBT * D + (size_t)d.Gt * u) * 4 + 64;
+  t->ksb = clampi(512 / pr.D, 1, 8);
+  t->ipt = bt * u > XTHREADS ? 2 : 1;
+  t->smem_f = (D * gu + 2 * bt * D + (size_t)t->ksf * bt * gu) * 4 + 64;
+  t->smem_b = (gu * D + gu * bt + (size_t)4 * t->ksb * bt * D + (size_t)d.Gt * u) * 4 + 64;
   return t->smem_f <= kSmemMax && t->smem_b <= kSmemMax;
 }
 // cs == 0: the preferred tile -- the whole head in one CTA up to head dim 64, else the smallest cluster with at most 32
 // units per CTA, else the smallest cluster that fits, else the streamed loops.  cs > 0: that cluster size or nothing
 // (cs == 1 falls back to the streamed loops when the head does not fit one CTA).
-bool pick_tile(const frnn_problem& pr, const Dims& d, int cs, Tile* t) {
+bool pick_tile(const frnn_problem& pr, const Dims& d, int cs, int bt, Tile* t) {
   if (cs > 0) {
-    if (cluster_tile(pr, d, cs, t)) return true;
+    if (cluster_tile(pr, d, cs, bt, t)) return true;
     if (cs != 1) return false;
   } else {
-    if (pr.D <= 64 && cluster_tile(pr, d, 1, t)) return true;
+    if (pr.D <= 64 && cluster_tile(pr, d, 1, bt, t)) return true;
     for (int c = 1; c <= 8; ++c)
-      if (cluster_tile(pr, d, c, t) && t->u <= 32) return true;
+      if (cluster_tile(pr, d, c, bt, t) && t->u <= 32) return true;
     for (int c = 1; c <= 8; ++c)
-      if (cluster_tile(pr, d, c, t)) return true;
+      if (cluster_tile(pr, d, c, bt, t)) return true;
   }
-  *t = Tile{1, pr.D, 0, 0, 0, false, fwd_smem(pr, d, false), bwd_smem(pr, d)};
+  if (bt != 0 && bt != XBT) return false;  // the streamed loops work on 8 rows
+  *t = Tile{1, pr.D, XBT, 0, 0, 0, false, fwd_smem(pr, d, false), bwd_smem(pr, d)};
   return t->smem_f <= kSmemMax && t->smem_b <= kSmemMax;
 }
 int validate(const frnn_problem* pr, Dims* d) {
@@ -768,7 +832,7 @@ int validate(const frnn_problem* pr, Dims* d) {
   if (pr->B < 1 || pr->T < 1 || pr->N < 1 || pr->N > 65535 || pr->D < 4 || pr->D > 1024 || pr->D % 4) return FRNN_ERR_SHAPE;
   if ((pr->B + XBT - 1) / XBT > 65535) return FRNN_ERR_SHAPE;
   Tile t;
-  if (!pick_tile(*pr, *d, 0, &t)) return FRNN_ERR_SHAPE;
+  if (!pick_tile(*pr, *d, 0, 0, &t)) return FRNN_ERR_SHAPE;
   return FRNN_OK;
 }
 int check(const frnn_plan* pl, Dims* d, Tile* t) {
@@ -776,7 +840,7 @@ int check(const frnn_plan* pl, Dims* d, Tile* t) {
   if (pl->abi_version != FRNN_ABI_VERSION) return FRNN_ERR_PLAN;
   const int rc = validate(&pl->prob, d);
   if (rc) return rc;
-  if (!pick_tile(pl->prob, *d, pl->cluster_size, t) || pl->batch_tile != XBT || pl->threads != XTHREADS ||
+  if (!pick_tile(pl->prob, *d, pl->cluster_size, pl->batch_tile, t) || pl->threads != XTHREADS ||
       pl->units_per_cta != t->u || pl->workspace_bytes != ws_layout(pl->prob, *d).total || pl->probe_noop_cell)
     return FRNN_ERR_PLAN;
   return FRNN_OK;
@@ -786,7 +850,7 @@ cudaError_t launch_cluster(K kern, const frnn_problem& pr, const Tile& t, size_t
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemMax);  // fixed maximum
   if (e != cudaSuccess) return e;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)t.cs, (unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
+  cfg.gridDim = dim3((unsigned)t.cs, (unsigned)((pr.B + t.bt - 1) / t.bt), (unsigned)pr.N);
   cfg.blockDim = dim3(XTHREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -824,15 +888,15 @@ __attribute__((visibility("hidden"))) int frnn_query_f32(const frnn_problem* pr,
   const int rc = validate(pr, &d);
   if (rc) return rc;
   if (!out) return FRNN_ERR_NULL;
-  if ((bt && bt != XBT) || stages) return FRNN_ERR_PLAN;  // 8 batch rows per CTA, no input ring
+  if (stages) return FRNN_ERR_PLAN;  // no input ring
   Tile tl;
-  if (!pick_tile(*pr, d, cs, &tl)) return FRNN_ERR_PLAN;
+  if (!pick_tile(*pr, d, cs, bt, &tl)) return FRNN_ERR_PLAN;
   frnn_plan pl = {};
   pl.abi_version = FRNN_ABI_VERSION;
   pl.prob = *pr;
   pl.cluster_size = tl.cs;
   pl.units_per_cta = tl.u;
-  pl.batch_tile = XBT;
+  pl.batch_tile = tl.bt;
   pl.threads = XTHREADS;
   pl.wx_stages = 0;
   pl.cache_slots = d.GC;
@@ -883,14 +947,20 @@ __attribute__((visibility("hidden"))) int frnn_forward_f32(const frnn_plan* plan
   p.wx_sb = wxs[0]; p.wx_st = wxs[1]; p.wx_sg = wxs[2]; p.wx_sn = wxs[3];
   if (tl.cluster) {
     p.U = tl.u; p.CS = tl.cs; p.KS = tl.ksf; p.test_drop = plan->test_drop_exchange;
-    auto launch = [&](auto k1, auto k2) { return tl.ipt == 1 ? launch_cluster(k1, pr, tl, tl.smem_f, p, stream) : launch_cluster(k2, pr, tl, tl.smem_f, p, stream); };
+    auto launch = [&](auto cell) {
+      constexpr int CL = decltype(cell)::value;
+      if (tl.ipt == 2) return launch_cluster(x32c_fwd_kernel<CL, 2, 8>, pr, tl, tl.smem_f, p, stream);
+      if (tl.bt == 8) return launch_cluster(x32c_fwd_kernel<CL, 1, 8>, pr, tl, tl.smem_f, p, stream);
+      if (tl.bt == 4) return launch_cluster(x32c_fwd_kernel<CL, 1, 4>, pr, tl, tl.smem_f, p, stream);
+      return launch_cluster(x32c_fwd_kernel<CL, 1, 2>, pr, tl, tl.smem_f, p, stream);
+    };
+    using std::integral_constant;
     switch (pr.cell) {
-      case CELL_LSTM: e = launch(x32c_fwd_kernel<CELL_LSTM, 1>, x32c_fwd_kernel<CELL_LSTM, 2>); break;
-      case CELL_GRU: e = launch(x32c_fwd_kernel<CELL_GRU, 1>, x32c_fwd_kernel<CELL_GRU, 2>); break;
-      case CELL_SLSTM: e = launch(x32c_fwd_kernel<CELL_SLSTM, 1>, x32c_fwd_kernel<CELL_SLSTM, 2>); break;
+      case CELL_LSTM: e = launch(integral_constant<int, CELL_LSTM>{}); break;
+      case CELL_GRU: e = launch(integral_constant<int, CELL_GRU>{}); break;
+      case CELL_SLSTM: e = launch(integral_constant<int, CELL_SLSTM>{}); break;
       default:
-        e = pr.forward_clip > 0.f ? launch(x32c_fwd_kernel<CELL_ELMAN_CLIP, 1>, x32c_fwd_kernel<CELL_ELMAN_CLIP, 2>)
-                                  : launch(x32c_fwd_kernel<CELL_ELMAN, 1>, x32c_fwd_kernel<CELL_ELMAN, 2>);
+        e = pr.forward_clip > 0.f ? launch(integral_constant<int, CELL_ELMAN_CLIP>{}) : launch(integral_constant<int, CELL_ELMAN>{});
         break;
     }
   } else {
@@ -957,16 +1027,22 @@ __attribute__((visibility("hidden"))) int frnn_backward_parts_f32(const frnn_pla
     p.status = reinterpret_cast<unsigned*>(ws);
     if (tl.cluster) {
       p.U = tl.u; p.CS = tl.cs; p.KS = tl.ksb; p.test_drop = plan->test_drop_exchange;
-      auto launch = [&](auto k1, auto k2) { return tl.ipt == 1 ? launch_cluster(k1, pr, tl, tl.smem_b, p, stream) : launch_cluster(k2, pr, tl, tl.smem_b, p, stream); };
-      switch (pr.cell) {
-        case CELL_LSTM: e = launch(x32c_bwd_kernel<CELL_LSTM, 1>, x32c_bwd_kernel<CELL_LSTM, 2>); break;
-        case CELL_GRU: e = launch(x32c_bwd_kernel<CELL_GRU, 1>, x32c_bwd_kernel<CELL_GRU, 2>); break;
-        case CELL_SLSTM: e = launch(x32c_bwd_kernel<CELL_SLSTM, 1>, x32c_bwd_kernel<CELL_SLSTM, 2>); break;
-        default:
-          e = pr.forward_clip > 0.f ? launch(x32c_bwd_kernel<CELL_ELMAN_CLIP, 1>, x32c_bwd_kernel<CELL_ELMAN_CLIP, 2>)
-                                    : launch(x32c_bwd_kernel<CELL_ELMAN, 1>, x32c_bwd_kernel<CELL_ELMAN, 2>);
-          break;
-      }
+      auto launch = [&](auto cell) {
+      constexpr int CL = decltype(cell)::value;
+      if (tl.ipt == 2) return launch_cluster(x32c_bwd_kernel<CL, 2, 8>, pr, tl, tl.smem_b, p, stream);
+      if (tl.bt == 8) return launch_cluster(x32c_bwd_kernel<CL, 1, 8>, pr, tl, tl.smem_b, p, stream);
+      if (tl.bt == 4) return launch_cluster(x32c_bwd_kernel<CL, 1, 4>, pr, tl, tl.smem_b, p, stream);
+      return launch_cluster(x32c_bwd_kernel<CL, 1, 2>, pr, tl, tl.smem_b, p, stream);
+    };
+    using std::integral_constant;
+    switch (pr.cell) {
+      case CELL_LSTM: e = launch(integral_constant<int, CELL_LSTM>{}); break;
+      case CELL_GRU: e = launch(integral_constant<int, CELL_GRU>{}); break;
+      case CELL_SLSTM: e = launch(integral_constant<int, CELL_SLSTM>{}); break;
+      default:
+        e = pr.forward_clip > 0.f ? launch(integral_constant<int, CELL_ELMAN_CLIP>{}) : launch(integral_constant<int, CELL_ELMAN>{});
+        break;
+    }
     } else {
       const dim3 grid((unsigned)((pr.B + XBT - 1) / XBT), (unsigned)pr.N);
       const size_t smem = bwd_smem(pr, d);
@@ -991,12 +1067,12 @@ __attribute__((visibility("hidden"))) int frnn_backward_parts_f32(const frnn_pla
     q.states = static_cast<const float*>(a->states); q.s0 = static_cast<const float*>(a->s0); q.dR = grads;
     q.cell = pr.cell; q.B = pr.B; q.T = pr.T; q.N = pr.N; q.D = pr.D; q.Gr = d.Gr; q.Gw = d.Gw;
     q.K = (long long)pr.B * pr.T;
-    const int mt = (d.Gr * pr.D + 63) / 64, pt = (pr.D + 63) / 64;
+    const int mt = (d.Gr * pr.D + DR_M - 1) / DR_M, pt = (pr.D + DR_P - 1) / DR_P;
     long long splits = 592 / ((long long)mt * pt * pr.N);  // about four CTAs per SM
     if (splits < 1) splits = 1;
     if (splits > (q.K + 127) / 128) splits = (q.K + 127) / 128;
     if ((long long)pr.N * splits > 65535) splits = 65535 / pr.N;
-    q.rows_per_split = (int)(((q.K + splits - 1) / splits + 31) / 32 * 32);
+    q.rows_per_split = (int)(((q.K + splits - 1) / splits + DR_K - 1) / DR_K * DR_K);
     splits = (q.K + q.rows_per_split - 1) / q.rows_per_split;
     x32_dr_kernel<<<dim3((unsigned)mt, (unsigned)pt, (unsigned)(pr.N * splits)), XTHREADS, 0, stream>>>(q);
     e = cudaGetLastError();

@@ -102,22 +102,23 @@ def test_float32_first_benchmark_configuration(cuda_device):
     _check("lstm", got, ref, "C1")
 
 
-@pytest.mark.parametrize("function,D,cs", [("lstm", 64, 1), ("lstm", 64, 2), ("lstm", 64, 4), ("lstm", 64, 8), ("gru", 96, 3),
-                                           ("gru", 128, 0), ("slstm", 192, 0), ("elman", 128, 0), ("elman", 512, 0),
-                                           ("lstm", 128, 2), ("slstm", 128, 4), ("gru", 256, 0), ("lstm", 48, 1)])
-def test_float32_cluster_sizes(cuda_device, function, D, cs):
-    """The cluster loops at every cluster size (0 = the preferred one): exchange of h slices forward, of partial sums of
-    dh in the reverse loop; ragged batch (11 rows = one full and one partial tile)."""
+@pytest.mark.parametrize("function,D,cs,bt", [("lstm", 64, 1, 8), ("lstm", 64, 2, 4), ("lstm", 64, 4, 2), ("lstm", 64, 8, 8),
+                                              ("gru", 96, 3, 0), ("gru", 128, 0, 8), ("slstm", 192, 0, 4), ("elman", 128, 0, 0),
+                                              ("elman", 512, 0, 8), ("lstm", 128, 2, 8), ("slstm", 128, 4, 0), ("gru", 256, 0, 2),
+                                              ("lstm", 48, 1, 0), ("lstm", 256, 0, 8), ("lstm", 256, 0, 4), ("slstm", 64, 1, 8)])
+def test_float32_cluster_sizes(cuda_device, function, D, cs, bt):
+    """The cluster loops at every cluster size and batch tile (0 = the preferred one): exchange of h slices forward, of
+    partial sums of dh in the reverse loop; ragged batch (11 rows: the last tile is partial for every tile size)."""
     from flashrnn_b200 import _native
 
     B, T, N = 11, 10, 2
-    plan = _native.query(_native.make_problem(function, B, T, N, D, True, True, f32=True), cs, 0)
-    assert plan.cluster_size * plan.units_per_cta == D and (cs == 0 or plan.cluster_size == cs)
+    plan = _native.query(_native.make_problem(function, B, T, N, D, True, True, f32=True), cs, bt)
+    assert plan.cluster_size * plan.units_per_cta == D and (cs == 0 or plan.cluster_size == cs) and (bt == 0 or plan.batch_tile == bt)
     Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=5 + D + cs, random_init=(function != "slstm"), dtype=torch.float32)
     g = torch.Generator().manual_seed(9)
     cot = torch.randn(s0.shape[0], B, T, N, D, generator=g, dtype=torch.float64).float().double()
     if function == "slstm":
         cot[1:] = 0
-    got = run_native(function, Wx, R, b, s0, cot=cot, dtype=torch.float32, cluster_size=cs)
+    got = run_native(function, Wx, R, b, s0, cot=cot, dtype=torch.float32, cluster_size=cs, batch_tile=bt)
     ref = run_oracle(function, Wx, R, b, s0, cot=cot)
-    _check(function, got, ref, f"{function} D{D} cs{cs}", n_ds0=1 if function == "slstm" else None)
+    _check(function, got, ref, f"{function} D{D} cs{cs} bt{bt}", n_ds0=1 if function == "slstm" else None)

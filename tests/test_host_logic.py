@@ -266,16 +266,27 @@ def test_floor_probe_exists_for_the_benchmark_tiles_only():
 
 
 def test_float32_problems_take_the_float32_loops():
-    """dtype_io = float32: one geometry (a CTA per head and 8 batch rows), fp32 cache and workspace, any head_dim % 4."""
+    """dtype_io = float32: clusters of CTAs with fp32 slices of R in shared memory (batch tiles of 8, 4 or 2 rows: the
+    smallest whose grid still fits one wave of SMs), fp32 cache and workspace, any head_dim % 4."""
     Gr, Gt, GC = 4, 4, 4
     B, T, N, D = 5, 7, 3, 20
     plan = _native.query(_native.make_problem("lstm", B, T, N, D, True, True, f32=True))
-    assert (plan.cluster_size, plan.units_per_cta, plan.batch_tile, plan.threads) == (1, D, 8, 256)
+    assert (plan.cluster_size, plan.units_per_cta, plan.batch_tile, plan.threads) == (1, D, 2, 256)
+    for name, shape, tile in [("lstm", (16, 1024, 4, 256), (8, 32, 8)), ("gru", (32, 2048, 8, 128), (4, 32, 8)),
+                              ("slstm", (8, 4096, 4, 192), (6, 32, 2)), ("elman", (1024, 64, 16, 64), (1, 64, 8)),
+                              ("lstm", (4, 8, 1, 512), (1, 512, 8))]:  # the last one: R streamed from L2, one CTA per head
+        pl = _native.query(_native.make_problem(name, *shape, True, True, f32=True))
+        assert (pl.cluster_size, pl.units_per_cta, pl.batch_tile) == tile, (name, shape)
+    forced = _native.query(_native.make_problem("lstm", 16, 8, 2, 64, True, True, f32=True), 4, 8)
+    assert (forced.cluster_size, forced.units_per_cta, forced.batch_tile) == (4, 16, 8)
     assert plan.prob.dtype_io == _native.DTYPE_F32 and plan.prob.dtype_state == _native.DTYPE_F32
     assert plan.cache_bytes == B * T * GC * N * D * 4
     assert plan.grads_count == Gr * N * D * D + Gt * N * D and plan.workspace_bytes >= plan.grads_offset + 4 * plan.grads_count
     with pytest.raises(_native.FrnnError) as e:  # no other tile exists
         _native.query(_native.make_problem("lstm", B, T, N, D, True, True, f32=True), 2, 8)
+    assert e.value.code == -6
+    with pytest.raises(_native.FrnnError) as e:  # batch tiles are 8, 4 or 2 rows
+        _native.query(_native.make_problem("lstm", B, T, N, D, True, True, f32=True), 1, 16)
     assert e.value.code == -6
     with pytest.raises(_native.FrnnError) as e:
         _native.query(_native.make_problem("lstm", B, T, N, 1030, True, True, f32=True))
