@@ -302,8 +302,11 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
   const uint32_t my_slice0 = smem_u32(hbuf + (size_t)unit0 * BT);
   const uint32_t buf_bytes = (uint32_t)(BT * D * 4);
   const uint32_t full_u32 = smem_u32(&full[0]);
-  const int nrp = GU >> 1, nwork = nrp * KS, KQ = (D + KS - 1) / KS;
-
+  // Matrix phase: a thread keeps TM gate rows x BT batch rows of sums over its share of k.  Shared memory delivers one
+  // 32-bit word per lane and wavefront whatever the width of the load, so a step costs TM + BT wavefronts per TM * BT
+  // FFMA of a warp: 4 x 8 sums per thread instead of 2 x 8 took 12 % off the loop of LSTM B16 N4 D256.
+  constexpr int TM = BT == 8 ? 4 : 2;  // (smaller tiles: more k-splits would cost the cell phase more than the loads save)
+  const int nrg = GU / TM, nwork = nrg * KS, KQ = (D + KS - 1) / KS;
   for (int t = 0; t < T; ++t) {
     const int cur = t & 1, nxt = cur ^ 1;
     float wxc[IPT][Gw];
@@ -330,26 +333,30 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
     {
       const float* hcur = hbuf + (size_t)cur * BT * D;
       for (int w = tid; w < nwork; w += XTHREADS) {
-        const int kc = w / nrp, rp = w - kc * nrp;
+        const int kc = w / nrg, rg = w - kc * nrg;
         const int k0 = kc * KQ, k1 = (k0 + KQ < D) ? k0 + KQ : D;
-        float acc[2][BT];
+        float acc[TM][BT];
 #pragma unroll
-        for (int b = 0; b < BT; ++b) acc[0][b] = acc[1][b] = 0.f;
-        const float* rr = Rs + 2 * rp;
-#pragma unroll 4
+        for (int r = 0; r < TM; ++r)
+#pragma unroll
+          for (int b = 0; b < BT; ++b) acc[r][b] = 0.f;
+        const float* rr = Rs + TM * rg;
+#pragma unroll(TM == 4 ? 2 : 4)
         for (int k = k0; k < k1; ++k) {
-          const float2 r = *reinterpret_cast<const float2*>(rr + (size_t)k * GU);
-          float hv[BT];
+          float rv[TM], hv[BT];
+          load_row<TM>(rr + (size_t)k * GU, rv);
           load_row<BT>(hcur + k * BT, hv);
 #pragma unroll
-          for (int b = 0; b < BT; ++b) {
-            acc[0][b] = fmaf(r.x, hv[b], acc[0][b]);
-            acc[1][b] = fmaf(r.y, hv[b], acc[1][b]);
-          }
+          for (int r = 0; r < TM; ++r)
+#pragma unroll
+            for (int b = 0; b < BT; ++b) acc[r][b] = fmaf(rv[r], hv[b], acc[r][b]);
         }
 #pragma unroll
-        for (int b = 0; b < BT; ++b)
-          *reinterpret_cast<float2*>(part + ((size_t)kc * BT + b) * GU + 2 * rp) = make_float2(acc[0][b], acc[1][b]);
+        for (int b = 0; b < BT; ++b) {
+          float* dst = part + ((size_t)kc * BT + b) * GU + TM * rg;
+          if constexpr (TM == 4) *reinterpret_cast<float4*>(dst) = make_float4(acc[0][b], acc[1][b], acc[2][b], acc[3][b]);
+          else *reinterpret_cast<float2*>(dst) = make_float2(acc[0][b], acc[1][b]);
+        }
       }
     }
     __syncthreads();
@@ -403,7 +410,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_fwd_kernel(const XParams p) 
   if (CS > 1) { cluster_arrive(); cluster_wait(); }  // no CTA leaves while a copy from or into it may be in flight
 }
 
-// Shared memory of the reverse loop (floats): Rb[Gr*U][D] | delta[Gr*U][8] | send[2][CS][MSG] | recv[2][CS][MSG] |
+// Shared memory of the reverse loop (floats): Rb[Gr*U][D + 8] | delta[Gr*U][8] | send[2][CS][MSG] | recv[2][CS][MSG] |
 // dbs[Gt][U] | 2 mbarriers + flag, MSG = KS*8*U.  Rb[g*U + u][p] = R[g][n][unit0 + u][p].
 // Reduce-scatter: CTA c multiplies ITS deltas with its rows of R for all D columns p and sends the owner of p the
 // partial sums; message for CTA x: [kc][b][u] with p = x*U + u (the CTA's own part goes straight into its recv slot).
@@ -413,14 +420,15 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
   constexpr int Gr = C::Gr, Gw = C::Gw, Gt = C::Gt, S = C::S, GC = C::GC, GCA = GC > 0 ? GC : 1, NNEED = C::NNEED, NEXT = C::NEXT;
   extern __shared__ __align__(16) float sm[];
   const int D = p.D, U = p.U, CS = p.CS, KS = p.KS, GU = Gr * U, T = p.T, B = p.B, N = p.N;
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.z, b0 = blockIdx.y * BT;
   const uint32_t crank = CS > 1 ? cluster_ctarank() : 0u;
   const int unit0 = (int)crank * U;
   const size_t ND = (size_t)N * D;
   const int MSG = KS * BT * U;
+  const int DP = D + 8;  // row pitch of Rb
   float* Rb = sm;
-  float* delta = Rb + (size_t)GU * D;
+  float* delta = Rb + (size_t)GU * DP;
   float* send = delta + GU * BT;
   float* recv = send + 2 * CS * MSG;
   float* dbs = recv + 2 * CS * MSG;
@@ -430,7 +438,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
 
   for (int i = tid; i < GU * D; i += XTHREADS) {
     const int j = i / D, pc = i - j * D, g = j / U, u = j - g * U;
-    Rb[i] = p.R[(((size_t)g * N + n) * D + unit0 + u) * D + pc];
+    Rb[(size_t)j * DP + pc] = p.R[(((size_t)g * N + n) * D + unit0 + u) * D + pc];
   }
   for (int i = tid; i < Gt * U; i += XTHREADS) dbs[i] = 0.f;
 
@@ -498,7 +506,7 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
     __syncthreads();
   }
   const uint32_t full_u32 = smem_u32(&full[0]);
-  const int KQ = (GU + KS - 1) / KS, hD = D >> 1, nwork = hD * KS;
+  const int ncg8 = (D + 31) >> 5, ntasks = ncg8 * KS, KQ = ((GU + KS - 1) / KS + 3) & ~3;  // rows per k-split, a multiple of 4
 
   // sum of the partial sums that arrived for item i in buffer x
   auto gather = [&](int i, int x) {
@@ -582,30 +590,60 @@ __global__ void __launch_bounds__(XTHREADS, 1) x32c_bwd_kernel(const XParams p) 
     const int quit = (CS > 1) ? *gave_up : 0;
     if (exch) {
       // ---------------- matrix phase: partial dh_{t-1}[b][p] = sum over this thread's (g, u) of delta[b][g,u] * R[g][u][p]
-      for (int w = tid; w < nwork; w += XTHREADS) {
-        const int kc = w / hD, pc = 2 * (w - kc * hD);  // columns pc, pc + 1 (same owner: U is even)
-        const int j0 = kc * KQ, j1 = (j0 + KQ < GU) ? j0 + KQ : GU;
-        float acc[2][BT];
+      // A warp task: 32 columns (lane >> 2 picks 4 of them) x one of the KS row ranges; inside the range lane & 3 takes
+      // every fourth row, and the four sums meet again through shuffles.  4 x BT sums per thread: 4 + BT words from shared
+      // memory per 4 * BT FFMA (see the forward loop), and a message stays one [BT][U] block per k-split.  Rows of Rb are
+      // D + 8 words apart, so the four rows a quarter-warp reads together fall into different banks.
+      for (int task = warp; task < ntasks; task += XTHREADS >> 5) {
+        const int kx = task / ncg8, pc = (task - kx * ncg8) * 32 + (lane >> 2) * 4;  // columns pc .. pc+3
+        const int j0 = kx * KQ + (lane & 3), j1 = ((kx + 1) * KQ < GU) ? (kx + 1) * KQ : GU;
+        const bool live = pc < D;
+        float acc[4][BT];
 #pragma unroll
-        for (int b = 0; b < BT; ++b) acc[0][b] = acc[1][b] = 0.f;
-        const float* rr = Rb + pc;
-#pragma unroll 4
-        for (int jj = j0; jj < j1; ++jj) {
-          const float2 r = *reinterpret_cast<const float2*>(rr + (size_t)jj * D);
-          float dv[BT];
-          load_row<BT>(delta + jj * BT, dv);
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int b = 0; b < BT; ++b) {
-            acc[0][b] = fmaf(r.x, dv[b], acc[0][b]);
-            acc[1][b] = fmaf(r.y, dv[b], acc[1][b]);
+          for (int b = 0; b < BT; ++b) acc[c][b] = 0.f;
+        if (live) {
+          const float* rr = Rb + pc;
+#pragma unroll 2
+          for (int jj = j0; jj < j1; jj += 4) {
+            const float4 r = *reinterpret_cast<const float4*>(rr + (size_t)jj * DP);
+            float dv[BT];
+            load_row<BT>(delta + jj * BT, dv);
+#pragma unroll
+            for (int b = 0; b < BT; ++b) {
+              acc[0][b] = fmaf(r.x, dv[b], acc[0][b]);
+              acc[1][b] = fmaf(r.y, dv[b], acc[1][b]);
+              acc[2][b] = fmaf(r.z, dv[b], acc[2][b]);
+              acc[3][b] = fmaf(r.w, dv[b], acc[3][b]);
+            }
           }
         }
-        const int c = pc / U, u = pc - c * U;
-        // the owner's slot: recv[buf][crank] over there; the message leaves from send[buf][c], the own part stays here
-        float* dst = ((uint32_t)c == crank ? recv + ((size_t)buf * CS + crank) * MSG : send + ((size_t)buf * CS + c) * MSG) +
-                     (size_t)kc * BT * U + u;
+        // reduce-scatter over the four lanes of a column group: lane bit 1 keeps columns {0,1} or {2,3}, bit 0 one of the two
+        const bool hi1 = (lane & 2) != 0, hi0 = (lane & 1) != 0;
+        float two[2][BT], one[BT];
 #pragma unroll
-        for (int b = 0; b < BT; ++b) *reinterpret_cast<float2*>(dst + b * U) = make_float2(acc[0][b], acc[1][b]);
+        for (int b = 0; b < BT; ++b) {
+          const float s0 = hi1 ? acc[0][b] : acc[2][b], s1 = hi1 ? acc[1][b] : acc[3][b];
+          const float g0 = __shfl_xor_sync(0xffffffffu, s0, 2), g1 = __shfl_xor_sync(0xffffffffu, s1, 2);
+          two[0][b] = (hi1 ? acc[2][b] : acc[0][b]) + g0;
+          two[1][b] = (hi1 ? acc[3][b] : acc[1][b]) + g1;
+        }
+#pragma unroll
+        for (int b = 0; b < BT; ++b) {
+          const float s = hi0 ? two[0][b] : two[1][b];
+          const float g = __shfl_xor_sync(0xffffffffu, s, 1);
+          one[b] = (hi0 ? two[1][b] : two[0][b]) + g;
+        }
+        if (live) {
+          const int pcol = pc + (hi1 ? 2 : 0) + (hi0 ? 1 : 0);
+          const int c = pcol / U, u = pcol - c * U;
+          // the owner's slot: recv[buf][crank] over there; the message leaves from send[buf][c], the own part stays here
+          float* dst = ((uint32_t)c == crank ? recv + ((size_t)buf * CS + crank) * MSG : send + ((size_t)buf * CS + c) * MSG) +
+                       (size_t)kx * BT * U + u;
+#pragma unroll
+          for (int b = 0; b < BT; ++b) dst[b * U] = one[b];
+        }
       }
       if (CS > 1) fence_proxy_async_smem();
       __syncthreads();
@@ -792,19 +830,20 @@ constexpr int kResidentClusters[9] = {0, 148, 74, 45, 33, 26, 22, 17, 15};
 bool cluster_tile(const frnn_problem& pr, const Dims& d, int cs, int bt, Tile* t) {
   if (cs < 1 || cs > 8 || pr.D % cs) return false;
   if (bt != 0 && bt != 8 && bt != 4 && bt != 2) return false;
+  const int u = pr.D / cs;
+  if (u % 4 || u > 64) return false;
+  const size_t gu = (size_t)d.Gr * u, D = (size_t)pr.D;
   if (bt == 0) {
     bt = 8;
     while (bt > 2 && (long long)((pr.B + bt / 2 - 1) / (bt / 2)) * pr.N <= kResidentClusters[cs]) bt /= 2;
   }
-  const int u = pr.D / cs;
-  if (u % 4 || u > 64) return false;
-  const size_t gu = (size_t)d.Gr * u, D = (size_t)pr.D;
   t->cs = cs; t->u = u; t->bt = bt; t->cluster = true;
-  t->ksf = clampi((int)(512 / gu), 1, 8);
-  t->ksb = clampi(512 / pr.D, 1, 8);
+  const int tm = bt == 8 ? 4 : 2;  // gate rows per thread in the forward matrix phase
+  t->ksf = clampi((int)(XTHREADS * tm / gu), 1, clampi((int)(32768 / (bt * gu * 4)), 1, 16));  // partial sums within 32 KB
+  t->ksb = clampi((XTHREADS / 32) / ((pr.D + 31) / 32), 1, 8);  // warp tasks of 32 columns: as many row ranges as fill the warps
   t->ipt = bt * u > XTHREADS ? 2 : 1;
   t->smem_f = (D * gu + 2 * bt * D + (size_t)t->ksf * bt * gu) * 4 + 64;
-  t->smem_b = (gu * D + gu * bt + (size_t)4 * t->ksb * bt * D + (size_t)d.Gt * u) * 4 + 64;
+  t->smem_b = (gu * (D + 8) + gu * bt + (size_t)4 * t->ksb * bt * D + (size_t)d.Gt * u) * 4 + 64;
   return t->smem_f <= kSmemMax && t->smem_b <= kSmemMax;
 }
 // cs == 0: the preferred tile -- the whole head in one CTA up to head dim 64, else the smallest cluster with at most 32
