@@ -59,8 +59,8 @@ typedef struct frnn_problem {
   int32_t B, T, N, D;    /* batch, time steps, heads, head dim                     */
   int32_t dtype_io;      /* dtype of Wx, R, b, dWx, dR, db : FRNN_DTYPE_BF16 or _F16 (MMA operand type; accumulation and
                             gate math are fp32 either way), or FRNN_DTYPE_F32: the float32 loops (fp32 products on the
-                            CUDA cores, exp-based nonlinearities; accurate to ~1e-5 against an fp32 reference, an order
-                            of magnitude slower than the 16-bit tensor-core loops; any head_dim % 4 == 0 up to 1024)  */
+                            CUDA cores, exp-based nonlinearities; accurate to ~1e-5 against an fp32 reference, 4-5 x
+                            slower than the 16-bit tensor-core loops; any head_dim % 4 == 0 up to 1024)              */
   int32_t dtype_state;   /* dtype of s0, states, dstates, ds0 : same as dtype_io, or F32 (F32 io needs F32 states) */
   int32_t training;      /* 1: forward writes the activation cache for backward     */
   float forward_clip;    /* > 0: clamp the new h to [-v, v]   (forward_clipval)     */
@@ -76,14 +76,14 @@ typedef struct frnn_plan {
   frnn_problem prob;
   int32_t cluster_size;    /* CTAs that share one (head, batch tile); exchange h through DSMEM */
   int32_t units_per_cta;   /* hidden units of the head owned by one CTA                      */
-  int32_t batch_tile;      /* batch rows per CTA (8, 16 or 32)                               */
+  int32_t batch_tile;      /* batch rows per CTA (8, 16, 32 or 128; float32 loops: 8, 4 or 2) */
   int32_t threads;         /* threads per CTA of the time-loop kernels                       */
   int32_t wx_stages;       /* time steps of Wx prefetched ahead into shared memory           */
   int32_t cache_slots;     /* activation values cached per (b,t,n,d) in training             */
   int32_t test_drop_exchange; /* TEST HOOK, leave 0.  1: CTA 0 of every cluster withholds one exchange message
                                  (forward: its h of step 1; backward: its first message) so that its peers' bounded
                                  waits expire; the kernels then finish with invalid results and report it in the
-                                 status block.  With the 128-row loops (batch_tile 128): one tile copy (step index 2)
+                                 status block (float32 cluster loops: the message of step 1 in both loops).  With the 128-row loops (batch_tile 128): one tile copy (step index 2)
                                  is announced to its barrier and never issued.  Exercises the failure-detection path
                                  without faulting the GPU.                                                          */
   int32_t keep_packed_r;      /* 0: frnn_forward clears the status block and repacks R into the workspace (default).
@@ -154,7 +154,9 @@ int frnn_abi_version(void);
 int frnn_query(const frnn_problem* problem, frnn_plan* out);
 
 /* Same as frnn_query but with the tile forced by the caller (used to measure the tile table);
- * any of the three may be 0 = "use the table's value".  Invalid combinations return FRNN_ERR_PLAN. */
+ * any of the three may be 0 = "use the table's value".  Invalid combinations return FRNN_ERR_PLAN.
+ * float32 problems: cluster_size 1..8 (units per CTA a multiple of 4, at most 64, its fp32 slice of R within shared
+ * memory; cluster_size 1 otherwise selects the loops that stream R from L2), batch_tile 8, 4 or 2, wx_stages 0. */
 int frnn_query_tile(const frnn_problem* problem, int cluster_size, int batch_tile, int wx_stages, frnn_plan* out);
 
 /* Whole-sequence forward: one persistent launch (plus a small weight-repack launch).

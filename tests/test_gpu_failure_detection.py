@@ -100,3 +100,41 @@ def test_wide_loops_report_a_copy_that_never_lands(cuda_device):
     nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
     nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
     assert st.code == 0 and torch.isfinite(dWx.float()).all()
+
+
+def test_float32_cluster_loops_report_a_withheld_message(cuda_device):
+    """The float32 cluster loops use the same exchange protocol: forward (h slices) and reverse loop (partial sums of dh)
+    each report the message CTA 0 withholds, the kernels end, and a clean run follows in the same context."""
+    Wx, R, b, s0 = [t.to(cuda_device, torch.float32) for t in make_inputs("lstm", 8, 6, 1, 128, seed=33, dtype=torch.float32)]
+    B, T, _, N, D = Wx.shape
+    plan = nv.query(nv.make_problem("lstm", B, T, N, D, True, True, f32=True))
+    assert plan.cluster_size > 1
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream(cuda_device).cuda_stream)
+    states = torch.zeros(2, B, T, N, D, device=cuda_device, dtype=torch.float32)
+    cache = torch.zeros(int(plan.cache_bytes), device=cuda_device, dtype=torch.uint8)
+    ws = torch.zeros(int(plan.workspace_bytes), device=cuda_device, dtype=torch.uint8)
+    L = nv.lib()
+    fa = nv.FrnnFwdArgs(P(Wx), P(R), P(b), P(s0), P(states), P(cache), P(ws))
+    st = nv.FrnnDevStatus()
+    t0 = time.time()
+    plan.test_drop_exchange = 1
+    nv.check("frnn_forward", L.frnn_forward(ctypes.byref(plan), ctypes.byref(fa), stream))
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 1 and st.cta < plan.cluster_size * N * ((B + plan.batch_tile - 1) // plan.batch_tile)
+    plan.test_drop_exchange = 0
+    nv.check("frnn_forward", L.frnn_forward(ctypes.byref(plan), ctypes.byref(fa), stream))
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 0 and torch.isfinite(states).all()
+    dst = torch.ones_like(states)
+    dWx, ds0 = torch.zeros_like(Wx), torch.zeros_like(s0)
+    ba = nv.FrnnBwdArgs(P(R), P(s0), P(states), P(cache), P(dst), P(dWx), P(ds0), P(ws))
+    plan.test_drop_exchange = 1
+    nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 1
+    assert time.time() - t0 < 30.0  # bounded: about a second per expired wait
+    plan.test_drop_exchange = 0
+    nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
+    nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
+    assert st.code == 0 and torch.isfinite(dWx).all()
