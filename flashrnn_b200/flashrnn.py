@@ -18,7 +18,7 @@ reference (flashrnn/flashrnn/flashrnn.py:124-207, 1093-1135).  What changed on p
 * ``dtype`` is ``"bfloat16"`` or ``"float16"`` (the MMA operand type; accumulation and gate math are fp32 for both,
   where the reference accumulates float16 in float16, fused/flashrnn_fused_forward.cu), or ``"float32"``: everything in
   fp32 on the CUDA cores -- accurate to ~1e-5 against the fp32 ``vanilla`` loop (the reference multiplies in tf32
-  there, fused/flashrnn_fused_forward.cu:108-112), an order of magnitude slower than the 16-bit tensor-core loops.
+  there, fused/flashrnn_fused_forward.cu:108-112), 4-5 x slower than the 16-bit tensor-core loops.
 """
 from __future__ import annotations
 
