@@ -122,3 +122,14 @@ def test_float32_cluster_sizes(cuda_device, function, D, cs, bt):
     got = run_native(function, Wx, R, b, s0, cot=cot, dtype=torch.float32, cluster_size=cs, batch_tile=bt)
     ref = run_oracle(function, Wx, R, b, s0, cot=cot)
     _check(function, got, ref, f"{function} D{D} cs{cs} bt{bt}", n_ds0=1 if function == "slstm" else None)
+
+
+@pytest.mark.parametrize("function", ["lstm", "gru", "elman", "slstm"])
+def test_float32_odd_head_dims(cuda_device, function):
+    """Head dims on both sides of every switch of the tile table (one CTA, clusters of 2..8, R streamed from L2)."""
+    for D in (4, 12, 36, 68, 100, 132, 196, 260, 324, 516):
+        B, T, N = 3, 5, 2
+        Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=D, random_init=(function != "slstm"), dtype=torch.float32)
+        got = run_native(function, Wx, R, b, s0, dtype=torch.float32)
+        ref = run_oracle(function, Wx, R, b, s0)
+        _check(function, got, ref, f"{function} D{D}", n_ds0=1 if function == "slstm" else None)

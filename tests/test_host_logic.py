@@ -296,3 +296,13 @@ def test_float32_problems_take_the_float32_loops():
     with pytest.raises(_native.FrnnError) as e:
         _native.query(bad)
     assert e.value.code == -4
+
+
+def test_float32_tile_table_covers_every_head_dim():
+    """Every head dim the float32 loops accept gets a tile whose units add up to the head, for every cell."""
+    for function in ("lstm", "gru", "elman", "slstm"):
+        for D in range(4, 1025, 4):
+            for B in (1, 8, 100):
+                plan = _native.query(_native.make_problem(function, B, 3, 2, D, True, True, f32=True))
+                assert plan.cluster_size * plan.units_per_cta == D and plan.batch_tile in (2, 4, 8), (function, D, B)
+                assert plan.units_per_cta <= 64 or plan.cluster_size == 1
