@@ -41,7 +41,8 @@ class FrnnPlan(ctypes.Structure):
         ("abi_version", ctypes.c_int32), ("prob", FrnnProblem), ("cluster_size", ctypes.c_int32),
         ("units_per_cta", ctypes.c_int32), ("batch_tile", ctypes.c_int32), ("threads", ctypes.c_int32),
         ("wx_stages", ctypes.c_int32), ("cache_slots", ctypes.c_int32), ("test_drop_exchange", ctypes.c_int32),
-        ("keep_packed_r", ctypes.c_int32), ("probe_noop_cell", ctypes.c_int32), ("reserved", ctypes.c_int32 * 3),
+        ("keep_packed_r", ctypes.c_int32), ("probe_noop_cell", ctypes.c_int32), ("wide_forward", ctypes.c_int32),
+        ("reserved", ctypes.c_int32 * 2),
         ("cache_bytes", ctypes.c_uint64), ("workspace_bytes", ctypes.c_uint64), ("grads_offset", ctypes.c_uint64),
         ("grads_count", ctypes.c_uint64),
     ]

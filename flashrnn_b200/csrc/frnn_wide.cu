@@ -302,6 +302,294 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 }
 
 
+// ================================================================================================ LSTM forward
+// The same loop for the four-gate LSTM cell at head dim 64: the accumulator of a step is [128 rows][4 gates x 64] fp32 =
+// 256 columns of tensor memory (two of them alternate), filled by
+//   acc[:, g] = Wx_t[g] * I  (4 gates x 4 MMAs, N = 64)  +  1 * b  (one MMA, N = 256)      -- issued ahead of the step
+//   acc      += h_{t-1} * R^T                             (4 MMAs, N = 256; R as [4*64 rows][64 k])
+// Two row threads per batch row (8 warps: two per scheduler, so that one hides the other's latencies -- with one thread per
+// row the cell phase of 64 units x 5 nonlinearities ran at half the speed) read the accumulator 16 units at a time (4 gates
+// x 16 columns), keep the cell state c of their 32 units in registers (fp32), write h_t into the shared-memory tile the next step multiplies and a bulk store sends to
+// `states[0]`, and store c_t and the four cached activations straight to global memory (a thread owns 128 contiguous
+// bytes per value kind).  The activation cache is written in the layout of the REVERSE loop's own tile (one CTA per head,
+// 16 batch rows: frnn_bwd_kernel reads it as it reads its forward kernel's), so only the forward loop changes.
+// Wx_t arrives as one tensor-map copy of [4 gates][128 rows][64] per step into a ring of two 64 KB stages; the stage of
+// step t is refilled with step t+2 as soon as the step's MMAs are known to have completed.
+struct WideLstmParams {
+  const elem_t* R;     // [4,N,64,64]
+  const elem_t* bias;  // [4,N,64]
+  const elem_t* s0;    // [2,B,1,N,64]
+  elem_t* states;      // [2,B,T,N,64]; h leaves through the tensor map, c through plain stores
+  uint32_t* cache;     // reverse loop's layout (16-row tiles): [t][head][tile][slot][row in tile][unit pair]; or null
+  unsigned* status;
+  int B, T, N;
+};
+constexpr int WL_G = 4;
+constexpr int WL_AHEAD = 6;     // steps between the L2 prefetch of a Wx box and its copy into shared memory
+constexpr int WL_THREADS = 288;  // warps 0-7: two row threads per batch row; warp 8, one lane: every bulk copy and MMA
+constexpr uint32_t WL_OFF_WX = 0;                                   // 2 stages x 4 gate tiles
+constexpr uint32_t WL_OFF_H = WL_OFF_WX + 2 * WL_G * WTILE;         // h_t in tile t & 1
+constexpr uint32_t WL_OFF_R = WL_OFF_H + 2 * WTILE;                 // [256][64] K-major, 128-byte swizzle
+constexpr uint32_t WL_OFF_I = WL_OFF_R + WL_G * WMAT;
+constexpr uint32_t WL_OFF_ONES = WL_OFF_I + WMAT;                   // A operand [128 rows][16 k], k = 0 holds 1.0
+constexpr uint32_t WL_OFF_BIAS = WL_OFF_ONES + 4096;                // B operand [256 rows][16 k], k = 0 holds b[row]
+constexpr uint32_t WL_OFF_BAR = WL_OFF_BIAS + 8192;
+constexpr uint32_t WL_SMEM = WL_OFF_BAR + 8 * 8 + 16 + 1024;
+static_assert(WL_SMEM <= 227 * 1024, "shared memory of the LSTM loop");
+
+// one 256-bit store (32-byte aligned address)
+__device__ __forceinline__ void st_global_32B(void* q, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(q), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x),
+               "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+
+// 4 x 16 consecutive fp32 columns (the four gates of 16 units), one wait
+__device__ __forceinline__ void tmem_ld16x4(uint32_t t0, uint32_t t1, uint32_t t2, uint32_t t3, uint32_t (&a)[16], uint32_t (&b)[16],
+                                            uint32_t (&c)[16], uint32_t (&d)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%64];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%65];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47}, [%66];\n\t"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%67];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]),
+        "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]),
+        "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]), "=r"(c[4]), "=r"(c[5]), "=r"(c[6]), "=r"(c[7]), "=r"(c[8]), "=r"(c[9]), "=r"(c[10]), "=r"(c[11]), "=r"(c[12]), "=r"(c[13]), "=r"(c[14]), "=r"(c[15]),
+        "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]), "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15])
+      : "r"(t0), "r"(t1), "r"(t2), "r"(t3) : "memory");
+}
+
+__global__ void __launch_bounds__(WL_THREADS, 1)
+wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states, const WideLstmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_raw + (base - raw);
+  uint64_t* wx_full = reinterpret_cast<uint64_t*>(sm + WL_OFF_BAR);  // [2] bytes of a Wx stage have landed
+  uint64_t* acc_full = wx_full + 2;                                  // [2] MMAs into accumulator x have completed
+  uint64_t* h_ready = acc_full + 2;                                  // 256 arrivals: h_t is in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(h_ready + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T, N = p.N, B = p.B;
+
+  // ---- operands written once
+  for (int c = tid; c < WL_G * WD * 8; c += WL_THREADS) {  // R: row j = g * 64 + d holds R[g][n][d][:]
+    const uint32_t j = c >> 3, q = c & 7, g = j >> 6, d = j & 63;
+    *reinterpret_cast<uint4*>(sm + WL_OFF_R + sw128(j, q)) =
+        *reinterpret_cast<const uint4*>(p.R + (((size_t)g * N + n) * WD + d) * WD + q * 8);
+  }
+  for (int c = tid; c < WD * 8; c += WL_THREADS) {  // identity: 1.0 at k = d
+    const uint32_t d = c >> 3, j = c & 7;
+    const uint32_t w = (d & 7) >> 1, one = ((d >> 3) == j) ? (kOneBits << (16 * (d & 1))) : 0u;
+    *reinterpret_cast<uint4*>(sm + WL_OFF_I + sw128(d, j)) =
+        make_uint4(w == 0 ? one : 0u, w == 1 ? one : 0u, w == 2 ? one : 0u, w == 3 ? one : 0u);
+  }
+  for (int r = tid; r < WM; r += WL_THREADS) {
+    unsigned char* q = sm + WL_OFF_ONES + (r >> 3) * 256 + (r & 7) * 16;
+    *reinterpret_cast<uint4*>(q) = make_uint4(kOneBits, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  for (int j = tid; j < WL_G * WD; j += WL_THREADS) {
+    unsigned char* q = sm + WL_OFF_BIAS + (j >> 3) * 256 + (j & 7) * 16;
+    *reinterpret_cast<uint4*>(q) = make_uint4(elem_bits(p.bias[((size_t)(j >> 6) * N + n) * WD + (j & 63)]), 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(q + 128) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  const int row = tid & (WM - 1), half = tid >> 7;  // row threads: two per batch row, units 32 * half .. 32 * half + 31
+  const bool row_ok = tid < 2 * WM && b0 + row < B;
+  if (tid < WM) {  // h_{-1} -> tile 1 (step t reads tile (t + 1) & 1 and writes tile t & 1)
+    const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)(row_ok ? b0 + row : 0) * N + n) * WD);
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j)
+      *reinterpret_cast<uint4*>(sm + WL_OFF_H + WTILE + sw128(tid, j)) = row_ok ? src[j] : make_uint4(0u, 0u, 0u, 0u);
+  }
+  if (tid == 0) {
+    mbar_init(&wx_full[0], 1);
+    mbar_init(&wx_full[1], 1);
+    mbar_init(&acc_full[0], 1);
+    mbar_init(&acc_full[1], 1);
+    mbar_init(h_ready, 2 * WM);
+    fence_mbar_init();
+  }
+  if (warp == 8) tmem_alloc(tmem_slot, 512);  // two accumulators of 4 x 64 fp32 columns
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      // ------------------------------------------------------------ producer: bulk copies and MMAs
+      const uint32_t idesc64 = instr_desc_16(WM, WD, 0, 0), idesc256 = instr_desc_16(WM, WL_G * WD, 0, 0);
+      const void* tmw = &tm_wx;
+      const void* tms = &tm_states;
+      constexpr uint32_t HI = desc_hi(1024, true), HIP = desc_hi(256, false), TILE16 = WTILE >> 4;
+      const uint32_t wx_lo = (base + WL_OFF_WX) >> 4, h_lo = (base + WL_OFF_H) >> 4, r_lo = (base + WL_OFF_R) >> 4,
+                     i_lo = (base + WL_OFF_I) >> 4, ones_lo = ((base + WL_OFF_ONES) >> 4) | ((128u >> 4) << 16),
+                     bias_lo = ((base + WL_OFF_BIAS) >> 4) | ((128u >> 4) << 16);
+      int loads = 0, seen = 0;  // Wx stages requested / seen to land (both in step order)
+      auto load_wx = [&](int t) {  // [4 gates][128 rows][64] of step t -> stage t & 1
+        mbar_arrive_expect_tx(&wx_full[t & 1], WL_G * WTILE);
+        tma_load_5d(base + WL_OFF_WX + (uint32_t)(t & 1) * WL_G * WTILE, tmw, 0, b0, 0, n, t, &wx_full[t & 1]);
+        ++loads;
+      };
+      auto wait_wx = [&](int t) {
+        if (!mbar_wait_bounded(&wx_full[t & 1], (uint32_t)((t >> 1) & 1))) return false;
+        seen = t + 1;
+        return true;
+      };
+      auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I (per gate) + ones * bias
+        const uint32_t d = tmem + (uint32_t)(t & 1) * (WL_G * WD), a = wx_lo + (uint32_t)(t & 1) * WL_G * TILE16;
+#pragma unroll
+        for (uint32_t g = 0; g < WL_G; ++g)
+#pragma unroll
+          for (uint32_t k = 0; k < 4; ++k) umma_parts(d + g * WD, a + g * TILE16 + 2 * k, HI, i_lo + 2 * k, HI, idesc64, k);
+        umma_parts(d, ones_lo, HIP, bias_lo, HIP, idesc256, 1u);
+      };
+      // With two stages only one or two copies are in flight, and a box is 512 pieces of 128 bytes on 128 different pages
+      // (batch rows lie far apart): each box is asked into L2 WL_AHEAD steps before its copy into shared memory.
+      for (int t = 2; t < T && t < 2 + WL_AHEAD; ++t) tma_prefetch_5d(tmw, 0, b0, 0, n, t);
+      load_wx(0);
+      if (T > 1) load_wx(1);
+      bool ok = wait_wx(0);
+      if (ok) issue_pre(0);
+      else report_timeout(p.status, 0);
+      for (int t = 0; ok && t < T; ++t) {
+        if (t > 0) {
+          if (!mbar_wait_bounded(h_ready, (uint32_t)((t - 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
+          tc_fence_after();
+        }
+        // the row threads of step t overwrite the tile of h_{t-2}, whose store was issued a whole step ago
+        bulk_wait_group_read<0>();
+        const uint32_t a = h_lo + (uint32_t)((t + 1) & 1) * TILE16, d = tmem + (uint32_t)(t & 1) * (WL_G * WD);
+#pragma unroll
+        for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc256, 1u);
+        umma_commit(&acc_full[t & 1]);
+        if (t > 0) {  // h_{t-1} -> states[0][b0.., t-1, n, :]
+          tma_store_5d(tms, base + WL_OFF_H + (uint32_t)((t - 1) & 1) * WTILE, 0, n, t - 1, b0, 0);
+          bulk_commit_group();
+        }
+        if (t + 1 < T) {
+          if (!wait_wx(t + 1)) { report_timeout(p.status, t); ok = false; break; }
+          issue_pre(t + 1);
+        }
+        if (t + 2 < T) {  // the stage of step t is free once its MMAs (all issued before the commit above) have completed
+          if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
+          load_wx(t + 2);
+        }
+        if (t + 2 + WL_AHEAD < T) tma_prefetch_5d(tmw, 0, b0, 0, n, t + 2 + WL_AHEAD);
+      }
+      if (ok) {
+        if (mbar_wait_bounded(h_ready, (uint32_t)((T - 1) & 1))) {
+          tma_store_5d(tms, base + WL_OFF_H + (uint32_t)((T - 1) & 1) * WTILE, 0, n, T - 1, b0, 0);
+          bulk_commit_group();
+        } else {
+          report_timeout(p.status, T);
+        }
+      }
+      // never leave with copies in flight (only an expired wait leaves a load unobserved)
+      for (int i = (seen > loads - 2 ? seen : loads - 2); i < loads; ++i) mbar_wait_bounded(&wx_full[i & 1], (uint32_t)((i >> 1) & 1));
+      bulk_wait_group<0>();
+    }
+  } else {
+    // ------------------------------------------------------------ row threads: half a batch row (32 units) each; a warp
+    // reads the tensor-memory lanes of its quarter (warp & 3), so warps w and w + 4 share 32 rows
+    const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const int b = b0 + row;
+    const size_t ND = (size_t)N * WD;
+    float cst[32];  // cell state of this half row, fp32 over all steps
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)B + (row_ok ? b : 0)) * ND + (size_t)n * WD + 32 * half);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 w = row_ok ? src[j] : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 v = unpack_x2(ww[e]);
+          cst[j * 8 + 2 * e] = v.x;
+          cst[j * 8 + 2 * e + 1] = v.y;
+        }
+      }
+    }
+    // c_t -> states[1][b][t][n][:];  cache: 16-row tiles of the reverse loop, see WideLstmParams
+    elem_t* c_out = p.states + (((size_t)B + (row_ok ? b : 0)) * T) * ND + (size_t)n * WD;
+    const size_t tiles16 = (size_t)((B + 15) / 16);
+    uint32_t* ch = p.cache ? p.cache + (((size_t)n * tiles16 + (size_t)(b >> 4)) * WL_G) * 512 + (size_t)(b & 15) * 32 : nullptr;
+    const size_t ch_step = (size_t)N * tiles16 * WL_G * 512;
+    for (int t = 0; t < T; ++t) {
+      if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); break; }
+      tc_fence_after();
+      unsigned char* hdst = sm + WL_OFF_H + (uint32_t)(t & 1) * WTILE;
+      const uint32_t acc = trow + (uint32_t)(t & 1) * (WL_G * WD);
+      uint4 out[1 + WL_G][4];  // c_t and the four activations of this thread's 32 units, packed for the stores below
+#pragma unroll
+      for (int qq = 0; qq < 2; ++qq) {  // units 16 q .. 16 q + 15
+        const int q = 2 * half + qq;
+        uint32_t ri[16], rf[16], rz[16], ro[16];
+        tmem_ld16x4(acc + 16 * q, acc + WD + 16 * q, acc + 2 * WD + 16 * q, acc + 3 * WD + 16 * q, ri, rf, rz, ro);
+        float hv[16], gi[16], gf[16], gz[16], go[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          gi[j] = fast_sigmoid(__uint_as_float(ri[j]));
+          gf[j] = fast_sigmoid(__uint_as_float(rf[j]));
+          gz[j] = fast_tanh(__uint_as_float(rz[j]));
+          go[j] = fast_sigmoid(__uint_as_float(ro[j]));
+          const float c = gf[j] * cst[16 * qq + j] + gi[j] * gz[j];
+          cst[16 * qq + j] = c;
+          hv[j] = go[j] * fast_tanh(c);
+        }
+        auto pack16 = [](const float (&v)[16], uint4& lo, uint4& hi) {
+          lo = make_uint4(pack_x2(v[0], v[1]), pack_x2(v[2], v[3]), pack_x2(v[4], v[5]), pack_x2(v[6], v[7]));
+          hi = make_uint4(pack_x2(v[8], v[9]), pack_x2(v[10], v[11]), pack_x2(v[12], v[13]), pack_x2(v[14], v[15]));
+        };
+        uint4 lo, hi;
+        pack16(hv, lo, hi);
+        *reinterpret_cast<uint4*>(hdst + sw128(row, 2 * q)) = lo;
+        *reinterpret_cast<uint4*>(hdst + sw128(row, 2 * q + 1)) = hi;
+        float cv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) cv[j] = cst[16 * qq + j];
+        pack16(cv, out[0][2 * qq], out[0][2 * qq + 1]);
+        pack16(gi, out[1][2 * qq], out[1][2 * qq + 1]);
+        pack16(gf, out[2][2 * qq], out[2][2 * qq + 1]);
+        pack16(gz, out[3][2 * qq], out[3][2 * qq + 1]);
+        pack16(go, out[4][2 * qq], out[4][2 * qq + 1]);
+      }
+      // h_t is complete: hand it to the next step first; the 20 global stores of this thread (c_t and the cache, 80 KB per
+      // step and CTA) come after the arrival, off the chain h_t -> MMA -> accumulator (LB forward loop 2.87 -> 2.63 ms
+      // together with the 32-byte stores).
+      fence_proxy_async_smem();  // the tile is read by the tensor core and by the bulk store
+      tc_fence_before();
+      mbar_arrive(h_ready);
+      if (row_ok) {  // 64 contiguous bytes per value kind: two 32-byte stores, each one whole sector
+        uint4* cdst = reinterpret_cast<uint4*>(c_out) + 4 * half;
+        st_global_32B(cdst, out[0][0], out[0][1]);
+        st_global_32B(cdst + 2, out[0][2], out[0][3]);
+        if (ch != nullptr) {
+#pragma unroll
+          for (int g = 0; g < WL_G; ++g) {
+            uint4* gdst = reinterpret_cast<uint4*>(ch + 512 * g) + 4 * half;
+            st_global_32B(gdst, out[1 + g][0], out[1 + g][1]);
+            st_global_32B(gdst + 2, out[1 + g][2], out[1 + g][3]);
+          }
+        }
+      }
+      c_out += ND;
+      if (ch != nullptr) ch += ch_step;
+
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+
 // ================================================================================================ backward
 struct WideBwdParams {
   const elem_t* R;  // [1,N,64,64]
@@ -733,6 +1021,14 @@ bool map_pairs(CUtensorMap* tm, const void* base, int B, int T, int N, RowStride
 }
 bool pairs_ok(int B, int T) { return B % 8 == 0 && T >= 2; }
 
+// Wx [B,T,4,N,64] seen as (d, b, g, n, t): one box [4 gates][128 rows][64] per (tile, head, step)
+bool map_wx_gates(CUtensorMap* tm, const void* base, int B, int T, int N, long long sb, long long st, long long sg, long long sn) {
+  const uint64_t dims[5] = {WD, (uint64_t)B, WL_G, (uint64_t)N, (uint64_t)T};
+  const uint64_t strides[4] = {(uint64_t)sb * 2, (uint64_t)sg * 2, (uint64_t)sn * 2, (uint64_t)st * 2};
+  const uint32_t box[5] = {WD, WM, WL_G, 1, 1};
+  return encode_tiles16(tm, base, dims, strides, box);
+}
+
 }  // namespace
 
 bool wide_supported(int cell, int D, int state_f32, float fclip, float gclip, int grad_cut) {
@@ -759,6 +1055,32 @@ cudaError_t launch_wide_forward(const void* Wx, long long wx_sb, long long wx_st
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WF_SMEM);
   if (e != cudaSuccess) return e;
   kern<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), W_THREADS, WF_SMEM, stream>>>(tm_wx, tm_st, p);
+  return cudaGetLastError();
+}
+
+// 128-row forward loop of the LSTM cell at head dim 64 (16-bit states, no forward clamp); the reverse loop stays on the
+// cluster kernels' 16-row tiles, whose cache layout the forward loop writes
+bool wide_lstm_forward_supported(int cell, int D, int state_f32, float fclip) {
+  return cell == CELL_LSTM && D == WD && !state_f32 && !(fclip > 0.f);
+}
+
+cudaError_t launch_wide_lstm_forward(const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
+                                     const void* bias, const void* s0, void* states, void* cache, unsigned* status, int B, int T,
+                                     int N, cudaStream_t stream) {
+  CUtensorMap tm_wx, tm_st;
+  if (!map_wx_gates(&tm_wx, Wx, B, T, N, wx_sb, wx_st, wx_sg, wx_sn) || !map_sbtnd(&tm_st, states, B, T, N, dense_strides(T, N)))
+    return cudaErrorNotSupported;
+  WideLstmParams p;
+  p.R = static_cast<const elem_t*>(R);
+  p.bias = static_cast<const elem_t*>(bias);
+  p.s0 = static_cast<const elem_t*>(s0);
+  p.states = static_cast<elem_t*>(states);
+  p.cache = static_cast<uint32_t*>(cache);
+  p.status = status;
+  p.B = B; p.T = T; p.N = N;
+  cudaError_t e = cudaFuncSetAttribute(wide_fwd_lstm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WL_SMEM);
+  if (e != cudaSuccess) return e;
+  wide_fwd_lstm_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), WL_THREADS, WL_SMEM, stream>>>(tm_wx, tm_st, p);
   return cudaGetLastError();
 }
 

@@ -44,3 +44,56 @@ def test_wide_is_the_default_for_large_batches():
     # cells / options the 128-row loops do not cover keep the warp-MMA loops (16-row tiles for large multi-gate batches)
     assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True)).batch_tile == 16
     assert nv.query(nv.make_problem("elman", 1024, 16, 16, 64, True, True)).batch_tile == 8
+
+
+@pytest.mark.parametrize("B,T,N", [(128, 5, 1), (128, 1, 2), (128, 2, 1), (130, 9, 2), (37, 12, 3), (300, 33, 2), (264, 34, 3), (8, 3, 1)])
+def test_wide_lstm_forward_matches_oracle(cuda_device, B, T, N):
+    """LSTM, head dim 64: the forward loop on the 128-row tensor-core kernel (forced with batch_tile=128), the reverse
+    loop on 16-row tiles that read the cache the forward loop wrote: states and every gradient against the oracle."""
+    plan = nv.query(nv.make_problem("lstm", B, T, N, 64, False, True), 0, 128)
+    assert (plan.wide_forward, plan.cluster_size, plan.batch_tile) == (1, 1, 16)
+    Wx, R, b, s0 = make_inputs("lstm", B, T, N, 64, seed=B + T, random_init=True)
+    g = torch.Generator().manual_seed(11)
+    cot = torch.randn(2, B, T, N, 64, generator=g, dtype=torch.float64).to(torch.bfloat16).to(torch.float64)
+    got = run_native("lstm", Wx, R, b, s0, cot=cot, batch_tile=128)
+    ref = run_oracle("lstm", Wx, R, b, s0, cot=cot)
+    errs = assert_parity("lstm", got, ref, tag=f"wide lstm B{B} T{T} N{N}", zero_init=False)
+    assert errs["h"] < 1.5e-2
+
+
+def test_wide_lstm_forward_variants(cuda_device):
+    """Inference (no cache), a time-major Wx read through strides, float16, and the same problem on the 16-row tiles."""
+    from flashrnn_b200 import FlashRNNConfig, flashrnn
+
+    B, T, N, D = 136, 11, 2, 64
+    Wx, R, b, s0 = make_inputs("lstm", B, T, N, D, seed=17, random_init=True)
+    ref = run_oracle("lstm", Wx, R, b, s0)
+    a = run_native("lstm", Wx, R, b, s0, batch_tile=128)
+    c = run_native("lstm", Wx, R, b, s0, batch_tile=16)
+    assert np.abs(a["states"] - c["states"]).max() < 2e-2
+    for k in ("dWx", "dR", "db"):
+        assert np.linalg.norm((a[k] - c[k]).ravel()) / np.linalg.norm(c[k].ravel()) < 1e-2, k
+    dev = [x.to(cuda_device, torch.bfloat16) for x in (Wx, R, b, s0)]
+    cfg = FlashRNNConfig(function="lstm", head_dim=D, num_heads=N, batch_size=B, batch_tile=128)
+    with torch.no_grad():
+        inf, last = flashrnn(*dev, function="lstm", config=cfg)
+    assert np.abs(inf.double().cpu().numpy() - ref["states"]).max() < 2e-2 * max(1.0, float(np.abs(ref["states"]).max()))
+    assert np.abs(last.double().cpu().numpy() - ref["last"]).max() < 2e-2 * max(1.0, float(np.abs(ref["last"]).max()))
+    cfg_t = FlashRNNConfig(function="lstm", head_dim=D, num_heads=N, batch_size=B, batch_tile=128, input_shape="TBGHD")
+    with torch.no_grad():
+        alt, _ = flashrnn(dev[0].permute(1, 0, 2, 3, 4).contiguous(), dev[1], dev[2], dev[3], function="lstm", config=cfg_t)
+    assert torch.equal(inf, alt)
+    Wx16, R16, b16, s16 = make_inputs("lstm", B, T, N, D, seed=17, random_init=True, dtype=torch.float16)
+    got16 = run_native("lstm", Wx16, R16, b16, s16, dtype=torch.float16, batch_tile=128)
+    assert_parity("lstm", got16, run_oracle("lstm", Wx16, R16, b16, s16), tag="wide lstm f16", zero_init=False)
+
+
+def test_wide_lstm_forward_is_the_default_for_large_batches():
+    big = nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True))
+    assert (big.wide_forward, big.batch_tile, big.cluster_size) == (1, 16, 1)
+    assert nv.query(nv.make_problem("lstm", 64, 16, 16, 64, False, True)).wide_forward == 0
+    assert nv.query(nv.make_problem("lstm", 512, 16, 16, 64, False, True)).wide_forward == 0  # 64 CTAs of 128 rows: too few
+    assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, True, True)).wide_forward == 0  # fp32 states
+    assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 128, False, True)).wide_forward == 0
+    assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True), 1, 16).wide_forward == 0  # a forced tile
+    assert nv.query(nv.make_problem("gru", 1024, 16, 16, 64, False, True)).wide_forward == 0
