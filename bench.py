@@ -442,7 +442,8 @@ def measure(job: Job, function, B, T, N, D, f32, *, allreduce, group=True, clust
         "ms_per_step": ms, "ms_per_step_best": min(block_ms), "blocks": nblocks, "timed_seconds": sum(block_ms) * args.steps * 1e-3,
         "kernel_ms": {"forward_loop": fwd_ms, "backward_loop": bwd_ms, "recurrent_grad": dr_ms},
         "us_per_time_step": {"forward": 1e3 * fwd_ms / T, "backward": 1e3 * bwd_ms / T},
-        "tile": {"cluster_size": plan.cluster_size, "units_per_cta": plan.units_per_cta, "batch_tile": plan.batch_tile, "threads": plan.threads},
+        "tile": {"cluster_size": plan.cluster_size, "units_per_cta": plan.units_per_cta, "batch_tile": plan.batch_tile, "threads": plan.threads,
+                 "wide_forward": int(plan.wide_forward)},  # 1: forward loop on the 128-row tcgen05 kernel (LSTM, head dim 64)
         "roofline": {
             "bound": "hbm", "kernel": "wide_bwd_elman_kernel (reverse time loop, dR and db inside)" if wide else "frnn_bwd_kernel (reverse time loop)",
             "achieved": achieved, "peak": job.hbm_peak, "unit": "GB/s", "frac": achieved / job.hbm_peak, "peak_source": job.peak_source,
