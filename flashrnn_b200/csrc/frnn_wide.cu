@@ -513,10 +513,17 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         }
       }
     }
-    // c_t -> states[1][b][t][n][:];  cache: 16-row tiles of the reverse loop, see WideLstmParams
-    elem_t* c_out = p.states + (((size_t)B + (row_ok ? b : 0)) * T) * ND + (size_t)n * WD;
+    // c_t -> states[1][b][t][n][:];  cache: 16-row tiles of the reverse loop, see WideLstmParams.  Pointers to this lane's
+    // 32-byte slot (units 32 half + 16 odd ..) in the even and in the odd row of its lane pair.
+    const bool odd = (lane & 1) != 0;
+    const int be = b & ~1;
+    const bool ok_e = be < B, ok_o = be + 1 < B;
+    elem_t* c_e = p.states + (((size_t)B + (ok_e ? be : 0)) * T) * ND + (size_t)n * WD + 32 * half + (odd ? 16 : 0);
+    elem_t* c_o = c_e + (size_t)T * ND;
     const size_t tiles16 = (size_t)((B + 15) / 16);
-    uint32_t* ch = p.cache ? p.cache + (((size_t)n * tiles16 + (size_t)(b >> 4)) * WL_G) * 512 + (size_t)(b & 15) * 32 : nullptr;
+    uint32_t* ch_e = p.cache ? p.cache + (((size_t)n * tiles16 + (size_t)(be >> 4)) * WL_G) * 512 + (size_t)(be & 15) * 32 + 16 * half + (odd ? 8 : 0)
+                             : nullptr;
+    uint32_t* ch_o = ch_e ? ch_e + 32 : nullptr;
     const size_t ch_step = (size_t)N * tiles16 * WL_G * 512;
     for (int t = 0; t < T; ++t) {
       if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); break; }
@@ -563,21 +570,25 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
       fence_proxy_async_smem();  // the tile is read by the tensor core and by the bulk store
       tc_fence_before();
       mbar_arrive(h_ready);
-      if (row_ok) {  // 64 contiguous bytes per value kind: two 32-byte stores, each one whole sector
-        uint4* cdst = reinterpret_cast<uint4*>(c_out) + 4 * half;
-        st_global_32B(cdst, out[0][0], out[0][1]);
-        st_global_32B(cdst + 2, out[0][2], out[0][3]);
-        if (ch != nullptr) {
+      // A thread owns 64 contiguous bytes per value kind.  Neighbouring lanes (rows 2m, 2m+1) swap halves so that each of
+      // the two store instructions covers 16 rows x 64 contiguous bytes instead of 32 rows x 32: the memory system is
+      // charged per piece of a 128-byte line, and this halves the pieces.
 #pragma unroll
-          for (int g = 0; g < WL_G; ++g) {
-            uint4* gdst = reinterpret_cast<uint4*>(ch + 512 * g) + 4 * half;
-            st_global_32B(gdst, out[1 + g][0], out[1 + g][1]);
-            st_global_32B(gdst + 2, out[1 + g][2], out[1 + g][3]);
-          }
-        }
+      for (int k = 0; k < 1 + WL_G; ++k) {
+        if (k > 0 && ch_e == nullptr) break;
+        const uint4 s0 = odd ? out[k][0] : out[k][2], s1 = odd ? out[k][1] : out[k][3];
+        uint4 r0, r1;
+        r0.x = __shfl_xor_sync(0xffffffffu, s0.x, 1); r0.y = __shfl_xor_sync(0xffffffffu, s0.y, 1);
+        r0.z = __shfl_xor_sync(0xffffffffu, s0.z, 1); r0.w = __shfl_xor_sync(0xffffffffu, s0.w, 1);
+        r1.x = __shfl_xor_sync(0xffffffffu, s1.x, 1); r1.y = __shfl_xor_sync(0xffffffffu, s1.y, 1);
+        r1.z = __shfl_xor_sync(0xffffffffu, s1.z, 1); r1.w = __shfl_xor_sync(0xffffffffu, s1.w, 1);
+        void* de = k == 0 ? static_cast<void*>(c_e) : static_cast<void*>(ch_e + 512 * (k - 1));
+        void* dn = k == 0 ? static_cast<void*>(c_o) : static_cast<void*>(ch_o + 512 * (k - 1));
+        if (ok_e) st_global_32B(de, odd ? r0 : out[k][0], odd ? r1 : out[k][1]);
+        if (ok_o) st_global_32B(dn, odd ? out[k][2] : r0, odd ? out[k][3] : r1);
       }
-      c_out += ND;
-      if (ch != nullptr) ch += ch_step;
+      c_e += ND; c_o += ND;
+      if (ch_e != nullptr) { ch_e += ch_step; ch_o += ch_step; }
 
     }
   }
