@@ -389,7 +389,7 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   if (plan->wide_forward) {  // LSTM, head dim 64: 128-row forward loop; cache in the layout of the reverse loop's tile
     if (plan->probe_noop_cell) return FRNN_ERR_PLAN;
     e = launch_wide_lstm_forward(a->Wx, wxs[0], wxs[1], wxs[2], wxs[3], a->R, a->b, a->s0, a->states, pr.training ? a->cache : nullptr,
-                                 reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, stream);
+                                 reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, plan->test_drop_exchange, stream);
     return (int)(e == cudaSuccess ? copy_last() : e);
   }
   if (!plan->keep_packed_r) e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);

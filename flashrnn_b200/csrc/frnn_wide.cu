@@ -323,6 +323,7 @@ struct WideLstmParams {
   uint32_t* cache;     // reverse loop's layout (16-row tiles): [t][head][tile][slot][row in tile][unit pair]; or null
   unsigned* status;
   int B, T, N;
+  int test_drop;  // test hook: the copy of one Wx box (step index 2) is announced to its barrier but never issued
 };
 constexpr int WL_G = 4;
 constexpr int WL_AHEAD = 6;     // steps between the L2 prefetch of a Wx box and its copy into shared memory
@@ -431,7 +432,8 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
       int loads = 0, seen = 0;  // Wx stages requested / seen to land (both in step order)
       auto load_wx = [&](int t) {  // [4 gates][128 rows][64] of step t -> stage t & 1
         mbar_arrive_expect_tx(&wx_full[t & 1], WL_G * WTILE);
-        tma_load_5d(base + WL_OFF_WX + (uint32_t)(t & 1) * WL_G * WTILE, tmw, 0, b0, 0, n, t, &wx_full[t & 1]);
+        if (!(p.test_drop && t == 2))
+          tma_load_5d(base + WL_OFF_WX + (uint32_t)(t & 1) * WL_G * WTILE, tmw, 0, b0, 0, n, t, &wx_full[t & 1]);
         ++loads;
       };
       auto wait_wx = [&](int t) {
@@ -1077,7 +1079,7 @@ bool wide_lstm_forward_supported(int cell, int D, int state_f32, float fclip) {
 
 cudaError_t launch_wide_lstm_forward(const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
                                      const void* bias, const void* s0, void* states, void* cache, unsigned* status, int B, int T,
-                                     int N, cudaStream_t stream) {
+                                     int N, int test_drop, cudaStream_t stream) {
   CUtensorMap tm_wx, tm_st;
   if (!map_wx_gates(&tm_wx, Wx, B, T, N, wx_sb, wx_st, wx_sg, wx_sn) || !map_sbtnd(&tm_st, states, B, T, N, dense_strides(T, N)))
     return cudaErrorNotSupported;
@@ -1089,6 +1091,7 @@ cudaError_t launch_wide_lstm_forward(const void* Wx, long long wx_sb, long long 
   p.cache = static_cast<uint32_t*>(cache);
   p.status = status;
   p.B = B; p.T = T; p.N = N;
+  p.test_drop = test_drop;
   cudaError_t e = cudaFuncSetAttribute(wide_fwd_lstm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WL_SMEM);
   if (e != cudaSuccess) return e;
   wide_fwd_lstm_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), WL_THREADS, WL_SMEM, stream>>>(tm_wx, tm_st, p);

@@ -83,8 +83,8 @@ typedef struct frnn_plan {
   int32_t test_drop_exchange; /* TEST HOOK, leave 0.  1: CTA 0 of every cluster withholds one exchange message
                                  (forward: its h of step 1; backward: its first message) so that its peers' bounded
                                  waits expire; the kernels then finish with invalid results and report it in the
-                                 status block (float32 cluster loops: the message of step 1 in both loops).  With the 128-row loops (batch_tile 128): one tile copy (step index 2)
-                                 is announced to its barrier and never issued.  Exercises the failure-detection path
+                                 status block (float32 cluster loops: the message of step 1 in both loops).  With the 128-row loops (batch_tile 128, or wide_forward): one tile copy (step
+                                 index 2) is announced to its barrier and never issued.  Exercises the failure-detection path
                                  without faulting the GPU.                                                          */
   int32_t keep_packed_r;      /* 0: frnn_forward clears the status block and repacks R into the workspace (default).
                                  1: the workspace is as an earlier frnn_forward with this plan left it and R has not

@@ -138,3 +138,20 @@ def test_float32_cluster_loops_report_a_withheld_message(cuda_device):
     nv.check("frnn_backward", L.frnn_backward(ctypes.byref(plan), ctypes.byref(ba), stream))
     nv.check("status", L.frnn_read_device_status(P(ws), stream, ctypes.byref(st)))
     assert st.code == 0 and torch.isfinite(dWx).all()
+
+
+def test_wide_lstm_forward_reports_a_copy_that_never_lands(cuda_device):
+    """128-row LSTM forward loop: the copy of one Wx box is announced and never issued; the issuing thread and the row
+    threads give up after their bounded waits and report it; a clean run follows in the same context."""
+    Wx, R, b, s0 = [t.to(cuda_device, torch.bfloat16) for t in make_inputs("lstm", 128, 8, 2, 64, seed=7)]
+    bad = FlashRNNConfig(function="lstm", head_dim=64, num_heads=2, batch_size=128, batch_tile=128,
+                         check_device_status=True, _test_drop_exchange=True)
+    t0 = time.time()
+    with pytest.raises(RuntimeError, match="device-side wait expired in the forward"):
+        with torch.no_grad():
+            flashrnn(Wx, R, b, s0, function="lstm", config=bad)
+    assert time.time() - t0 < 20.0
+    ok = FlashRNNConfig(function="lstm", head_dim=64, num_heads=2, batch_size=128, batch_tile=128, check_device_status=True)
+    with torch.no_grad():
+        states, _ = flashrnn(Wx, R, b, s0, function="lstm", config=ok)
+    assert torch.isfinite(states.float()).all()
