@@ -45,6 +45,7 @@ WORKLOADS = {
     "C5s": ("elman", 1024, 256, 16, 64, False),  # C5 with T cut to 256 (2.1 GB resident): the size ncu captures use
     "LB": ("lstm", 1024, 512, 16, 64, False),    # large-batch LSTM (the reference's batch-size sweeps): 16-row tiles, HBM-side regime
     "LBs": ("lstm", 512, 128, 16, 64, False),    # LB cut to 0.7 GB resident (512 CTAs, same tile): the size ncu captures use
+    "GB": ("gru", 1024, 512, 16, 64, False),     # large-batch GRU, as LB
 }
 DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm": (4, 4, 4, 4)}
 METRIC = "fwd+bwd tokens/sec (B*T/s)"

@@ -59,10 +59,10 @@ cudaError_t launch_wide_forward(const void* Wx, long long wx_sb, long long wx_st
 cudaError_t launch_wide_backward(const void* R, const void* s0, const void* states, const void* dstates, long long ds_sb,
                                  long long ds_st, long long ds_sn, void* dWx, void* ds0, float* dR, float* dbias,
                                  unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream);
-// 128-row forward loop of the LSTM cell at head dim 64 (frnn_wide.cu); writes the activation cache in the layout of the
+// 128-row forward loop of the LSTM and GRU cells at head dim 64 (frnn_wide.cu); writes the activation cache in the layout of the
 // cluster kernels' tile (1 CTA per head, 16 batch rows), which runs the reverse loop
-bool wide_lstm_forward_supported(int cell, int D, int state_f32, float fclip);
-cudaError_t launch_wide_lstm_forward(const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
+bool wide_gates_forward_supported(int cell, int D, int state_f32, float fclip);
+cudaError_t launch_wide_gates_forward(int cell, const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
                                      const void* bias, const void* s0, void* states, void* cache, unsigned* status, int B, int T,
                                      int N, int test_drop, cudaStream_t stream);
 // dR fed by tensor-map bulk copies (frnn_dr_tma.cu): bf16 states, head dims 64 .. 256 in steps of 64

@@ -302,8 +302,9 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 }
 
 
-// ================================================================================================ LSTM forward
-// The same loop for the four-gate LSTM cell at head dim 64: the accumulator of a step is [128 rows][4 gates x 64] fp32 =
+// ================================================================================================ LSTM / GRU forward
+// The same loop for the multi-gate cells at head dim 64, described for the four-gate LSTM cell (the GRU differs as noted
+// at the kernel): the accumulator of a step is [128 rows][4 gates x 64] fp32 =
 // 256 columns of tensor memory (two of them alternate), filled by
 //   acc[:, g] = Wx_t[g] * I  (4 gates x 4 MMAs, N = 64)  +  1 * b  (one MMA, N = 256)      -- issued ahead of the step
 //   acc      += h_{t-1} * R^T                             (4 MMAs, N = 256; R as [4*64 rows][64 k])
@@ -315,7 +316,7 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 // 16 batch rows: frnn_bwd_kernel reads it as it reads its forward kernel's), so only the forward loop changes.
 // Wx_t arrives as one tensor-map copy of [4 gates][128 rows][64] per step into a ring of two 64 KB stages; the stage of
 // step t is refilled with step t+2 as soon as the step's MMAs are known to have completed.
-struct WideLstmParams {
+struct WideGatesParams {
   const elem_t* R;     // [4,N,64,64]
   const elem_t* bias;  // [4,N,64]
   const elem_t* s0;    // [2,B,1,N,64]
@@ -360,8 +361,12 @@ __device__ __forceinline__ void tmem_ld16x4(uint32_t t0, uint32_t t1, uint32_t t
       : "r"(t0), "r"(t1), "r"(t2), "r"(t3) : "memory");
 }
 
+// CELL: CELL_LSTM, or CELL_GRU -- three input gates (r, z, n) and three recurrent ones (g~, r, z): accumulator columns
+// [g~ | r | z | n] = [R0 h + b0 | Wx0 + R1 h + b1 | Wx1 + R2 h + b2 | Wx2 + b3], so the recurrent product covers the first
+// 192 columns, the input gates the last 192, and the row threads carry h instead of c.
+template <int CELL>
 __global__ void __launch_bounds__(WL_THREADS, 1)
-wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states, const WideLstmParams p) {
+wide_fwd_gates_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_constant__ CUtensorMap tm_states, const WideGatesParams p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -371,11 +376,15 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
   uint64_t* h_ready = acc_full + 2;                                  // 256 arrivals: h_t is in shared memory
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(h_ready + 1);
 
+  constexpr bool GRU = CELL == CELL_GRU;
+  constexpr int NGW = GRU ? 3 : 4;         // gates of Wx
+  constexpr int NGR = GRU ? 3 : 4;         // gates of R
+  constexpr uint32_t WX_COL0 = GRU ? WD : 0;  // accumulator column of the first Wx gate
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n = blockIdx.y, b0 = blockIdx.x * WM, T = p.T, N = p.N, B = p.B;
 
   // ---- operands written once
-  for (int c = tid; c < WL_G * WD * 8; c += WL_THREADS) {  // R: row j = g * 64 + d holds R[g][n][d][:]
+  for (int c = tid; c < NGR * WD * 8; c += WL_THREADS) {  // R: row j = g * 64 + d holds R[g][n][d][:]
     const uint32_t j = c >> 3, q = c & 7, g = j >> 6, d = j & 63;
     *reinterpret_cast<uint4*>(sm + WL_OFF_R + sw128(j, q)) =
         *reinterpret_cast<const uint4*>(p.R + (((size_t)g * N + n) * WD + d) * WD + q * 8);
@@ -422,7 +431,8 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
   if (warp == 8) {
     if (lane == 0) {
       // ------------------------------------------------------------ producer: bulk copies and MMAs
-      const uint32_t idesc64 = instr_desc_16(WM, WD, 0, 0), idesc256 = instr_desc_16(WM, WL_G * WD, 0, 0);
+      const uint32_t idesc64 = instr_desc_16(WM, WD, 0, 0), idesc256 = instr_desc_16(WM, WL_G * WD, 0, 0),
+                     idesc_r = instr_desc_16(WM, NGR * WD, 0, 0);
       const void* tmw = &tm_wx;
       const void* tms = &tm_states;
       constexpr uint32_t HI = desc_hi(1024, true), HIP = desc_hi(256, false), TILE16 = WTILE >> 4;
@@ -431,7 +441,7 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
                      bias_lo = ((base + WL_OFF_BIAS) >> 4) | ((128u >> 4) << 16);
       int loads = 0, seen = 0;  // Wx stages requested / seen to land (both in step order)
       auto load_wx = [&](int t) {  // [4 gates][128 rows][64] of step t -> stage t & 1
-        mbar_arrive_expect_tx(&wx_full[t & 1], WL_G * WTILE);
+        mbar_arrive_expect_tx(&wx_full[t & 1], NGW * WTILE);
         if (!(p.test_drop && t == 2))
           tma_load_5d(base + WL_OFF_WX + (uint32_t)(t & 1) * WL_G * WTILE, tmw, 0, b0, 0, n, t, &wx_full[t & 1]);
         ++loads;
@@ -441,13 +451,13 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         seen = t + 1;
         return true;
       };
-      auto issue_pre = [&](int t) {  // acc[t & 1] = Wx_t * I (per gate) + ones * bias
+      auto issue_pre = [&](int t) {  // acc[t & 1] = ones * bias (all 256 columns, overwriting), then += Wx_t[g] * I per gate
         const uint32_t d = tmem + (uint32_t)(t & 1) * (WL_G * WD), a = wx_lo + (uint32_t)(t & 1) * WL_G * TILE16;
+        umma_parts(d, ones_lo, HIP, bias_lo, HIP, idesc256, 0u);
 #pragma unroll
-        for (uint32_t g = 0; g < WL_G; ++g)
+        for (uint32_t g = 0; g < (uint32_t)NGW; ++g)
 #pragma unroll
-          for (uint32_t k = 0; k < 4; ++k) umma_parts(d + g * WD, a + g * TILE16 + 2 * k, HI, i_lo + 2 * k, HI, idesc64, k);
-        umma_parts(d, ones_lo, HIP, bias_lo, HIP, idesc256, 1u);
+          for (uint32_t k = 0; k < 4; ++k) umma_parts(d + WX_COL0 + g * WD, a + g * TILE16 + 2 * k, HI, i_lo + 2 * k, HI, idesc64, 1u);
       };
       // With two stages only one or two copies are in flight, and a box is 512 pieces of 128 bytes on 128 different pages
       // (batch rows lie far apart): each box is asked into L2 WL_AHEAD steps before its copy into shared memory.
@@ -466,7 +476,7 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         bulk_wait_group_read<0>();
         const uint32_t a = h_lo + (uint32_t)((t + 1) & 1) * TILE16, d = tmem + (uint32_t)(t & 1) * (WL_G * WD);
 #pragma unroll
-        for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc256, 1u);
+        for (uint32_t k = 0; k < 4; ++k) umma_parts(d, a + 2 * k, HI, r_lo + 2 * k, HI, idesc_r, 1u);
         umma_commit(&acc_full[t & 1]);
         if (t > 0) {  // h_{t-1} -> states[0][b0.., t-1, n, :]
           tma_store_5d(tms, base + WL_OFF_H + (uint32_t)((t - 1) & 1) * WTILE, 0, n, t - 1, b0, 0);
@@ -500,9 +510,9 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
     const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const int b = b0 + row;
     const size_t ND = (size_t)N * WD;
-    float cst[32];  // cell state of this half row, fp32 over all steps
+    float cst[32];  // LSTM: cell state c of this half row (fp32 over all steps); GRU: h_{t-1}, as rounded to 16 bits
     {
-      const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)B + (row_ok ? b : 0)) * ND + (size_t)n * WD + 32 * half);
+      const uint4* src = reinterpret_cast<const uint4*>(p.s0 + ((size_t)(GRU ? 0 : B) + (row_ok ? b : 0)) * ND + (size_t)n * WD + 32 * half);
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint4 w = row_ok ? src[j] : make_uint4(0u, 0u, 0u, 0u);
@@ -515,7 +525,7 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         }
       }
     }
-    // c_t -> states[1][b][t][n][:];  cache: 16-row tiles of the reverse loop, see WideLstmParams.  Pointers to this lane's
+    // c_t -> states[1][b][t][n][:];  cache: 16-row tiles of the reverse loop, see WideGatesParams.  Pointers to this lane's
     // 32-byte slot (units 32 half + 16 odd ..) in the even and in the odd row of its lane pair.
     const bool odd = (lane & 1) != 0;
     const int be = b & ~1;
@@ -538,16 +548,24 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         const int q = 2 * half + qq;
         uint32_t ri[16], rf[16], rz[16], ro[16];
         tmem_ld16x4(acc + 16 * q, acc + WD + 16 * q, acc + 2 * WD + 16 * q, acc + 3 * WD + 16 * q, ri, rf, rz, ro);
-        float hv[16], gi[16], gf[16], gz[16], go[16];
+        float hv[16], gi[16], gf[16], gz[16], go[16];  // h_t and the four cached values (LSTM: i, f, z, o; GRU: g~, r, z, n)
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          gi[j] = fast_sigmoid(__uint_as_float(ri[j]));
-          gf[j] = fast_sigmoid(__uint_as_float(rf[j]));
-          gz[j] = fast_tanh(__uint_as_float(rz[j]));
-          go[j] = fast_sigmoid(__uint_as_float(ro[j]));
-          const float c = gf[j] * cst[16 * qq + j] + gi[j] * gz[j];
-          cst[16 * qq + j] = c;
-          hv[j] = go[j] * fast_tanh(c);
+          if constexpr (GRU) {
+            gi[j] = __uint_as_float(ri[j]);
+            gf[j] = fast_sigmoid(__uint_as_float(rf[j]));
+            gz[j] = fast_sigmoid(__uint_as_float(rz[j]));
+            go[j] = fast_tanh(__uint_as_float(ro[j]) + gf[j] * gi[j]);
+            hv[j] = gz[j] * cst[16 * qq + j] + (1.f - gz[j]) * go[j];
+          } else {
+            gi[j] = fast_sigmoid(__uint_as_float(ri[j]));
+            gf[j] = fast_sigmoid(__uint_as_float(rf[j]));
+            gz[j] = fast_tanh(__uint_as_float(rz[j]));
+            go[j] = fast_sigmoid(__uint_as_float(ro[j]));
+            const float c = gf[j] * cst[16 * qq + j] + gi[j] * gz[j];
+            cst[16 * qq + j] = c;
+            hv[j] = go[j] * fast_tanh(c);
+          }
         }
         auto pack16 = [](const float (&v)[16], uint4& lo, uint4& hi) {
           lo = make_uint4(pack_x2(v[0], v[1]), pack_x2(v[2], v[3]), pack_x2(v[4], v[5]), pack_x2(v[6], v[7]));
@@ -557,10 +575,20 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
         pack16(hv, lo, hi);
         *reinterpret_cast<uint4*>(hdst + sw128(row, 2 * q)) = lo;
         *reinterpret_cast<uint4*>(hdst + sw128(row, 2 * q + 1)) = hi;
-        float cv[16];
+        if constexpr (GRU) {  // the recurrence continues from the rounded h, the value every reader of `states` sees
 #pragma unroll
-        for (int j = 0; j < 16; ++j) cv[j] = cst[16 * qq + j];
-        pack16(cv, out[0][2 * qq], out[0][2 * qq + 1]);
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t wl[4] = {lo.x, lo.y, lo.z, lo.w}, wh[4] = {hi.x, hi.y, hi.z, hi.w};
+            const float2 a2 = unpack_x2(wl[e]), b2 = unpack_x2(wh[e]);
+            cst[16 * qq + 2 * e] = a2.x; cst[16 * qq + 2 * e + 1] = a2.y;
+            cst[16 * qq + 8 + 2 * e] = b2.x; cst[16 * qq + 8 + 2 * e + 1] = b2.y;
+          }
+        } else {
+          float cv[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) cv[j] = cst[16 * qq + j];
+          pack16(cv, out[0][2 * qq], out[0][2 * qq + 1]);
+        }
         pack16(gi, out[1][2 * qq], out[1][2 * qq + 1]);
         pack16(gf, out[2][2 * qq], out[2][2 * qq + 1]);
         pack16(gz, out[3][2 * qq], out[3][2 * qq + 1]);
@@ -576,7 +604,7 @@ wide_fwd_lstm_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_con
       // the two store instructions covers 16 rows x 64 contiguous bytes instead of 32 rows x 32: the memory system is
       // charged per piece of a 128-byte line, and this halves the pieces.
 #pragma unroll
-      for (int k = 0; k < 1 + WL_G; ++k) {
+      for (int k = GRU ? 1 : 0; k < 1 + WL_G; ++k) {  // (the GRU has no second state)
         if (k > 0 && ch_e == nullptr) break;
         const uint4 s0 = odd ? out[k][0] : out[k][2], s1 = odd ? out[k][1] : out[k][3];
         uint4 r0, r1;
@@ -1035,10 +1063,11 @@ bool map_pairs(CUtensorMap* tm, const void* base, int B, int T, int N, RowStride
 bool pairs_ok(int B, int T) { return B % 8 == 0 && T >= 2; }
 
 // Wx [B,T,4,N,64] seen as (d, b, g, n, t): one box [4 gates][128 rows][64] per (tile, head, step)
-bool map_wx_gates(CUtensorMap* tm, const void* base, int B, int T, int N, long long sb, long long st, long long sg, long long sn) {
-  const uint64_t dims[5] = {WD, (uint64_t)B, WL_G, (uint64_t)N, (uint64_t)T};
+bool map_wx_gates(CUtensorMap* tm, const void* base, int gates, int B, int T, int N, long long sb, long long st, long long sg,
+                  long long sn) {
+  const uint64_t dims[5] = {WD, (uint64_t)B, (uint64_t)gates, (uint64_t)N, (uint64_t)T};
   const uint64_t strides[4] = {(uint64_t)sb * 2, (uint64_t)sg * 2, (uint64_t)sn * 2, (uint64_t)st * 2};
-  const uint32_t box[5] = {WD, WM, WL_G, 1, 1};
+  const uint32_t box[5] = {WD, WM, (uint32_t)gates, 1, 1};
   return encode_tiles16(tm, base, dims, strides, box);
 }
 
@@ -1071,19 +1100,20 @@ cudaError_t launch_wide_forward(const void* Wx, long long wx_sb, long long wx_st
   return cudaGetLastError();
 }
 
-// 128-row forward loop of the LSTM cell at head dim 64 (16-bit states, no forward clamp); the reverse loop stays on the
-// cluster kernels' 16-row tiles, whose cache layout the forward loop writes
-bool wide_lstm_forward_supported(int cell, int D, int state_f32, float fclip) {
-  return cell == CELL_LSTM && D == WD && !state_f32 && !(fclip > 0.f);
+// 128-row forward loop of the LSTM and GRU cells at head dim 64 (16-bit states, no forward clamp); the reverse loop stays
+// on the cluster kernels' 16-row tiles, whose cache layout the forward loop writes
+bool wide_gates_forward_supported(int cell, int D, int state_f32, float fclip) {
+  return (cell == CELL_LSTM || cell == CELL_GRU) && D == WD && !state_f32 && !(fclip > 0.f);
 }
 
-cudaError_t launch_wide_lstm_forward(const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
+cudaError_t launch_wide_gates_forward(int cell, const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
                                      const void* bias, const void* s0, void* states, void* cache, unsigned* status, int B, int T,
                                      int N, int test_drop, cudaStream_t stream) {
   CUtensorMap tm_wx, tm_st;
-  if (!map_wx_gates(&tm_wx, Wx, B, T, N, wx_sb, wx_st, wx_sg, wx_sn) || !map_sbtnd(&tm_st, states, B, T, N, dense_strides(T, N)))
+  if (!map_wx_gates(&tm_wx, Wx, cell == CELL_GRU ? 3 : 4, B, T, N, wx_sb, wx_st, wx_sg, wx_sn) ||
+      !map_sbtnd(&tm_st, states, B, T, N, dense_strides(T, N)))
     return cudaErrorNotSupported;
-  WideLstmParams p;
+  WideGatesParams p;
   p.R = static_cast<const elem_t*>(R);
   p.bias = static_cast<const elem_t*>(bias);
   p.s0 = static_cast<const elem_t*>(s0);
@@ -1092,9 +1122,10 @@ cudaError_t launch_wide_lstm_forward(const void* Wx, long long wx_sb, long long 
   p.status = status;
   p.B = B; p.T = T; p.N = N;
   p.test_drop = test_drop;
-  cudaError_t e = cudaFuncSetAttribute(wide_fwd_lstm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WL_SMEM);
+  auto kern = cell == CELL_GRU ? wide_fwd_gates_kernel<CELL_GRU> : wide_fwd_gates_kernel<CELL_LSTM>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WL_SMEM);
   if (e != cudaSuccess) return e;
-  wide_fwd_lstm_kernel<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), WL_THREADS, WL_SMEM, stream>>>(tm_wx, tm_st, p);
+  kern<<<dim3((unsigned)((B + WM - 1) / WM), (unsigned)N), WL_THREADS, WL_SMEM, stream>>>(tm_wx, tm_st, p);
   return cudaGetLastError();
 }
 

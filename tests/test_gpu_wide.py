@@ -46,18 +46,20 @@ def test_wide_is_the_default_for_large_batches():
     assert nv.query(nv.make_problem("elman", 1024, 16, 16, 64, True, True)).batch_tile == 8
 
 
+@pytest.mark.parametrize("function", ["lstm", "gru"])
 @pytest.mark.parametrize("B,T,N", [(128, 5, 1), (128, 1, 2), (128, 2, 1), (130, 9, 2), (37, 12, 3), (300, 33, 2), (264, 34, 3), (8, 3, 1)])
-def test_wide_lstm_forward_matches_oracle(cuda_device, B, T, N):
-    """LSTM, head dim 64: the forward loop on the 128-row tensor-core kernel (forced with batch_tile=128), the reverse
-    loop on 16-row tiles that read the cache the forward loop wrote: states and every gradient against the oracle."""
-    plan = nv.query(nv.make_problem("lstm", B, T, N, 64, False, True), 0, 128)
+def test_wide_lstm_forward_matches_oracle(cuda_device, function, B, T, N):
+    """LSTM and GRU, head dim 64: the forward loop on the 128-row tensor-core kernel (forced with batch_tile=128), the
+    reverse loop on 16-row tiles that read the cache the forward loop wrote: states and every gradient against the oracle."""
+    plan = nv.query(nv.make_problem(function, B, T, N, 64, False, True), 0, 128)
     assert (plan.wide_forward, plan.cluster_size, plan.batch_tile) == (1, 1, 16)
-    Wx, R, b, s0 = make_inputs("lstm", B, T, N, 64, seed=B + T, random_init=True)
+    Wx, R, b, s0 = make_inputs(function, B, T, N, 64, seed=B + T, random_init=True)
+    S = s0.shape[0]
     g = torch.Generator().manual_seed(11)
-    cot = torch.randn(2, B, T, N, 64, generator=g, dtype=torch.float64).to(torch.bfloat16).to(torch.float64)
-    got = run_native("lstm", Wx, R, b, s0, cot=cot, batch_tile=128)
-    ref = run_oracle("lstm", Wx, R, b, s0, cot=cot)
-    errs = assert_parity("lstm", got, ref, tag=f"wide lstm B{B} T{T} N{N}", zero_init=False)
+    cot = torch.randn(S, B, T, N, 64, generator=g, dtype=torch.float64).to(torch.bfloat16).to(torch.float64)
+    got = run_native(function, Wx, R, b, s0, cot=cot, batch_tile=128)
+    ref = run_oracle(function, Wx, R, b, s0, cot=cot)
+    errs = assert_parity(function, got, ref, tag=f"wide {function} B{B} T{T} N{N}", zero_init=False)
     assert errs["h"] < 1.5e-2
 
 
@@ -96,4 +98,5 @@ def test_wide_lstm_forward_is_the_default_for_large_batches():
     assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, True, True)).wide_forward == 0  # fp32 states
     assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 128, False, True)).wide_forward == 0
     assert nv.query(nv.make_problem("lstm", 1024, 16, 16, 64, False, True), 1, 16).wide_forward == 0  # a forced tile
-    assert nv.query(nv.make_problem("gru", 1024, 16, 16, 64, False, True)).wide_forward == 0
+    assert nv.query(nv.make_problem("gru", 1024, 16, 16, 64, False, True)).wide_forward == 1
+    assert nv.query(nv.make_problem("slstm", 1024, 16, 16, 64, False, True)).wide_forward == 0
