@@ -92,7 +92,7 @@ static bool wide_problem(const frnn_problem& pr) {
 static bool is_wide(const frnn_plan& pl) { return pl.batch_tile == kWideBatchTile; }
 // LSTM and GRU at head dim 64: the forward loop alone has a 128-row form (the reverse loop stays on 16-row tiles)
 static bool wide_gates_problem(const frnn_problem& pr) {
-  return wide_gates_forward_supported(pr.cell, pr.D, pr.dtype_state == FRNN_DTYPE_F32, pr.forward_clip);
+  return wide_gates_forward_supported(pr.cell, pr.D, pr.dtype_state == FRNN_DTYPE_F32);
 }
 static int plan_threads(const CellDims& cd, int units, int bt) { return bt == kWideBatchTile ? kWideThreads : 2 * cd.Gr * units; }
 
@@ -389,7 +389,7 @@ int FRNN_ENTRY(frnn_forward)(const frnn_plan* plan, const frnn_fwd_args* a, void
   if (plan->wide_forward) {  // LSTM / GRU, head dim 64: 128-row forward loop; cache in the layout of the reverse loop's tile
     if (plan->probe_noop_cell) return FRNN_ERR_PLAN;
     e = launch_wide_gates_forward(pr.cell, a->Wx, wxs[0], wxs[1], wxs[2], wxs[3], a->R, a->b, a->s0, a->states, pr.training ? a->cache : nullptr,
-                                 reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, plan->test_drop_exchange, stream);
+                                 reinterpret_cast<unsigned*>(ws), pr.B, pr.T, pr.N, pr.forward_clip, plan->test_drop_exchange, stream);
     return (int)(e == cudaSuccess ? copy_last() : e);
   }
   if (!plan->keep_packed_r) e = launch_pack_recurrent(a->R, ws + w.rpack_fwd, cd.Gr, pr.N, pr.D, 0, stream);

@@ -61,10 +61,10 @@ cudaError_t launch_wide_backward(const void* R, const void* s0, const void* stat
                                  unsigned* status, int B, int T, int N, int test_drop, cudaStream_t stream);
 // 128-row forward loop of the LSTM and GRU cells at head dim 64 (frnn_wide.cu); writes the activation cache in the layout of the
 // cluster kernels' tile (1 CTA per head, 16 batch rows), which runs the reverse loop
-bool wide_gates_forward_supported(int cell, int D, int state_f32, float fclip);
+bool wide_gates_forward_supported(int cell, int D, int state_f32);
 cudaError_t launch_wide_gates_forward(int cell, const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
                                      const void* bias, const void* s0, void* states, void* cache, unsigned* status, int B, int T,
-                                     int N, int test_drop, cudaStream_t stream);
+                                     int N, float fclip, int test_drop, cudaStream_t stream);
 // dR fed by tensor-map bulk copies (frnn_dr_tma.cu): bf16 states, head dims 64 .. 256 in steps of 64
 bool recurrent_grad_tma_supported(int D, int state_f32);
 cudaError_t launch_recurrent_grad_tma(int cell, int B, int T, int N, int D, int Gr, int Gw, const void* dWx, const void* dg0,

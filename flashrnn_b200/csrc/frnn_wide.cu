@@ -325,6 +325,7 @@ struct WideGatesParams {
   unsigned* status;
   int B, T, N;
   int test_drop;  // test hook: the copy of one Wx box (step index 2) is announced to its barrier but never issued
+  float fclip;    // > 0: the new h is clamped to [-fclip, fclip]
 };
 constexpr int WL_G = 4;
 constexpr int WL_AHEAD = 6;     // steps between the L2 prefetch of a Wx box and its copy into shared memory
@@ -566,6 +567,10 @@ wide_fwd_gates_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
             cst[16 * qq + j] = c;
             hv[j] = go[j] * fast_tanh(c);
           }
+        }
+        if (p.fclip > 0.f) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) hv[j] = clampf(hv[j], p.fclip);
         }
         auto pack16 = [](const float (&v)[16], uint4& lo, uint4& hi) {
           lo = make_uint4(pack_x2(v[0], v[1]), pack_x2(v[2], v[3]), pack_x2(v[4], v[5]), pack_x2(v[6], v[7]));
@@ -1100,15 +1105,15 @@ cudaError_t launch_wide_forward(const void* Wx, long long wx_sb, long long wx_st
   return cudaGetLastError();
 }
 
-// 128-row forward loop of the LSTM and GRU cells at head dim 64 (16-bit states, no forward clamp); the reverse loop stays
+// 128-row forward loop of the LSTM and GRU cells at head dim 64 (16-bit states); the reverse loop stays
 // on the cluster kernels' 16-row tiles, whose cache layout the forward loop writes
-bool wide_gates_forward_supported(int cell, int D, int state_f32, float fclip) {
-  return (cell == CELL_LSTM || cell == CELL_GRU) && D == WD && !state_f32 && !(fclip > 0.f);
+bool wide_gates_forward_supported(int cell, int D, int state_f32) {
+  return (cell == CELL_LSTM || cell == CELL_GRU) && D == WD && !state_f32;
 }
 
 cudaError_t launch_wide_gates_forward(int cell, const void* Wx, long long wx_sb, long long wx_st, long long wx_sg, long long wx_sn, const void* R,
                                      const void* bias, const void* s0, void* states, void* cache, unsigned* status, int B, int T,
-                                     int N, int test_drop, cudaStream_t stream) {
+                                     int N, float fclip, int test_drop, cudaStream_t stream) {
   CUtensorMap tm_wx, tm_st;
   if (!map_wx_gates(&tm_wx, Wx, cell == CELL_GRU ? 3 : 4, B, T, N, wx_sb, wx_st, wx_sg, wx_sn) ||
       !map_sbtnd(&tm_st, states, B, T, N, dense_strides(T, N)))
@@ -1122,6 +1127,7 @@ cudaError_t launch_wide_gates_forward(int cell, const void* Wx, long long wx_sb,
   p.status = status;
   p.B = B; p.T = T; p.N = N;
   p.test_drop = test_drop;
+  p.fclip = fclip;
   auto kern = cell == CELL_GRU ? wide_fwd_gates_kernel<CELL_GRU> : wide_fwd_gates_kernel<CELL_LSTM>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)WL_SMEM);
   if (e != cudaSuccess) return e;

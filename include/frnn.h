@@ -98,7 +98,7 @@ typedef struct frnn_plan {
   int32_t wide_forward;       /* 1: the forward loop runs as the 128-row tensor-core loop (tcgen05, one CTA per head and
                                  128 batch rows) while the reverse loop keeps the tile above, whose cache layout the
                                  forward loop writes.  Set by frnn_query for large-batch LSTM and GRU problems at
-                                 head_dim 64 (16-bit states, no forward clamp) on 16-row tiles; frnn_query_tile(cluster_size 1,
+                                 head_dim 64 (16-bit states) on 16-row tiles; frnn_query_tile(cluster_size 1,
                                  batch_tile 128) asks for it, any other forced tile leaves it 0.                       */
   int32_t reserved[2];
   uint64_t cache_bytes;     /* size of the activation cache (opaque layout, tied to this plan) */

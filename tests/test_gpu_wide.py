@@ -85,6 +85,12 @@ def test_wide_lstm_forward_variants(cuda_device):
     with torch.no_grad():
         alt, _ = flashrnn(dev[0].permute(1, 0, 2, 3, 4).contiguous(), dev[1], dev[2], dev[3], function="lstm", config=cfg_t)
     assert torch.equal(inf, alt)
+    for function in ("lstm", "gru"):  # forward clamp and the gradient options (the reverse loop's) on top of the 128-row forward
+        Wc, Rc, bc, sc = make_inputs(function, B, T, N, D, seed=19, random_init=True)
+        gotc = run_native(function, Wc, Rc, bc, sc, batch_tile=128, forward_clipval=0.4, gradient_recurrent_clipval=0.05)
+        assert np.abs(gotc["states"][0]).max() <= 0.4 * (1 + 2.0 ** -8)  # the clamp value as rounded to bfloat16
+        assert_parity(function, gotc, run_oracle(function, Wc, Rc, bc, sc, forward_clip=0.4, clip=0.05), tag=f"wide {function} clip",
+                      zero_init=False)
     Wx16, R16, b16, s16 = make_inputs("lstm", B, T, N, D, seed=17, random_init=True, dtype=torch.float16)
     got16 = run_native("lstm", Wx16, R16, b16, s16, dtype=torch.float16, batch_tile=128)
     assert_parity("lstm", got16, run_oracle("lstm", Wx16, R16, b16, s16), tag="wide lstm f16", zero_init=False)
