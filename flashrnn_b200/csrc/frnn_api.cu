@@ -488,7 +488,8 @@ int FRNN_ENTRY(frnn_backward_parts)(const frnn_plan* plan, const frnn_bwd_args* 
     if (e != cudaSuccess) return (int)e;
   }
   // measured on B200: the tcgen05 kernel wins from head_dim 128 up (C2 0.167 vs 0.212 ms, C3 0.263 vs 0.304 ms) and at
-  // head_dim 64 when the gates fill two 128-row tiles (LSTM B1024 T512 N16 D64: 1.43 vs 1.60 ms); for the one-gate Elman
+  // head_dim 64 when the gates fill two 128-row tiles (LSTM B1024 T512 N16 D64: 1.43 vs 1.60 ms; the GRU's 192 rows, one
+  // and a half tiles, lose: 1.43 vs 1.25 ms); for the one-gate Elman
   // cell at head_dim 64 (half a tile) the warp-MMA kernel with its many small CTAs streams faster (C5 1.55 vs 3.1 ms)
   // (the tcgen05 kernel keeps a whole row tile of dR, N = D <= 256 columns, in one TMEM allocation)
   if ((parts & FRNN_PART_DR) && (pr.D >= 128 || cd.Gr * pr.D >= 256) && recurrent_grad_tma_supported(pr.D, lp.state_f32))
