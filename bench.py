@@ -571,7 +571,7 @@ def run_ours(args):
             return {"value": tokens_per_s(Bw, Tw, ranks, m["ms_per_step"]), "unit": "tokens/s", **more, **m}
 
         if world == 1:
-            for name in ("C3", "C4", "C5", "LB"):
+            for name in ("C3", "C4", "C5", "LB", "GB"):
                 if name == args.workload:
                     continue
                 fn, Bw, Tw, Nw, Dw, f32w = WORKLOADS[name]
