@@ -304,16 +304,18 @@ wide_fwd_elman_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 
 // ================================================================================================ LSTM / GRU forward
 // The same loop for the multi-gate cells at head dim 64, described for the four-gate LSTM cell (the GRU differs as noted
-// at the kernel): the accumulator of a step is [128 rows][4 gates x 64] fp32 =
-// 256 columns of tensor memory (two of them alternate), filled by
-//   acc[:, g] = Wx_t[g] * I  (4 gates x 4 MMAs, N = 64)  +  1 * b  (one MMA, N = 256)      -- issued ahead of the step
-//   acc      += h_{t-1} * R^T                             (4 MMAs, N = 256; R as [4*64 rows][64 k])
-// Two row threads per batch row (8 warps: two per scheduler, so that one hides the other's latencies -- with one thread per
-// row the cell phase of 64 units x 5 nonlinearities ran at half the speed) read the accumulator 16 units at a time (4 gates
-// x 16 columns), keep the cell state c of their 32 units in registers (fp32), write h_t into the shared-memory tile the next step multiplies and a bulk store sends to
-// `states[0]`, and store c_t and the four cached activations straight to global memory (a thread owns 128 contiguous
-// bytes per value kind).  The activation cache is written in the layout of the REVERSE loop's own tile (one CTA per head,
-// 16 batch rows: frnn_bwd_kernel reads it as it reads its forward kernel's), so only the forward loop changes.
+// at the kernel): the accumulator of a step is [128 rows][4 gates x 64] fp32 = 256 columns of tensor memory (two of
+// them alternate), filled by
+//   acc      = 1 * b  (one MMA, N = 256, overwriting);  acc[:, g] += Wx_t[g] * I  (4 gates x 4 MMAs, N = 64)  -- issued ahead
+//   acc     += h_{t-1} * R^T                            (4 MMAs, N = 256; R as [4*64 rows][64 k])
+// Two row threads per batch row (8 warps, two per scheduler; a warp reads the tensor-memory lanes of its quarter, so
+// warps w and w + 4 share 32 rows and split the 64 units) read the accumulator 16 units at a time (4 gates x 16 columns),
+// keep the cell state c of their 32 units in registers (fp32) and write h_t into the shared-memory tile that the next
+// step multiplies and a bulk store sends to `states[0]`.  After the arrival that hands h_t on, c_t and the four cached
+// activations go straight to global memory: a thread owns 64 contiguous bytes per value kind, neighbouring lanes swap
+// halves, and each 32-byte store instruction covers 16 rows x 64 bytes.  The activation cache is written in the layout of
+// the REVERSE loop's own tile (one CTA per head, 16 batch rows: frnn_bwd_kernel reads it as it reads its forward
+// kernel's), so only the forward loop changes.
 // Wx_t arrives as one tensor-map copy of [4 gates][128 rows][64] per step into a ring of two 64 KB stages; the stage of
 // step t is refilled with step t+2 as soon as the step's MMAs are known to have completed.
 struct WideGatesParams {
