@@ -532,7 +532,7 @@ const char* frnn_status_string(int code) {
     case FRNN_OK: return "ok";
     case FRNN_ERR_NULL: return "frnn: a required pointer is NULL";
     case FRNN_ERR_CELL: return "frnn: unknown cell (expected lstm, gru, elman or slstm)";
-    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {32,64,96,128,192,256} or a multiple of 64 up to 1024; float32: a multiple of 4 up to 1024)";
+    case FRNN_ERR_SHAPE: return "frnn: unsupported shape (B,T,N >= 1; head_dim in {16,32,64,96,128,192,256} or a multiple of 64 up to 1024; float32: a multiple of 4 up to 1024)";
     case FRNN_ERR_DTYPE: return "frnn: unsupported dtype (Wx/R/b bfloat16 or float16 with states of the same type or float32; or everything float32)";
     case FRNN_ERR_ALIGN: return "frnn: tensor pointers must be 16-byte aligned";
     case FRNN_ERR_PLAN: return "frnn: invalid plan or tile for this problem";

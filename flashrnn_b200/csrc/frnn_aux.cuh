@@ -5,9 +5,9 @@
 namespace FRNN_NS {
 
 // head dims (D = 16*KT) and batch tiles (BT = 8*NT) the time-loop kernels are instantiated for
-#define FRNN_FOREACH_KT(X, ...) X(2, __VA_ARGS__) X(4, __VA_ARGS__) X(6, __VA_ARGS__) X(8, __VA_ARGS__) X(12, __VA_ARGS__) X(16, __VA_ARGS__)
-constexpr int kNumKT = 6;
-constexpr int kKTs[kNumKT] = {2, 4, 6, 8, 12, 16};
+#define FRNN_FOREACH_KT(X, ...) X(1, __VA_ARGS__) X(2, __VA_ARGS__) X(4, __VA_ARGS__) X(6, __VA_ARGS__) X(8, __VA_ARGS__) X(12, __VA_ARGS__) X(16, __VA_ARGS__)
+constexpr int kNumKT = 7;
+constexpr int kKTs[kNumKT] = {1, 2, 4, 6, 8, 12, 16};
 constexpr int kNumNT = 3;
 constexpr int kNTs[kNumNT] = {1, 2, 4};
 

@@ -310,3 +310,20 @@ def test_error_paths(cuda_device):
         flashrnn(Wx, R[:3], b, function="lstm")
     out, last = flashrnn(Wx[:, :0], R, b, function="lstm")
     assert out.shape == (2, 2, 0, 1, 32) and last.shape == (2, 2, 1, 1, 32)
+
+
+@pytest.mark.parametrize("function", CELLS)
+@pytest.mark.parametrize("B,T,N,state_f32", [(3, 7, 2, False), (16, 12, 48, False), (9, 5, 3, True), (300, 6, 4, False), (40, 9, 5, False)])
+def test_parity_head_dim_16(cuda_device, function, B, T, N, state_f32):
+    """Head dim 16, the smallest of the reference's head-dim sweep (16 x 48 heads): one 16-unit tile per gate and CTA,
+    8-row and (large batches of the multi-gate cells) 16-row batch tiles, random cotangent and initial states."""
+    D = 16
+    Wx, R, b, s0 = make_inputs(function, B, T, N, D, seed=B + T + N, random_init=(function != "slstm"), state_f32=state_f32)
+    S = s0.shape[0]
+    g = torch.Generator().manual_seed(5)
+    cot = torch.randn(S, B, T, N, D, generator=g, dtype=torch.float64).to(torch.bfloat16).to(torch.float64)
+    if function == "slstm":
+        cot[1:] = 0
+    got = run_native(function, Wx, R, b, s0, cot=cot, state_f32=state_f32)
+    ref = run_oracle(function, Wx, R, b, s0, cot=cot)
+    assert_parity(function, got, ref, tag=f"{function} D16 B{B} T{T} N{N}", zero_init=(function == "slstm"))
