@@ -46,6 +46,9 @@ WORKLOADS = {
     "LB": ("lstm", 1024, 512, 16, 64, False),    # large-batch LSTM (the reference's batch-size sweeps): 16-row tiles, HBM-side regime
     "LBs": ("lstm", 512, 128, 16, 64, False),    # LB cut to 0.7 GB resident (512 CTAs, same tile): the size ncu captures use
     "GB": ("gru", 1024, 512, 16, 64, False),     # large-batch GRU, as LB
+    # the head-dim sweep of the reference's README figure (LSTM bf16 B16 T1024, head_dim x heads = 768)
+    "H16": ("lstm", 16, 1024, 48, 16, False), "H32": ("lstm", 16, 1024, 24, 32, False), "H64": ("lstm", 16, 1024, 12, 64, False),
+    "H128": ("lstm", 16, 1024, 6, 128, False), "H256": ("lstm", 16, 1024, 3, 256, False), "H768": ("lstm", 16, 1024, 1, 768, False),
 }
 DIMS = {"lstm": (4, 4, 4, 2), "gru": (3, 3, 4, 1), "elman": (1, 1, 1, 1), "slstm": (4, 4, 4, 4)}
 METRIC = "fwd+bwd tokens/sec (B*T/s)"
