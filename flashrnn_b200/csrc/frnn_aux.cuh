@@ -13,9 +13,7 @@ constexpr int kNTs[kNumNT] = {1, 2, 4};
 
 // head dims above 256 (multiples of 64 up to kStreamMaxD) run the streamed kernels: kStreamKT k-steps of R per warp
 // in registers, U = kStreamU units per CTA, cluster size D / kStreamU (up to 16, non-portable above 8)
-constexpr int kStreamKT = 8;
-constexpr int kStreamU = 64;
-constexpr int kStreamMaxD = 1024;
+// (kStreamKT, kStreamU, kStreamMaxD: frnn_common.cuh)
 
 struct LoopKernel {
   const void* fn;      // kernel entry

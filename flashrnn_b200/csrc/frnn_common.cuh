@@ -304,16 +304,23 @@ __device__ __forceinline__ void warp_mma_rows(const uint4 (&Areg)[KT], const ele
 // Continues such a product over the k-steps [k0, k1) whose A fragments do not fit the register file and are streamed
 // from global memory every time step (head dims above 256): fragment k of this warp's row tile sits at asrc[k * 32]
 // (lane offset already applied).  Accumulates into `acc`.  k1 - k0 must be even.
-template <int NT>
+// SMEM: the fragments are a copy of that range kept in shared memory (plain loads) instead of global memory.
+template <int NT, bool SMEM = false>
 __device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k1, const elem_t* opnd, int stride,
                                                 int kofs, int ushift, int slice_elems, int lane, float (&acc)[NT][4]) {
+  auto frag = [&](int k) -> uint4 {
+    if constexpr (SMEM) return asrc[(size_t)k * 32];
+    else return __ldg(asrc + (size_t)k * 32);
+  };
   const int j = lane >> 3, r = lane & 7;
   const int kmask = (1 << ushift) - 1;
+  // (one accumulator chain: four independent chains were measured and lost -- head dim 768 forward loop 3.64 -> 3.89 ms,
+  // reverse loop 5.00 -> 6.47 ms)
   if constexpr (NT == 1) {
     const uint32_t base = smem_u32(opnd + r * stride + kofs + (j & 1) * 8);
 #pragma unroll 2
     for (int k = k0; k < k1; k += 2) {
-      const uint4 a0 = __ldg(asrc + (size_t)k * 32), a1 = __ldg(asrc + (size_t)(k + 1) * 32);
+      const uint4 a0 = frag(k), a1 = frag(k + 1);
       uint32_t b0, b1, b2, b3;
       const int kk = k + (j >> 1);
       ldmatrix_x4(base + (uint32_t)(((kk >> ushift) * slice_elems + (kk & kmask) * 16) * 2), b0, b1, b2, b3);
@@ -324,7 +331,7 @@ __device__ __forceinline__ void warp_mma_stream(const uint4* asrc, int k0, int k
     const uint32_t base = smem_u32(opnd + ((j >> 1) * 8 + r) * stride + kofs + (j & 1) * 8);
 #pragma unroll 2
     for (int k = k0; k < k1; ++k) {
-      const uint4 a = __ldg(asrc + (size_t)k * 32);
+      const uint4 a = frag(k);
       const uint32_t koff = (uint32_t)(((k >> ushift) * slice_elems + (k & kmask) * 16) * 2);
 #pragma unroll
       for (int np = 0; np < NT / 2; ++np) {
@@ -399,6 +406,21 @@ __device__ __forceinline__ void warp_mma_tiles(const uint4* Areg, const elem_t* 
 // (8-row batch tiles of the 4-gate cells keep only every second thread busy in the pointwise phase).
 __host__ __device__ constexpr int ring_row_len(int U, int BT, int threads) {
   return (U / 2) * BT < threads ? (U / 2) * BT : threads;
+}
+
+// Streamed kernels (head dims above 256): of the k-steps of R that do not fit a warp's registers, as many as the rest of
+// the shared-memory budget holds stay there for all T steps (one 512-byte fragment set per warp and k-step, an even
+// number of them); only what is left is re-read from L2 in every step.  `base_bytes` = the kernel's other shared memory.
+constexpr int kStreamKT = 8;      // k-steps of R a warp of the streamed kernels keeps in registers
+constexpr int kStreamU = 64;      // units per CTA of the streamed kernels (cluster size D / 64, up to 16)
+constexpr int kStreamMaxD = 1024;
+constexpr size_t kSmemBudget = 227 * 1024;
+__host__ __device__ constexpr int stream_ksm(int D, int kt_regs, int threads, size_t base_bytes) {
+  const int want = D / 16 - kt_regs;
+  const size_t per = (size_t)(threads / 32) * 512;
+  if (want <= 0 || base_bytes + 64 >= kSmemBudget) return 0;
+  const int fit = (int)((kSmemBudget - base_bytes - 64) / per) & ~1;
+  return fit < want ? fit : want;
 }
 
 template <int KT> struct MaxThreads { static constexpr int v = (KT >= 16) ? 256 : (KT >= 12) ? 384 : 512; };

@@ -75,8 +75,12 @@ __host__ __device__ constexpr size_t fwd_smem_bytes(int D, int U, int threads) {
   constexpr int BT = NT * 8;
   constexpr int IPT = (BT + 4 * C::Gr - 1) / (4 * C::Gr);
   const int CS = D / U;
-  return (size_t)2 * CS * BT * (U + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
-         (size_t)kStages * C::Gw * IPT * ring_row_len(U, BT, threads) * 4 + 32;
+  const size_t base = (size_t)2 * CS * BT * (U + 8) * 2 + (size_t)BT * (C::Gr * U + 4) * 4 +
+                      (size_t)kStages * C::Gw * IPT * ring_row_len(U, BT, threads) * 4 + 32;
+  if (D <= 256) return base;
+  // streamed kernels: fragments of R kept in shared memory behind the other buffers (16-byte aligned)
+  const size_t b16 = (base + 15) / 16 * 16;
+  return b16 + (size_t)stream_ksm(D, kStreamKT, threads, b16) * (threads / 32) * 512;
 }
 
 // KT = k-steps (16 columns of R each) a warp keeps in registers.  DYN == false: that is the whole row, D = 16 * KT.
@@ -119,6 +123,18 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
   const uint4* rsrc = p.Rpack + ((((size_t)n * Gr + g_w) * ktot + (unit0 / 16 + ug_w)) * ktot) * 32 + lane;
 #pragma unroll
   for (int k = 0; k < KT; ++k) Rreg[k] = __ldg(rsrc + k * 32);
+  // streamed kernels: the next `ksm` k-steps of this warp's fragments stay in shared memory (each lane reads back only
+  // what it wrote itself), the rest is re-read from L2 in every step
+  int ksm = 0;
+  const uint4* rsm = nullptr;
+  if constexpr (DYN) {
+    const size_t base = (size_t)2 * CS * SL * 2 + (size_t)BT * PS * 4 + (size_t)kStages * Gw * IPT * RL * 4 + 32;
+    const size_t b16 = (base + 15) / 16 * 16;  // as fwd_smem_bytes lays it out
+    ksm = stream_ksm(D, KT, nthr, b16);
+    uint4* mine = reinterpret_cast<uint4*>(smem_raw + b16) + (size_t)warp * ksm * 32 + lane;
+    for (int k = 0; k < ksm; ++k) mine[(size_t)k * 32] = __ldg(rsrc + (size_t)(KT + k) * 32);
+    rsm = mine - (size_t)KT * 32;  // indexed by the k-step itself, like rsrc
+  }
 
   // ---- this thread's items: everything that does not change over time is computed once
   const int half_u = U >> 1, nitems = half_u * BT;
@@ -229,7 +245,10 @@ __global__ void __launch_bounds__(LaunchBounds<CELL, KT>::threads, LaunchBounds<
     {
       float acc[NT][4];
       warp_mma_rows<KT, NT>(Rreg, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
-      if constexpr (DYN) warp_mma_stream<NT>(rsrc, KT, ktot, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
+      if constexpr (DYN) {
+        warp_mma_stream<NT, true>(rsm, KT, KT + ksm, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
+        warp_mma_stream<NT>(rsrc, KT + ksm, ktot, hbuf + (size_t)cur * CS * SL, US, 0, ushift, SL, lane, acc);
+      }
       const int gid = lane >> 2, tig = lane & 3;
       float* dst = pre + g_w * U + ug_w * 16 + gid;
 #pragma unroll
