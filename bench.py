@@ -160,6 +160,14 @@ def bind_to_gpu_numa_node(gpu_index: int):
         bus = bus[-12:] if len(bus) > 12 else bus  # 00000000:1b:00.0 -> 0000:1b:00.0
         node = int(Path(f"/sys/bus/pci/devices/{bus}/numa_node").read_text())
         if node < 0:
+            # sysfs does not say (containers often hide it): ask NVML for the cores closest to the GPU
+            ncpu = os.cpu_count() or 1
+            words = pynvml.nvmlDeviceGetCpuAffinity(pynvml.nvmlDeviceGetHandleByIndex(physical_index(gpu_index)), (ncpu + 63) // 64)
+            near = {64 * i + j for i, w in enumerate(words) for j in range(64) if (int(w) >> j) & 1}
+            allowed = near & os.sched_getaffinity(0)
+            if allowed and allowed != os.sched_getaffinity(0):
+                os.sched_setaffinity(0, allowed)
+                return f"nvml affinity: {len(allowed)} cores"
             return None
         cpus = set()
         for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
