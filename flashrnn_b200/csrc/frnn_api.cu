@@ -203,9 +203,9 @@ static int fill_plan(const frnn_problem* pr, int cs, int bt, int stages, frnn_pl
   pl.batch_tile = cbt;
   pl.threads = plan_threads(cd, pl.units_per_cta, cbt);
   pl.wx_stages = kStages;
-  // measured on B200: LSTM B1024 T512 N16 D64 (128 CTAs of 128 rows) forward loop 2.7 ms against 3.40 ms on the 16-row
+  // measured on B200: LSTM B1024 T512 N16 D64 (128 CTAs of 128 rows) forward loop 2.07 ms against 3.40 ms on the 16-row
   // tiles; B512 T128 N16 (64 CTAs) 0.49 against 0.51 ms -- a step of the 128-row loop takes ~3.8 us however few CTAs run,
-  // so it pays once its CTAs occupy most of the SMs.  GRU B1024 T512 N16 D64: 2.08 against 3.25 ms.
+  // so it pays once its CTAs occupy most of the SMs.  GRU B1024 T512 N16 D64: 1.74 against 3.25 ms.
   pl.wide_forward = wide_gates_problem(*pr) && ccs == 1 && cbt == 16 &&
                     (bt == kWideBatchTile || (!cs && !bt && (long long)(pr->B / kWideBatchTile) * pr->N >= 96));
   pl.cache_slots = cache_slots_of(*pr, cd);

@@ -330,7 +330,6 @@ struct WideGatesParams {
   float fclip;    // > 0: the new h is clamped to [-fclip, fclip]
 };
 constexpr int WL_G = 4;
-constexpr int WL_AHEAD = 6;     // steps between the L2 prefetch of a Wx box and its copy into shared memory
 constexpr int WL_THREADS = 288;  // warps 0-7: two row threads per batch row; warp 8, one lane: every bulk copy and MMA
 constexpr uint32_t WL_OFF_WX = 0;                                   // 2 stages x 4 gate tiles
 constexpr uint32_t WL_OFF_H = WL_OFF_WX + 2 * WL_G * WTILE;         // h_t in tile t & 1
@@ -462,9 +461,6 @@ wide_fwd_gates_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
 #pragma unroll
           for (uint32_t k = 0; k < 4; ++k) umma_parts(d + WX_COL0 + g * WD, a + g * TILE16 + 2 * k, HI, i_lo + 2 * k, HI, idesc64, 1u);
       };
-      // With two stages only one or two copies are in flight, and a box is 512 pieces of 128 bytes on 128 different pages
-      // (batch rows lie far apart): each box is asked into L2 WL_AHEAD steps before its copy into shared memory.
-      for (int t = 2; t < T && t < 2 + WL_AHEAD; ++t) tma_prefetch_5d(tmw, 0, b0, 0, n, t);
       load_wx(0);
       if (T > 1) load_wx(1);
       bool ok = wait_wx(0);
@@ -493,7 +489,6 @@ wide_fwd_gates_kernel(const __grid_constant__ CUtensorMap tm_wx, const __grid_co
           if (!mbar_wait_bounded(&acc_full[t & 1], (uint32_t)((t >> 1) & 1))) { report_timeout(p.status, t); ok = false; break; }
           load_wx(t + 2);
         }
-        if (t + 2 + WL_AHEAD < T) tma_prefetch_5d(tmw, 0, b0, 0, n, t + 2 + WL_AHEAD);
       }
       if (ok) {
         if (mbar_wait_bounded(h_ready, (uint32_t)((T - 1) & 1))) {
