@@ -45,6 +45,7 @@ WORKLOADS = {
     "C5s": ("elman", 1024, 256, 16, 64, False),  # C5 with T cut to 256 (2.1 GB resident): the size ncu captures use
     "LB": ("lstm", 1024, 512, 16, 64, False),    # large-batch LSTM (the reference's batch-size sweeps): 16-row tiles, HBM-side regime
     "LBs": ("lstm", 512, 128, 16, 64, False),    # LB cut to 0.7 GB resident (512 CTAs, same tile): the size ncu captures use
+    "LBm": ("lstm", 1024, 64, 16, 64, False),    # LB with T cut to 64 (1.3 GB resident, 128 CTAs of 128 rows): ncu captures of the memory-bound case
     "GB": ("gru", 1024, 512, 16, 64, False),     # large-batch GRU, as LB
     # the head-dim sweep of the reference's README figure (LSTM bf16 B16 T1024, head_dim x heads = 768)
     "H16": ("lstm", 16, 1024, 48, 16, False), "H32": ("lstm", 16, 1024, 24, 32, False), "H64": ("lstm", 16, 1024, 12, 64, False),
