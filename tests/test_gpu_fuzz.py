@@ -1,6 +1,7 @@
 """GPU: seeded random problems (cell, shape, dtypes, options, forced or default tile) against the fp64 oracle.  Every case
 is small enough for the oracle to finish in a fraction of a second; together they walk through combinations the
 hand-written cases do not pair up (e.g. float16 + fp32 states + gradient clip on a ragged batch at head dim 96)."""
+import os
 import random
 
 import numpy as np
@@ -37,7 +38,7 @@ def _case(seed):
     return function, kind, B, T, N, D, state_f32, opts, big_tile
 
 
-@pytest.mark.parametrize("seed", range(48))
+@pytest.mark.parametrize("seed", range(int(os.environ.get("FRNN_FUZZ_CASES", "48"))))  # more seeds: set FRNN_FUZZ_CASES
 def test_random_problem_against_oracle(cuda_device, seed):
     function, kind, B, T, N, D, state_f32, opts, big_tile = _case(seed)
     dt = getattr(torch, kind)
